@@ -1,0 +1,34 @@
+// Row-wise / element-wise trunk ops and the sampling kernels. See kc_fused.cu, kc_sample.cu.
+#pragma once
+
+#include "kc_common.cuh"
+
+namespace kc {
+
+cudaError_t launch_embed(const uint32_t* w, const bf16* scales, const bf16* biases, const uint32_t* ids, int n, int H,
+                         int bits, int group, float embed_scale, int vocab, bf16* out, cudaStream_t s);
+
+// h = y ? bf16(x + (w_pre ? rms_norm(y, w_pre) : y)) : x ; normed = w_out ? rms_norm(h, w_out) : unused.
+// row_map (optional) picks the input rows. h_out / normed may be null when not wanted.
+cudaError_t launch_add_rmsnorm(const bf16* x, const bf16* y, const bf16* w_pre, const bf16* w_out,
+                               const int32_t* row_map, int rows, int H, float eps, bf16* h_out, bf16* normed,
+                               cudaStream_t s);
+
+cudaError_t launch_rope_kv_write(const bf16* qkv, const bf16* bias, const float* inv_freq, const int32_t* token_pos,
+                                 const int32_t* kv_slot, int n, int Hq, int Hkv, int D, int traditional, int layer,
+                                 int NB, int BS, bf16* pool, bf16* q_out, cudaStream_t s);
+
+cudaError_t launch_glu(const bf16* gu, int n, int F, int gelu, bf16* out, cudaStream_t s);
+cudaError_t launch_softcap(bf16* x, long long total, float cap, cudaStream_t s);
+cudaError_t launch_copy_block(bf16* pool, int layers, int NB, size_t block_elems, uint32_t src, uint32_t dst,
+                              cudaStream_t s);
+
+// Greedy token per logits row; see kc_greedy_rows in kiln_cuda.h.
+cudaError_t launch_greedy_rows(const bf16* logits, int rows, int vocab, int normalize, uint32_t* tokens,
+                               cudaStream_t s);
+// The settle walk per verify segment; see kc_verify_accept in kiln_cuda.h.
+cudaError_t launch_verify_accept(const uint32_t* row_tokens, const int32_t* seq_row_offsets, const uint32_t* draft,
+                                 const int32_t* draft_offsets, const int32_t* draft_len, int n_seqs, int max_commit,
+                                 uint32_t* committed, int32_t* n_committed, int32_t* n_accepted, cudaStream_t s);
+
+}  // namespace kc

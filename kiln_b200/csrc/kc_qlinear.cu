@@ -1,0 +1,609 @@
+// Affine-dequant GEMM for sm_100a. See kc_qlinear.cuh for the data layout.
+//
+// qlinear_umma_kernel — one CTA per (128-row weight tile, k-split):
+//   warp 0      bulk-copies the weight records (cp.async.bulk, mbarrier tx)
+//   warp 1      TMA-loads the activation k-blocks (cp.async.bulk.tensor, 128B swizzle)
+//   warp 2      allocates TMEM, issues tcgen05.mma (weights = A/M side, activations = B/N side)
+//   warps 4-11  unpack the 4/8-bit words, apply scale/bias, write the bf16 A
+//               tile in the K-major 128-byte-swizzled layout the MMA reads;
+//               afterwards drain TMEM (tcgen05.ld) into y or the split-K partials.
+// The accumulator D[n, m] lives in TMEM: lane = weight row n, column = activation row m.
+// Every output element depends only on its own activation row and on a k order
+// fixed by (N, K), which is what lets verify rows share a step with other rows
+// and still reproduce the bits of a one-row decode.
+#include "kc_qlinear.cuh"
+
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+
+namespace kc {
+
+// ---------------------------------------------------------------------------
+// Re-tiling
+// ---------------------------------------------------------------------------
+
+__global__ void qweight_retile_kernel(uint8_t* __restrict__ records, const uint32_t* __restrict__ w,
+                                      const bf16* __restrict__ scales, const bf16* __restrict__ biases,
+                                      int N, int K, int bits, int group, int n_tiles, int kblocks,
+                                      int gpk, uint32_t packed_bytes, uint32_t record_bytes) {
+  const int words_per_row_kb = QL_KB * bits / 32;  // 8 (w4) or 16 (w8)
+  const int words_per_rec = QL_TILE_N * words_per_row_kb;
+  const int sb_per_rec = QL_TILE_N * gpk;
+  const long long per_rec = words_per_rec + sb_per_rec;
+  const long long total = (long long)n_tiles * kblocks * per_rec;
+  const int src_words_per_row = K * bits / 32;
+  const int groups_per_row = K / group;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long rec = i / per_rec;
+    const int e = (int)(i % per_rec);
+    const int tile = (int)(rec / kblocks), kb = (int)(rec % kblocks);
+    uint8_t* base = records + rec * (long long)record_bytes;
+    if (e < words_per_rec) {
+      const int r = e / words_per_row_kb, c = e % words_per_row_kb;
+      const int n = tile * QL_TILE_N + r;
+      uint32_t v = 0;
+      if (n < N) v = w[(long long)n * src_words_per_row + kb * words_per_row_kb + c];
+      if (bits == 4) {
+        uint32_t o = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          o |= ((v >> (8 * j)) & 0xFu) << (4 * j);
+          o |= ((v >> (8 * j + 4)) & 0xFu) << (16 + 4 * j);
+        }
+        v = o;
+      }
+      reinterpret_cast<uint32_t*>(base)[e] = v;
+    } else {
+      const int e2 = e - words_per_rec;
+      const int r = e2 / gpk, gi = e2 % gpk;
+      const int n = tile * QL_TILE_N + r;
+      bf162 sb = __floats2bfloat162_rn(0.f, 0.f);
+      if (n < N) {
+        const int g = (kb * QL_KB + gi * group) / group;
+        sb.x = scales[(long long)n * groups_per_row + g];
+        sb.y = biases[(long long)n * groups_per_row + g];
+      }
+      reinterpret_cast<bf162*>(base + packed_bytes)[e2] = sb;
+    }
+  }
+}
+
+int qlinear_plan_splits(int n_tiles, int kblocks, int sm_count) {
+  if (n_tiles * 2 >= sm_count) return 1;
+  static const int cand[] = {16, 12, 8, 6, 4, 3, 2};
+  for (int s : cand) {
+    if (kblocks % s) continue;
+    if (kblocks / s < 8) continue;
+    if (n_tiles * s <= sm_count) return s;
+  }
+  return 1;
+}
+
+cudaError_t qweight_build(QWeight* out, const uint32_t* w, const bf16* scales, const bf16* biases,
+                          int N, int K, int bits, int group, int sm_count, cudaStream_t s) {
+  QWeight q;
+  q.N = N; q.K = K; q.bits = bits; q.group = group;
+  q.n_tiles = (N + QL_TILE_N - 1) / QL_TILE_N;
+  q.kblocks = K / QL_KB;
+  q.gpk = std::max(1, QL_KB / group);
+  q.packed_bytes = QL_TILE_N * (QL_KB * bits / 8);
+  q.record_bytes = q.packed_bytes + QL_TILE_N * q.gpk * 4;
+  q.splits = qlinear_plan_splits(q.n_tiles, q.kblocks, sm_count);
+  cudaError_t e = cudaMalloc(&q.records, q.bytes());
+  if (e != cudaSuccess) return e;
+  const long long total = (long long)q.n_tiles * q.kblocks * (q.record_bytes / 4);
+  const int threads = 256;
+  const int blocks = (int)std::min<long long>((total + threads - 1) / threads, 148LL * 16);
+  qweight_retile_kernel<<<blocks, threads, 0, s>>>(q.records, w, scales, biases, N, K, bits, group,
+                                                   q.n_tiles, q.kblocks, q.gpk, q.packed_bytes,
+                                                   q.record_bytes);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) { cudaFree(q.records); return e; }
+  *out = q;
+  return cudaSuccess;
+}
+
+void qweight_free(QWeight* w) {
+  if (w && w->records) { cudaFree(w->records); w->records = nullptr; }
+}
+
+// ---------------------------------------------------------------------------
+// Tensor maps for the activation operand
+// ---------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+bool make_tmap_bf16_2d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer,
+                       uint32_t box_inner, uint32_t box_outer, const char** err) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) { *err = "cuTensorMapEncodeTiled entry point unavailable"; return false; }
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {inner * sizeof(bf16)};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box,
+                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { *err = "cuTensorMapEncodeTiled rejected the tensor geometry"; return false; }
+  return true;
+}
+
+bool act_operand_init(ActOperand* op, const bf16* ptr, int rows, int K, const char** err) {
+  op->ptr = ptr; op->rows = rows; op->K = K;
+  if (K % QL_KB) { *err = "activation width must be a multiple of 64"; return false; }
+  if (!make_tmap_bf16_2d(&op->map16, ptr, K, rows, QL_KB, 16, err)) return false;
+  if (!make_tmap_bf16_2d(&op->map64, ptr, K, rows, QL_KB, 64, err)) return false;
+  return true;
+}
+
+// ---------------------------------------------------------------------------
+// Dequantisation of one 8-element chunk -> 8 bf16 (16 bytes)
+// ---------------------------------------------------------------------------
+
+__device__ __forceinline__ uint4 dequant8_w4(uint32_t u, bf162 sb) {
+  const bf162 s2 = __bfloat162bfloat162(sb.x);
+  const bf162 b2 = __bfloat162bfloat162(sb.y);
+  const bf162 c128 = __floats2bfloat162_rn(128.f, 128.f);
+  uint32_t o[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    // 0x4300 | q is the bf16 value 128 + q (exact for q < 128); subtracting 128 is exact.
+    uint32_t t = ((u >> (4 * j)) & 0x000F000Fu) | 0x43004300u;
+    bf162 q = __hsub2(*reinterpret_cast<bf162*>(&t), c128);
+    bf162 wv = __hfma2(q, s2, b2);  // one rounding: bf16(q*s + b)
+    o[j] = *reinterpret_cast<uint32_t*>(&wv);
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+__device__ __forceinline__ uint4 dequant8_w8(uint32_t u0, uint32_t u1, bf162 sb) {
+  const float s = __bfloat162float(sb.x), b = __bfloat162float(sb.y);
+  float f[8];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    // byte k under the exponent of 2^23: the float 8388608 + q, minus 2^23 = q exactly.
+    f[k] = __uint_as_float(__byte_perm(u0, 0x4B000000u, 0x7540u | k)) - 8388608.f;
+    f[4 + k] = __uint_as_float(__byte_perm(u1, 0x4B000000u, 0x7540u | k)) - 8388608.f;
+  }
+  uint32_t o[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) o[j] = pack_bf162(fmaf(f[2 * j], s, b), fmaf(f[2 * j + 1], s, b));
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// ---------------------------------------------------------------------------
+// tcgen05 helpers
+// ---------------------------------------------------------------------------
+
+__device__ __forceinline__ uint64_t umma_smem_desc_sw128(uint32_t smem_addr) {
+  // K-major, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);       // start address
+  d |= (uint64_t)1 << 16;                           // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;                 // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                           // descriptor version (Blackwell)
+  d |= (uint64_t)2 << 61;                           // SWIZZLE_128B
+  return d;
+}
+
+__device__ __forceinline__ uint32_t umma_idesc_bf16(int m, int n) {
+  uint32_t d = 0;
+  d |= 1u << 4;                    // D format f32
+  d |= 1u << 7;                    // A format bf16
+  d |= 1u << 10;                   // B format bf16
+  // a_major (bit 15) = b_major (bit 16) = 0: both K-major
+  d |= (uint32_t)(n >> 3) << 17;   // N
+  d |= (uint32_t)(m >> 4) << 24;   // M
+  return d;
+}
+
+__device__ __forceinline__ void umma_bf16_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                             uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+        "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// ---------------------------------------------------------------------------
+// The kernel
+// ---------------------------------------------------------------------------
+
+constexpr int QL_THREADS = 384;        // 12 warps
+constexpr int QL_DQ_WARP0 = 4;         // first dequant/epilogue warp
+constexpr int QL_DQ_WARPS = 8;
+constexpr int QL_A_BYTES = QL_TILE_N * 128;  // one A stage
+
+struct QlKernelParams {
+  const uint8_t* records;
+  uint32_t record_bytes, packed_bytes;
+  int N, n_tiles, kblocks, bits, gpk;
+  int M, m_pad;          // live rows, rows rounded up to 16
+  int row0;              // first activation row
+  int splits, kb_per_split;
+  int a_stages, r_stages;
+  uint32_t raw_stride;   // record_bytes rounded up to 128
+  uint32_t tmem_cols;    // power of two >= max(32, m_pad)
+  bf16* y; int ldy;
+  float* partial;
+  uint32_t* status;
+};
+
+__global__ void __launch_bounds__(QL_THREADS, 1)
+qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_constant__ CUtensorMap map64,
+                    const QlKernelParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // 1024-byte alignment for the swizzled tiles.
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int AS = p.a_stages, RS = p.r_stages;
+  const uint32_t b_bytes = (uint32_t)p.m_pad * 128u;
+  uint8_t* sA = smem;
+  uint8_t* sB = sA + (size_t)AS * QL_A_BYTES;
+  uint8_t* sR = sB + (size_t)AS * b_bytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sR + (size_t)RS * p.raw_stride);
+  uint64_t* raw_full = bars;
+  uint64_t* raw_empty = raw_full + RS;
+  uint64_t* b_full = raw_empty + RS;
+  uint64_t* a_ready = b_full + AS;
+  uint64_t* ab_empty = a_ready + AS;
+  uint64_t* acc_full = ab_empty + AS;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x, split = blockIdx.y;
+  const int kb0 = split * p.kb_per_split;
+  const int nkb = p.kb_per_split;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < RS; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], QL_DQ_WARPS); }
+    for (int i = 0; i < AS; ++i) { mbar_init(&b_full[i], 1); mbar_init(&a_ready[i], QL_DQ_WARPS); mbar_init(&ab_empty[i], 1); }
+    mbar_init(acc_full, 1);
+    mbar_fence_init();
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(p.tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (warp == 1 && lane == 0) { tma_prefetch_desc(&map16); tma_prefetch_desc(&map64); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---- weight record producer ----
+    if (lane == 0) {
+      const uint8_t* src = p.records + ((size_t)tile * p.kblocks + kb0) * p.record_bytes;
+      for (int i = 0; i < nkb; ++i) {
+        const int rs = i % RS; const uint32_t ph = (i / RS) & 1;
+        if (!mbar_wait(&raw_empty[rs], ph ^ 1, p.status, KC_DEV_QLINEAR | 1)) break;
+        mbar_arrive_expect_tx(&raw_full[rs], p.record_bytes);
+        bulk_g2s(sR + (size_t)rs * p.raw_stride, src + (size_t)i * p.record_bytes, p.record_bytes,
+                 &raw_full[rs]);
+      }
+    }
+  } else if (warp == 1) {
+    // ---- activation producer ----
+    if (lane == 0) {
+      const int n64 = p.m_pad / 64, n16 = (p.m_pad % 64) / 16;
+      for (int i = 0; i < nkb; ++i) {
+        const int as = i % AS; const uint32_t ph = (i / AS) & 1;
+        if (!mbar_wait(&ab_empty[as], ph ^ 1, p.status, KC_DEV_QLINEAR | 2)) break;
+        mbar_arrive_expect_tx(&b_full[as], b_bytes);
+        uint8_t* dst = sB + (size_t)as * b_bytes;
+        const int x = (kb0 + i) * QL_KB;
+        int row = 0;
+        for (int j = 0; j < n64; ++j, row += 64) tma_load_2d(dst + row * 128, &map64, x, p.row0 + row, &b_full[as]);
+        for (int j = 0; j < n16; ++j, row += 16) tma_load_2d(dst + row * 128, &map16, x, p.row0 + row, &b_full[as]);
+      }
+    }
+  } else if (warp == 2) {
+    // ---- MMA issuer ----
+    if (lane == 0) {
+      const int n0 = p.m_pad > 256 ? 256 : p.m_pad;
+      const int n1 = p.m_pad - n0;
+      const uint32_t idesc0 = umma_idesc_bf16(QL_TILE_N, n0);
+      const uint32_t idesc1 = n1 ? umma_idesc_bf16(QL_TILE_N, n1) : 0;
+      bool ok = true;
+      for (int i = 0; i < nkb && ok; ++i) {
+        const int as = i % AS; const uint32_t ph = (i / AS) & 1;
+        ok = mbar_wait(&a_ready[as], ph, p.status, KC_DEV_QLINEAR | 3) &&
+             mbar_wait(&b_full[as], ph, p.status, KC_DEV_QLINEAR | 4);
+        if (!ok) break;
+        tc_fence_after();
+        const uint64_t da = umma_smem_desc_sw128(smem_u32(sA + (size_t)as * QL_A_BYTES));
+        const uint64_t db = umma_smem_desc_sw128(smem_u32(sB + (size_t)as * b_bytes));
+#pragma unroll
+        for (int ks = 0; ks < QL_KB / 16; ++ks) {
+          const uint32_t acc = (i > 0 || ks > 0) ? 1u : 0u;
+          // advancing K by 16 bf16 = 32 bytes inside the swizzle row: +2 in the address field
+          umma_bf16_ss(tmem_base, da + 2 * ks, db + 2 * ks, idesc0, acc);
+          if (n1) umma_bf16_ss(tmem_base + 256, da + 2 * ks, db + (256 * 128 >> 4) + 2 * ks, idesc1, acc);
+        }
+        umma_commit(&ab_empty[as]);
+      }
+      umma_commit(acc_full);
+    }
+  } else if (warp >= QL_DQ_WARP0) {
+    // ---- dequantisers ----
+    const int td = threadIdx.x - QL_DQ_WARP0 * 32;  // 0..255
+    const int c = td & 7, r0 = td >> 3;
+    const int gi = (p.gpk == 2) ? (c >> 2) : 0;
+    bool ok = true;
+    for (int i = 0; i < nkb && ok; ++i) {
+      const int rs = i % RS; const uint32_t rph = (i / RS) & 1;
+      const int as = i % AS; const uint32_t aph = (i / AS) & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(&raw_full[rs], rph, p.status, KC_DEV_QLINEAR | 5));
+      if (!ok) break;
+      const uint8_t* rec = sR + (size_t)rs * p.raw_stride;
+      const bf162* sb = reinterpret_cast<const bf162*>(rec + p.packed_bytes);
+      uint32_t u[4][2]; bf162 sbv[4];
+      if (p.bits == 4) {
+        const uint32_t* pk = reinterpret_cast<const uint32_t*>(rec);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { const int r = r0 + 32 * k; u[k][0] = pk[r * 8 + c]; u[k][1] = 0; sbv[k] = sb[r * p.gpk + gi]; }
+      } else {
+        const uint2* pk = reinterpret_cast<const uint2*>(rec);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { const int r = r0 + 32 * k; uint2 v = pk[r * 8 + c]; u[k][0] = v.x; u[k][1] = v.y; sbv[k] = sb[r * p.gpk + gi]; }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&raw_empty[rs]);
+      ok = __all_sync(0xffffffffu, mbar_wait(&ab_empty[as], aph ^ 1, p.status, KC_DEV_QLINEAR | 6));
+      if (!ok) break;
+      uint8_t* a = sA + (size_t)as * QL_A_BYTES;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int r = r0 + 32 * k;
+        const uint4 v = (p.bits == 4) ? dequant8_w4(u[k][0], sbv[k]) : dequant8_w8(u[k][0], u[k][1], sbv[k]);
+        *reinterpret_cast<uint4*>(a + r * 128 + ((c ^ (r & 7)) << 4)) = v;
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&a_ready[as]);
+    }
+    // ---- epilogue: TMEM -> global ----
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(acc_full, 0, p.status, KC_DEV_QLINEAR | 7));
+    if (ok) {
+      tc_fence_after();
+      const int q = warp & 3;                       // TMEM lane quarter this warp may read
+      const int half = (warp - QL_DQ_WARP0) >> 2;   // two warps share a quarter: split the columns
+      const int n = tile * QL_TILE_N + q * 32 + lane;
+      const int chunks = p.m_pad / 16;
+      for (int ch = half; ch < chunks; ch += 2) {
+        uint32_t v[16];
+        tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + ch * 16, v);
+        if (n < p.N) {
+          if (p.splits == 1) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int m = ch * 16 + j;
+              if (m < p.M) p.y[(size_t)(p.row0 + m) * p.ldy + n] = __float2bfloat16_rn(__uint_as_float(v[j]));
+            }
+          } else {
+            float* dst = p.partial + (size_t)split * p.M * p.N;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int m = ch * 16 + j;
+              if (m < p.M) dst[(size_t)m * p.N + n] = __uint_as_float(v[j]);
+            }
+          }
+        }
+      }
+    }
+  }
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(p.tmem_cols)
+                 : "memory");
+  }
+}
+
+cudaError_t qlinear_umma(const QLinearLaunch& l, cudaStream_t s) {
+  const QWeight& w = *l.w;
+  if (l.M < 1 || l.M > QL_MAX_M) return cudaErrorInvalidValue;
+  QlKernelParams p;
+  p.records = w.records; p.record_bytes = w.record_bytes; p.packed_bytes = w.packed_bytes;
+  p.N = w.N; p.n_tiles = w.n_tiles; p.kblocks = w.kblocks; p.bits = w.bits; p.gpk = w.gpk;
+  p.M = l.M; p.m_pad = (l.M + 15) & ~15; p.row0 = l.row0;
+  if (l.row0 % 16 || l.row0 + p.m_pad > l.x->rows) return cudaErrorInvalidValue;
+  p.splits = w.splits; p.kb_per_split = w.kblocks / w.splits;
+  p.raw_stride = (w.record_bytes + 127) & ~127u;
+  uint32_t cols = 32; while ((int)cols < p.m_pad) cols <<= 1;
+  p.tmem_cols = cols;
+  p.y = l.y; p.ldy = l.ldy; p.partial = l.partial; p.status = l.status;
+  // Shared memory plan: A+B ring (2..4 stages), the rest for the raw ring (<= 16).
+  const size_t budget = 200 * 1024;
+  const size_t ab = QL_A_BYTES + (size_t)p.m_pad * 128;
+  int as = (int)std::min<size_t>(4, (budget - 4 * p.raw_stride) / ab);
+  if (as < 2) as = 2;
+  as = std::min(as, std::max(2, p.kb_per_split));
+  size_t left = budget - (size_t)as * ab;
+  int rs = (int)std::min<size_t>(16, left / p.raw_stride);
+  if (rs < 2) rs = 2;
+  p.a_stages = as; p.r_stages = rs;
+  const size_t smem = 1024 + (size_t)as * ab + (size_t)rs * p.raw_stride + (2 * rs + 3 * as + 1) * 8 + 16;
+  static size_t configured = 0;
+  if (smem > configured) {
+    cudaError_t e = cudaFuncSetAttribute(qlinear_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)std::max<size_t>(smem, 227 * 1024 - 1024));
+    if (e != cudaSuccess) return e;
+    configured = std::max<size_t>(smem, 227 * 1024 - 1024);
+  }
+  dim3 grid(w.n_tiles, w.splits);
+  qlinear_umma_kernel<<<grid, QL_THREADS, smem, s>>>(l.x->map16, l.x->map64, p);
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------
+// Split-K reduction
+// ---------------------------------------------------------------------------
+
+__global__ void qlinear_reduce_kernel(const float* __restrict__ partial, int splits, int M, int N,
+                                      bf16* __restrict__ y, int ldy) {
+  const long long total = (long long)M * N / 2;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long e = i * 2;
+    const int m = (int)(e / N), n = (int)(e % N);
+    float2 acc = *reinterpret_cast<const float2*>(partial + e);
+    for (int s = 1; s < splits; ++s) {
+      const float2 v = *reinterpret_cast<const float2*>(partial + (size_t)s * M * N + e);
+      acc.x += v.x; acc.y += v.y;
+    }
+    *reinterpret_cast<bf162*>(y + (size_t)m * ldy + n) = __floats2bfloat162_rn(acc.x, acc.y);
+  }
+}
+
+cudaError_t qlinear_reduce_splits(const float* partial, int splits, int M, int N, bf16* y, int ldy,
+                                  cudaStream_t s) {
+  const long long total = (long long)M * N / 2;
+  const int threads = 256;
+  const int blocks = (int)std::min<long long>((total + threads - 1) / threads, 148LL * 8);
+  qlinear_reduce_kernel<<<blocks, threads, 0, s>>>(partial, splits, M, N, y, ldy);
+  return cudaGetLastError();
+}
+
+// ---------------------------------------------------------------------------
+// Development cross-check: the same GEMM on mma.sync (legacy tensor path).
+// ---------------------------------------------------------------------------
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm_x2(uint32_t (&r)[2], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];"
+               : "=r"(r[0]), "=r"(r[1]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+constexpr int QS_LD = 72;  // padded row (elements) for conflict-free ldmatrix
+
+__global__ void __launch_bounds__(256)
+qlinear_mma_sync_kernel(const uint8_t* __restrict__ records, uint32_t record_bytes, uint32_t packed_bytes,
+                        int N, int kblocks, int bits, int gpk, const bf16* __restrict__ x, int ldx, int M,
+                        int splits, int kb_per_split, bf16* __restrict__ y, int ldy, float* __restrict__ partial) {
+  __shared__ __align__(16) bf16 sA[QL_TILE_N * QS_LD];
+  __shared__ __align__(16) bf16 sX[64 * QS_LD];
+  const int tile = blockIdx.x, split = blockIdx.y, m0 = blockIdx.z * 64;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c = threadIdx.x & 7, r0 = threadIdx.x >> 3;
+  const int gi = (gpk == 2) ? (c >> 2) : 0;
+  float acc[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+
+  for (int i = 0; i < kb_per_split; ++i) {
+    const int kb = split * kb_per_split + i;
+    const uint8_t* rec = records + ((size_t)tile * kblocks + kb) * record_bytes;
+    const bf162* sb = reinterpret_cast<const bf162*>(rec + packed_bytes);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int r = r0 + 32 * k;
+      uint4 v;
+      if (bits == 4) v = dequant8_w4(reinterpret_cast<const uint32_t*>(rec)[r * 8 + c], sb[r * gpk + gi]);
+      else { const uint2 u = reinterpret_cast<const uint2*>(rec)[r * 8 + c]; v = dequant8_w8(u.x, u.y, sb[r * gpk + gi]); }
+      *reinterpret_cast<uint4*>(&sA[r * QS_LD + c * 8]) = v;
+    }
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int idx = threadIdx.x + 256 * k;
+      const int row = idx >> 3, ch = idx & 7;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (m0 + row < M) v = *reinterpret_cast<const uint4*>(x + (size_t)(m0 + row) * ldx + kb * QL_KB + ch * 8);
+      *reinterpret_cast<uint4*>(&sX[row * QS_LD + ch * 8]) = v;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+      uint32_t a[4];
+      ldsm_x4(a, &sA[(warp * 16 + (lane & 15)) * QS_LD + ks * 16 + (lane >> 4) * 8]);
+#pragma unroll
+      for (int nt = 0; nt < 8; ++nt) {
+        uint32_t b[2];
+        ldsm_x2(b, &sX[(nt * 8 + (lane & 7)) * QS_LD + ks * 16 + ((lane >> 3) & 1) * 8]);
+        mma_bf16_16816(acc[nt], a, b);
+      }
+    }
+    __syncthreads();
+  }
+  const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+  for (int nt = 0; nt < 8; ++nt) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = tile * QL_TILE_N + warp * 16 + g + (j >> 1) * 8;
+      const int m = m0 + nt * 8 + 2 * t + (j & 1);
+      if (n < N && m < M) {
+        if (splits == 1) y[(size_t)m * ldy + n] = __float2bfloat16_rn(acc[nt][j]);
+        else partial[((size_t)split * M + m) * N + n] = acc[nt][j];
+      }
+    }
+  }
+}
+
+cudaError_t qlinear_mma_sync(const QLinearLaunch& l, cudaStream_t s) {
+  const QWeight& w = *l.w;
+  dim3 grid(w.n_tiles, w.splits, (l.M + 63) / 64);
+  qlinear_mma_sync_kernel<<<grid, 256, 0, s>>>(w.records, w.record_bytes, w.packed_bytes, w.N, w.kblocks,
+                                               w.bits, w.gpk, l.x->ptr + (size_t)l.row0 * l.x->K, l.x->K, l.M, w.splits,
+                                               w.kblocks / w.splits, l.y + (size_t)l.row0 * l.ldy, l.ldy, l.partial);
+  return cudaGetLastError();
+}
+
+}  // namespace kc

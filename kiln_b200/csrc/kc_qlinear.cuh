@@ -1,0 +1,87 @@
+// Affine-quantised linear layer: y[M, N] = x[M, K] · dequant(W)ᵀ.
+//
+// Replaces mlx_quantized_matmul(x, w, scales, biases, transpose=true, group,
+// bits, "affine") as kiln calls it (crates/kiln-mlx/src/ops.rs:362-388;
+// crates/kiln-models/src/nn.rs:79-102, 179-193).
+//
+// Device layout ("records"). At load the mlx tensors (u32 [N, K*bits/32],
+// bf16 scales/biases [N, K/group]) are re-tiled so that everything one CTA
+// needs for one k-block is ONE contiguous, 16-byte aligned run that a single
+// bulk copy brings into shared memory:
+//
+//   record(tile t, kblock kb) = packed[128 rows][64*bits/8 bytes]
+//                             ++ sb[128 rows][gpk] as bf162 (scale, bias)
+//
+// with 128 output rows per tile, 64 input features per k-block and gpk =
+// max(1, 64/group) groups per k-block (group 128: the pair is repeated for both
+// k-blocks of the group). Rows past N are zero (scale = bias = 0 ⇒ w = 0).
+// 4-bit words are nibble-permuted so that (u >> 4j) & 0x000F000F yields the
+// element pair (2j, 2j+1) in bf162 order; 8-bit words keep mlx's byte order.
+#pragma once
+
+#include "kc_common.cuh"
+
+namespace kc {
+
+constexpr int QL_TILE_N = 128;  // output features per tile = UMMA M
+constexpr int QL_KB = 64;       // input features per k-block = one 128-byte swizzle row of bf16
+constexpr int QL_MAX_M = 512;   // activation rows per launch (TMEM columns)
+
+struct QWeight {
+  uint8_t* records = nullptr;  // [n_tiles][kblocks][record_bytes]
+  int N = 0, K = 0, bits = 0, group = 0;
+  int n_tiles = 0, kblocks = 0, gpk = 0;
+  uint32_t packed_bytes = 0;   // per record
+  uint32_t record_bytes = 0;
+  int splits = 1;              // fixed function of (N, K): never of M
+  size_t bytes() const { return (size_t)n_tiles * kblocks * record_bytes; }
+  // Algorithmic bytes of the mlx tensors this weight was built from.
+  size_t mlx_bytes() const { return (size_t)N * K * bits / 8 + (size_t)2 * N * (K / group) * 2; }
+};
+
+// Activation operand: a bf16 [rows, K] row-major device buffer plus the two
+// tensor maps (16-row and 64-row boxes of 64 features, 128-byte swizzle) the
+// TMA loads use.
+struct ActOperand {
+  const bf16* ptr = nullptr;
+  int rows = 0;  // allocated rows (multiple of 16)
+  int K = 0;
+  CUtensorMap map16;
+  CUtensorMap map64;
+};
+
+struct QLinearLaunch {
+  const QWeight* w;
+  const ActOperand* x;
+  int row0;         // first activation row of this launch (x, y and partial are indexed from it)
+  int M;            // live activation rows, 1..QL_MAX_M
+  bf16* y;          // [M, ldy] bf16 when the weight has splits == 1 (else unused)
+  int ldy;
+  float* partial;   // [splits][M][N] fp32 workspace when splits > 1 (rows relative to row0)
+  uint32_t* status; // device status word
+};
+
+// Fixed split-K plan: a function of the weight's shape only, so a row's
+// accumulation order never depends on how many rows ride the step.
+int qlinear_plan_splits(int n_tiles, int kblocks, int sm_count);
+
+// Re-tile on the device. w/scales/biases are device pointers in mlx layout.
+cudaError_t qweight_build(QWeight* out, const uint32_t* w, const bf16* scales, const bf16* biases,
+                          int N, int K, int bits, int group, int sm_count, cudaStream_t s);
+void qweight_free(QWeight* w);
+
+// Creates the tensor maps of an activation buffer. Returns false (and sets
+// *err) if the driver entry point is unavailable or rejects the geometry.
+bool act_operand_init(ActOperand* op, const bf16* ptr, int rows, int K, const char** err);
+
+// The product kernel (tcgen05 + TMEM + TMA). Returns a CUDA error.
+cudaError_t qlinear_umma(const QLinearLaunch& l, cudaStream_t s);
+// Development cross-check on the legacy tensor path (mma.sync); same records,
+// same split plan, same outputs up to accumulation order inside the MMA.
+cudaError_t qlinear_mma_sync(const QLinearLaunch& l, cudaStream_t s);
+
+// out[m, n] = bf16(sum over splits of partial[s][m][n]) in split order.
+cudaError_t qlinear_reduce_splits(const float* partial, int splits, int M, int N, bf16* y, int ldy,
+                                  cudaStream_t s);
+
+}  // namespace kc

@@ -1,0 +1,131 @@
+// Greedy sampling and the verify settle walk on the device.
+#include "kc_fused.cuh"
+
+namespace kc {
+
+namespace {
+
+struct ArgMax { float v; int i; };
+__device__ __forceinline__ ArgMax better(ArgMax a, ArgMax b) {
+  // larger value wins; on equal values the lower index wins (MLX argmax tie-break as
+  // observed in docs/decisions/0004-golden-parity-device-scope-and-dtype-aware-delta.md:53-56)
+  if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
+  return a;
+}
+
+// sample_from_row + Sampler::sample, greedy lane (crates/kiln-engine/src/engine.rs:879-901,
+// crates/kiln-engine/src/sampler.rs:100-104): logprobs = logits - logsumexp(logits) in the
+// logits dtype, then argmax. The logsumexp accumulates in fp32 and is rounded to bf16 before
+// the subtraction; the subtraction result is rounded to bf16, which can merge neighbouring
+// logits into ties — hence the explicit lowest-index rule.
+// normalize == 0: argmax of the raw row (crates/kiln-models/src/draft.rs:379-381).
+__global__ void __launch_bounds__(1024)
+greedy_rows_kernel(const bf16* __restrict__ logits, int vocab, int normalize, uint32_t* __restrict__ tokens) {
+  __shared__ float red_m[32], red_s[32];
+  __shared__ ArgMax red_a[32];
+  __shared__ float s_lse;
+  const bf16* row = logits + (size_t)blockIdx.x * vocab;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  if (normalize) {
+    float m = -INFINITY, s = 0.f;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+      const float x = __bfloat162float(row[i]);
+      if (x > m) { s = s * __expf(m - x) + 1.f; m = x; }
+      else s += __expf(x - m);
+    }
+    // merge (m, s) pairs
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float m2 = __shfl_xor_sync(0xffffffffu, m, o), s2 = __shfl_xor_sync(0xffffffffu, s, o);
+      const float mm = fmaxf(m, m2);
+      s = (m == -INFINITY ? 0.f : s * __expf(m - mm)) + (m2 == -INFINITY ? 0.f : s2 * __expf(m2 - mm));
+      m = mm;
+    }
+    if (lane == 0) { red_m[warp] = m; red_s[warp] = s; }
+    __syncthreads();
+    if (warp == 0) {
+      m = lane < nw ? red_m[lane] : -INFINITY;
+      s = lane < nw ? red_s[lane] : 0.f;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float m2 = __shfl_xor_sync(0xffffffffu, m, o), s2 = __shfl_xor_sync(0xffffffffu, s, o);
+        const float mm = fmaxf(m, m2);
+        s = (m == -INFINITY ? 0.f : s * __expf(m - mm)) + (m2 == -INFINITY ? 0.f : s2 * __expf(m2 - mm));
+        m = mm;
+      }
+      if (lane == 0) s_lse = bf16_round(m + logf(s));
+    }
+    __syncthreads();
+  }
+  const float lse = normalize ? s_lse : 0.f;
+  ArgMax best{-INFINITY, 0x7fffffff};
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    float x = __bfloat162float(row[i]);
+    if (normalize) x = bf16_round(x - lse);
+    best = better(best, ArgMax{x, i});
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    ArgMax b2{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+    best = better(best, b2);
+  }
+  if (lane == 0) red_a[warp] = best;
+  __syncthreads();
+  if (warp == 0) {
+    best = lane < nw ? red_a[lane] : ArgMax{-INFINITY, 0x7fffffff};
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      ArgMax b2{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
+      best = better(best, b2);
+    }
+    if (lane == 0) tokens[blockIdx.x] = (uint32_t)(best.i == 0x7fffffff ? 0 : best.i);
+  }
+}
+
+// The settle walk (engine.rs:2336-2366): walk rows j = 0..|draft|; row j's token is committed;
+// it "agrees" when j < |draft| and equals draft[j]; the walk stops after the first row that
+// does not agree. n_committed = rows walked, n_accepted = agreeing rows.
+__global__ void verify_accept_kernel(const uint32_t* __restrict__ row_tokens, const int32_t* __restrict__ seq_row_offsets,
+                                     const uint32_t* __restrict__ draft, const int32_t* __restrict__ draft_offsets,
+                                     const int32_t* __restrict__ draft_len, int n_seqs, int max_commit,
+                                     uint32_t* __restrict__ committed, int32_t* __restrict__ n_committed,
+                                     int32_t* __restrict__ n_accepted) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_seqs) return;
+  const int dl = draft_len[i];
+  if (dl < 0) { n_committed[i] = 0; n_accepted[i] = 0; return; }  // segment samples nothing
+  const uint32_t* rows = row_tokens + seq_row_offsets[i];
+  const uint32_t* d = draft + draft_offsets[i];
+  int acc = 0, com = 0;
+  for (int j = 0; j <= dl; ++j) {
+    const uint32_t tok = rows[j];
+    const bool agrees = j < dl && tok == d[j];
+    if (agrees) ++acc;
+    if (com < max_commit) committed[(size_t)i * max_commit + com] = tok;
+    ++com;
+    if (!agrees) break;
+  }
+  n_committed[i] = com;
+  n_accepted[i] = acc;
+}
+
+}  // namespace
+
+cudaError_t launch_greedy_rows(const bf16* logits, int rows, int vocab, int normalize, uint32_t* tokens,
+                               cudaStream_t s) {
+  if (rows <= 0) return cudaSuccess;
+  greedy_rows_kernel<<<rows, 1024, 0, s>>>(logits, vocab, normalize, tokens);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_verify_accept(const uint32_t* row_tokens, const int32_t* seq_row_offsets, const uint32_t* draft,
+                                 const int32_t* draft_offsets, const int32_t* draft_len, int n_seqs, int max_commit,
+                                 uint32_t* committed, int32_t* n_committed, int32_t* n_accepted, cudaStream_t s) {
+  if (n_seqs <= 0) return cudaSuccess;
+  verify_accept_kernel<<<(n_seqs + 127) / 128, 128, 0, s>>>(row_tokens, seq_row_offsets, draft, draft_offsets,
+                                                            draft_len, n_seqs, max_commit, committed, n_committed,
+                                                            n_accepted);
+  return cudaGetLastError();
+}
+
+}  // namespace kc
