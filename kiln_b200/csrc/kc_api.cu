@@ -69,7 +69,6 @@ struct kc_ctx {
   uint32_t* status = nullptr;  // device status word
   ncclComm_t comm = nullptr;
   int tp_rank = 0, tp_world = 1;
-  int use_mma_sync = 0;        // development switch (KC_QLINEAR=mma_sync)
 };
 
 struct kc_kv {
@@ -157,8 +156,6 @@ extern "C" int kc_ctx_create(int device, kc_ctx_t* out) {
   kc_ctx* c = new kc_ctx;
   c->device = device;
   c->sm_count = prop.multiProcessorCount;
-  const char* sw = getenv("KC_QLINEAR");
-  c->use_mma_sync = (sw && !strcmp(sw, "mma_sync")) ? 1 : 0;
   if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess ||
       cudaMalloc(&c->status, sizeof(uint32_t)) != cudaSuccess ||
       cudaMemsetAsync(c->status, 0, sizeof(uint32_t), c->stream) != cudaSuccess) {
@@ -319,7 +316,7 @@ static cudaError_t run_qlinear(kc_ctx* c, const QWeight& w, const ActOperand& x,
     QLinearLaunch l;
     l.w = &w; l.x = &x; l.row0 = row0; l.M = std::min(QL_MAX_M, M - row0);
     l.y = y; l.ldy = ldy; l.partial = partial; l.status = c->status;
-    cudaError_t e = c->use_mma_sync ? qlinear_mma_sync(l, c->stream) : qlinear_umma(l, c->stream);
+    cudaError_t e = qlinear_umma(l, c->stream);
     if (e != cudaSuccess) return e;
     if (w.splits > 1) {
       e = qlinear_reduce_splits(partial, w.splits, l.M, w.N, y + (size_t)row0 * ldy, ldy, c->stream);

@@ -206,6 +206,7 @@ __device__ __forceinline__ uint64_t umma_smem_desc_sw128(uint32_t smem_addr) {
 }
 
 __device__ __forceinline__ uint32_t umma_idesc_bf16(int m, int n) {
+  // kind::f16 takes A and B of the SAME 16-bit type: an f16 A against a bf16 B is an illegal instruction.
   uint32_t d = 0;
   d |= 1u << 4;                    // D format f32
   d |= 1u << 7;                    // A format bf16
@@ -216,7 +217,7 @@ __device__ __forceinline__ uint32_t umma_idesc_bf16(int m, int n) {
   return d;
 }
 
-__device__ __forceinline__ void umma_bf16_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+__device__ __forceinline__ void umma_f16_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
                                              uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
@@ -361,8 +362,8 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
         for (int ks = 0; ks < QL_KB / 16; ++ks) {
           const uint32_t acc = (i > 0 || ks > 0) ? 1u : 0u;
           // advancing K by 16 bf16 = 32 bytes inside the swizzle row: +2 in the address field
-          umma_bf16_ss(tmem_base, da + 2 * ks, db + 2 * ks, idesc0, acc);
-          if (n1) umma_bf16_ss(tmem_base + 256, da + 2 * ks, db + (256 * 128 >> 4) + 2 * ks, idesc1, acc);
+          umma_f16_ss(tmem_base, da + 2 * ks, db + 2 * ks, idesc0, acc);
+          if (n1) umma_f16_ss(tmem_base + 256, da + 2 * ks, db + (256 * 128 >> 4) + 2 * ks, idesc1, acc);
         }
         umma_commit(&ab_empty[as]);
       }
@@ -508,101 +509,6 @@ cudaError_t qlinear_reduce_splits(const float* partial, int splits, int M, int N
   const int threads = 256;
   const int blocks = (int)std::min<long long>((total + threads - 1) / threads, 148LL * 8);
   qlinear_reduce_kernel<<<blocks, threads, 0, s>>>(partial, splits, M, N, y, ldy);
-  return cudaGetLastError();
-}
-
-// ---------------------------------------------------------------------------
-// Development cross-check: the same GEMM on mma.sync (legacy tensor path).
-// ---------------------------------------------------------------------------
-
-__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
-}
-__device__ __forceinline__ void ldsm_x2(uint32_t (&r)[2], const void* p) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];"
-               : "=r"(r[0]), "=r"(r[1]) : "r"(smem_u32(p)));
-}
-__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
-}
-
-constexpr int QS_LD = 72;  // padded row (elements) for conflict-free ldmatrix
-
-__global__ void __launch_bounds__(256)
-qlinear_mma_sync_kernel(const uint8_t* __restrict__ records, uint32_t record_bytes, uint32_t packed_bytes,
-                        int N, int kblocks, int bits, int gpk, const bf16* __restrict__ x, int ldx, int M,
-                        int splits, int kb_per_split, bf16* __restrict__ y, int ldy, float* __restrict__ partial) {
-  __shared__ __align__(16) bf16 sA[QL_TILE_N * QS_LD];
-  __shared__ __align__(16) bf16 sX[64 * QS_LD];
-  const int tile = blockIdx.x, split = blockIdx.y, m0 = blockIdx.z * 64;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int c = threadIdx.x & 7, r0 = threadIdx.x >> 3;
-  const int gi = (gpk == 2) ? (c >> 2) : 0;
-  float acc[8][4];
-#pragma unroll
-  for (int i = 0; i < 8; ++i)
-#pragma unroll
-    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
-
-  for (int i = 0; i < kb_per_split; ++i) {
-    const int kb = split * kb_per_split + i;
-    const uint8_t* rec = records + ((size_t)tile * kblocks + kb) * record_bytes;
-    const bf162* sb = reinterpret_cast<const bf162*>(rec + packed_bytes);
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const int r = r0 + 32 * k;
-      uint4 v;
-      if (bits == 4) v = dequant8_w4(reinterpret_cast<const uint32_t*>(rec)[r * 8 + c], sb[r * gpk + gi]);
-      else { const uint2 u = reinterpret_cast<const uint2*>(rec)[r * 8 + c]; v = dequant8_w8(u.x, u.y, sb[r * gpk + gi]); }
-      *reinterpret_cast<uint4*>(&sA[r * QS_LD + c * 8]) = v;
-    }
-#pragma unroll
-    for (int k = 0; k < 2; ++k) {
-      const int idx = threadIdx.x + 256 * k;
-      const int row = idx >> 3, ch = idx & 7;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      if (m0 + row < M) v = *reinterpret_cast<const uint4*>(x + (size_t)(m0 + row) * ldx + kb * QL_KB + ch * 8);
-      *reinterpret_cast<uint4*>(&sX[row * QS_LD + ch * 8]) = v;
-    }
-    __syncthreads();
-#pragma unroll
-    for (int ks = 0; ks < 4; ++ks) {
-      uint32_t a[4];
-      ldsm_x4(a, &sA[(warp * 16 + (lane & 15)) * QS_LD + ks * 16 + (lane >> 4) * 8]);
-#pragma unroll
-      for (int nt = 0; nt < 8; ++nt) {
-        uint32_t b[2];
-        ldsm_x2(b, &sX[(nt * 8 + (lane & 7)) * QS_LD + ks * 16 + ((lane >> 3) & 1) * 8]);
-        mma_bf16_16816(acc[nt], a, b);
-      }
-    }
-    __syncthreads();
-  }
-  const int g = lane >> 2, t = lane & 3;
-#pragma unroll
-  for (int nt = 0; nt < 8; ++nt) {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int n = tile * QL_TILE_N + warp * 16 + g + (j >> 1) * 8;
-      const int m = m0 + nt * 8 + 2 * t + (j & 1);
-      if (n < N && m < M) {
-        if (splits == 1) y[(size_t)m * ldy + n] = __float2bfloat16_rn(acc[nt][j]);
-        else partial[((size_t)split * M + m) * N + n] = acc[nt][j];
-      }
-    }
-  }
-}
-
-cudaError_t qlinear_mma_sync(const QLinearLaunch& l, cudaStream_t s) {
-  const QWeight& w = *l.w;
-  dim3 grid(w.n_tiles, w.splits, (l.M + 63) / 64);
-  qlinear_mma_sync_kernel<<<grid, 256, 0, s>>>(w.records, w.record_bytes, w.packed_bytes, w.N, w.kblocks,
-                                               w.bits, w.gpk, l.x->ptr + (size_t)l.row0 * l.x->K, l.x->K, l.M, w.splits,
-                                               w.kblocks / w.splits, l.y + (size_t)l.row0 * l.ldy, l.ldy, l.partial);
   return cudaGetLastError();
 }
 

@@ -17,6 +17,9 @@
 // k-blocks of the group). Rows past N are zero (scale = bias = 0 ⇒ w = 0).
 // 4-bit words are nibble-permuted so that (u >> 4j) & 0x000F000F yields the
 // element pair (2j, 2j+1) in bf162 order; 8-bit words keep mlx's byte order.
+// Weights are dequantised to bf16 (w = bf16(q*scale + bias), one rounding) before
+// the tensor core sees them — the arithmetic class of MLX's own dequantise-then-
+// MMA kernels for wide batches, not of its fp32 row-vector kernels.
 #pragma once
 
 #include "kc_common.cuh"
@@ -74,11 +77,8 @@ void qweight_free(QWeight* w);
 // *err) if the driver entry point is unavailable or rejects the geometry.
 bool act_operand_init(ActOperand* op, const bf16* ptr, int rows, int K, const char** err);
 
-// The product kernel (tcgen05 + TMEM + TMA). Returns a CUDA error.
+// The GEMM (tcgen05 + TMEM + TMA). Returns a CUDA error.
 cudaError_t qlinear_umma(const QLinearLaunch& l, cudaStream_t s);
-// Development cross-check on the legacy tensor path (mma.sync); same records,
-// same split plan, same outputs up to accumulation order inside the MMA.
-cudaError_t qlinear_mma_sync(const QLinearLaunch& l, cudaStream_t s);
 
 // out[m, n] = bf16(sum over splits of partial[s][m][n]) in split order.
 cudaError_t qlinear_reduce_splits(const float* partial, int splits, int M, int N, bf16* y, int ldy,

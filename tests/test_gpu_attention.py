@@ -1,0 +1,105 @@
+"""Paged multi-query attention against the CPU oracle, plus the bit-equality grid of the reference's
+kernel-vs-gather probe (crates/kiln-engine/tests/paged_attn.rs:40-52, 175-182) re-aimed at this
+backend's invariant: verify row j (query length k+1) carries the bits of the one-row decode at the
+same position, for permuted block tables, ragged tails and contexts that straddle chunk boundaries.
+"""
+import numpy as np
+import pytest
+import torch
+
+from kiln_b200 import api
+from oracle import oracle as O
+from tests.conftest import cosine
+
+pytestmark = pytest.mark.gpu
+
+
+def outlier_values(shape, seed):
+    """xorshift-style outlier-heavy values: every 97th value x64 (paged_attn.rs:58-92 of the reference tests)."""
+    g = torch.Generator().manual_seed(seed)
+    v = torch.empty(shape).uniform_(-1, 1, generator=g)
+    v.view(-1)[::97] *= 64.0
+    return (v * 0.25).to(torch.bfloat16)
+
+
+def fill_pools(ctx, spec, seed):
+    """Identical random K/V content in a device pool set and an oracle pool set."""
+    kv = api.PagedKv(ctx, spec)
+    okv = O.OracleKv(spec.layers, spec.kv_heads, spec.head_dim, spec.num_blocks, spec.block_size)
+    arr = okv.array()
+    data = outlier_values(arr.shape, seed)
+    arr[...] = data.view(torch.int16).numpy().view(np.uint16)
+    per_block = spec.layers * 2 * spec.kv_heads * spec.block_size * spec.head_dim * 2
+    for b in range(spec.num_blocks):
+        # kc_kv_write_block payload: per layer the K rows then the V rows (paged.rs:280-304)
+        payload = arr[:, :, b].tobytes()
+        assert len(payload) == per_block
+        kv.write_block_bytes(b, payload)
+    return kv, okv
+
+
+GRID = [
+    # (head_dim, heads, kv_heads, block_size, [(len, offset), ...], softcap, window)
+    (128, 8, 2, 16, [(6, 40)], 0.0, 0),                       # one verify segment, gqa 4
+    (128, 8, 2, 16, [(1, 0), (1, 15), (1, 16), (1, 511), (1, 512), (1, 1300)], 0.0, 0),   # decode rows around tile/chunk edges
+    (128, 8, 2, 16, [(6, 506), (6, 510), (5, 1020), (6, 1023)], 0.0, 0),     # verify segments straddling chunk boundaries
+    (64, 8, 2, 32, [(5, 100), (5, 33), (1, 64)], 0.0, 0),     # head_dim 64, 32-token blocks
+    (128, 7, 1, 16, [(5, 200), (5, 7)], 0.0, 0),              # gqa 7 (3 row tiles)
+    (128, 8, 1, 16, [(5, 90)], 0.0, 0),                       # gqa 8
+    (256, 4, 2, 16, [(4, 70), (4, 600)], 50.0, 0),            # gemma-2 geometry with softcap
+    (256, 4, 2, 16, [(4, 70), (4, 600)], 50.0, 48),           # + sliding window
+    (128, 8, 2, 16, [(40, 0), (23, 100)], 0.0, 0),            # prefill-shaped segments (several work items each)
+]
+
+
+def build_seqs(segs, block_size, num_blocks, seed):
+    rng = np.random.default_rng(seed)
+    perm = rng.permutation(num_blocks)      # permuted block tables
+    at = 0
+    out = []
+    for (ln, off) in segs:
+        nb = (off + ln + block_size - 1) // block_size
+        out.append(api.SeqStep(ln, off, ln, [int(x) for x in perm[at:at + nb]]))
+        at += nb
+    return out
+
+
+@pytest.mark.parametrize("hd,heads,kvh,bs,segs,softcap,window", GRID)
+def test_matches_oracle(ctx, hd, heads, kvh, bs, segs, softcap, window):
+    nb = sum((off + ln + bs - 1) // bs for ln, off in segs) + 3
+    spec = api.KvSpec(2, kvh, hd, nb, bs)
+    kv, okv = fill_pools(ctx, spec, 11)
+    seqs = build_seqs(segs, bs, nb, 5)
+    n = sum(s.len for s in seqs)
+    q = outlier_values((n, heads, hd), 7)
+    scale = hd ** -0.5
+    want = O.paged_attention(okv, 1, q, seqs, scale, softcap, window)
+    got = api.paged_attention(ctx, kv, 1, q.cuda(), seqs, scale, softcap, window).cpu()
+    err = float((got.float() - want.float()).abs().max())
+    mag = max(1.0, float(want.float().abs().max()))
+    assert err <= 2e-2 * mag, f"max-abs {err} at magnitude {mag}"
+    assert cosine(got, want) >= 0.9999
+    assert ctx.device_status() == 0
+
+
+@pytest.mark.parametrize("hd,heads,kvh,bs", [(128, 8, 2, 16), (64, 8, 2, 32), (128, 7, 1, 16), (256, 4, 2, 16)])
+def test_verify_rows_carry_decode_bits(ctx, hd, heads, kvh, bs):
+    """Row j of a (k+1)-row segment == the one-row launch at the same position, bit for bit, also when
+    other sequences share the launch."""
+    offsets = [3, 250, 509, 1019, 1500]
+    k1 = 6
+    nb = sum((o + k1 + bs - 1) // bs for o in offsets) + 2
+    spec = api.KvSpec(1, kvh, hd, nb, bs)
+    kv, _ = fill_pools(ctx, spec, 21)
+    seqs = build_seqs([(k1, o) for o in offsets], bs, nb, 9)
+    n = k1 * len(offsets)
+    q = outlier_values((n, heads, hd), 8).cuda()
+    scale = hd ** -0.5
+    batched = api.paged_attention(ctx, kv, 0, q, seqs, scale).cpu()
+    row = 0
+    for s in seqs:
+        for j in range(s.len):
+            one = api.paged_attention(ctx, kv, 0, q[row:row + 1], [api.SeqStep(1, s.offset + j, 1, s.blocks)], scale).cpu()
+            assert torch.equal(one.view(torch.int16), batched[row:row + 1].view(torch.int16)), \
+                f"offset {s.offset} row {j}: verify row differs from decode row"
+            row += 1

@@ -1,0 +1,221 @@
+"""forward_step / verify_step end to end on small models, against the CPU oracle.
+
+Bars (from the north star): logits max-abs <= 2e-2 and cosine >= 0.9999 in bf16; accept decisions and
+emitted tokens bit-exact given identical logits; greedy output identical with speculation on or off.
+The reference's relational method is used for the last one (crates/kiln-models/tests/spec_decode.rs:1-7,
+392-417): a live speculation-off run on the same device is the baseline.
+"""
+import numpy as np
+import pytest
+import torch
+
+from kiln_b200 import api
+from kiln_b200.synth import PRESETS, synth_checkpoint
+from oracle import oracle as O
+from oracle.bookkeeping import BlockManager, BlockTable, settle_walk
+from tests.conftest import cosine
+
+pytestmark = pytest.mark.gpu
+
+MODELS = ["tiny-llama", "tiny-llama-d128", "tiny-qwen2", "tiny-gemma2"]
+BS = 16
+
+
+def load(ctx, name, num_blocks=64):
+    cfg = PRESETS[name]
+    ck = synth_checkpoint(cfg, seed=0)
+    model = api.CudaModel(ctx, cfg, ck, max_step_tokens=256, max_step_seqs=16)
+    kv = api.PagedKv(ctx, model.kv_spec(num_blocks, BS))
+    omodel = O.OracleModel(cfg, ck)
+    okv = O.OracleKv(cfg.num_hidden_layers, cfg.num_key_value_heads, cfg.head_dim, num_blocks, BS)
+    return cfg, model, kv, omodel, okv
+
+
+def prompts(cfg, lens, seed):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in lens]
+
+
+@pytest.mark.parametrize("name", MODELS)
+def test_logits_and_kv_match_oracle(ctx, name):
+    cfg, model, kv, omodel, okv = load(ctx, name)
+    ps = prompts(cfg, [37, 64, 5], 1)
+    mgr = BlockManager(64, BS)
+    tables = [BlockTable() for _ in ps]
+    # one ragged prefill step over all three prompts, sampling the last row of each
+    seqs, ids = [], []
+    for p, t in zip(ps, tables):
+        t.append_tokens(mgr, len(p))
+        seqs.append(api.SeqStep(len(p), 0, 1, list(t.blocks)))
+        ids += p
+    batch = api.StepBatch(ids, seqs)
+    want = omodel.forward_step(batch, okv)
+    got = model.forward_step(batch, kv)
+    ctx.sync()
+    got = got.cpu()
+    assert float((got.float() - want.float()).abs().max()) <= 2e-2
+    assert cosine(got, want) >= 0.9999
+    # then a mixed step: two verify segments (k = 4) and one plain decode
+    g = torch.Generator().manual_seed(2)
+    seqs, ids = [], []
+    for i, (p, t) in enumerate(zip(ps, tables)):
+        ln = 5 if i < 2 else 1
+        off = t.num_tokens
+        t.append_tokens(mgr, ln)
+        seqs.append(api.SeqStep(ln, off, ln, list(t.blocks)))
+        ids += torch.randint(0, cfg.vocab_size, (ln,), generator=g).tolist()
+    batch = api.StepBatch(ids, seqs)
+    want = omodel.forward_step(batch, okv)
+    got = model.forward_step(batch, kv)
+    ctx.sync()
+    got = got.cpu()
+    assert got.shape == want.shape == (11, cfg.vocab_size)
+    assert float((got.float() - want.float()).abs().max()) <= 2e-2
+    assert cosine(got, want) >= 0.9999
+    # greedy tokens from IDENTICAL logits are bit-exact
+    assert np.array_equal(api.greedy_rows(ctx, got.cuda()).cpu().numpy().astype(np.uint32), O.greedy_rows(got))
+    # K/V rows written by both steps agree with the oracle's pools (bf16 values within 2 ulp)
+    arr = okv.array()
+    worst = 0.0
+    for t in tables:
+        for b in t.blocks:
+            dev = np.frombuffer(kv.read_block_bytes(b), dtype=np.int16).reshape(cfg.num_hidden_layers, 2, -1)
+            ref = arr[:, :, b].reshape(cfg.num_hidden_layers, 2, -1).view(np.int16)
+            d = torch.from_numpy(dev.copy()).view(torch.bfloat16).float()
+            r = torch.from_numpy(ref.copy()).view(torch.bfloat16).float()
+            worst = max(worst, float((d - r).abs().max()))
+    assert worst <= 4e-2, f"KV rows differ from the oracle by {worst}"
+    assert ctx.device_status() == 0
+
+
+def greedy_run(model, kv, prompt_lists, n_new, drafter=None, k=4, num_blocks=64):
+    """Greedy generation of n_new tokens per prompt through verify_step. drafter(i, history) -> up to k ids."""
+    mgr = BlockManager(num_blocks, BS)
+    tables = [BlockTable() for _ in prompt_lists]
+    hist = [list(p) for p in prompt_lists]
+    gen = [[] for _ in prompt_lists]
+    # prefill everything but the last prompt token
+    seqs, ids = [], []
+    for p, t in zip(prompt_lists, tables):
+        t.append_tokens(mgr, len(p) - 1)
+        seqs.append(api.SeqStep(len(p) - 1, 0, 0, list(t.blocks)))
+        ids += p[:-1]
+    model.verify_step(api.StepBatch(ids, seqs), kv)
+    rounds = 0
+    while any(len(g) < n_new for g in gen):
+        seqs, ids, drafts, live = [], [], [], []
+        for i, t in enumerate(tables):
+            if len(gen[i]) >= n_new:
+                continue
+            remaining = n_new - len(gen[i])
+            d = list(drafter(i, hist[i]))[: min(k, remaining - 1)] if drafter else []
+            off = t.num_tokens
+            t.append_tokens(mgr, 1 + len(d))
+            seqs.append(api.SeqStep(1 + len(d), off, 1 + len(d), list(t.blocks)))
+            ids += [hist[i][-1]] + d
+            drafts.append(d)
+            live.append(i)
+        rows, ncom, nacc = model.verify_step(api.StepBatch(ids, seqs), kv)
+        at = 0
+        for j, i in enumerate(live):
+            seg = rows[at: at + 1 + len(drafts[j])].tolist()
+            at += 1 + len(drafts[j])
+            com, acc = settle_walk(seg, drafts[j])
+            assert (len(com), acc) == (int(ncom[j]), int(nacc[j])), "device walk disagrees with the host walk"
+            before = tables[i].num_tokens - (1 + len(drafts[j]))
+            hist[i] += com
+            gen[i] += com
+            tables[i].truncate(mgr, before + len(com))     # rollback (block.rs:381-396)
+        rounds += 1
+    return gen, rounds
+
+
+@pytest.mark.parametrize("name", MODELS)
+def test_speculation_on_equals_off(ctx, name):
+    cfg, model, kv, _, _ = load(ctx, name)
+    ps = prompts(cfg, [21, 48, 9, 33], 3)
+    n_new = 24
+    base, rounds_off = greedy_run(model, kv, ps, n_new)
+    assert rounds_off == n_new
+
+    # oracle drafter: proposes the true continuation -> every round accepts everything
+    def oracle_drafter(i, hist):
+        done = len(hist) - len(ps[i])
+        return base[i][done: done + 4]
+
+    kv.reset()
+    on, rounds_on = greedy_run(model, kv, ps, n_new, oracle_drafter)
+    assert on == base
+    assert rounds_on <= (n_new + 4) // 5 + 1
+
+    # adversarial drafter (spec_decode.rs:147-198): valid but wrong ids -> every round corrects and rolls back
+    def adversarial(i, hist):
+        return [11, 23, 5, 42]
+
+    kv.reset()
+    adv, _ = greedy_run(model, kv, ps, n_new, adversarial)
+    assert adv == base
+
+    # injected acceptance p = 0.7 (the headline configuration's drafter)
+    rng = np.random.default_rng(0)
+
+    def injected(i, hist):
+        done = len(hist) - len(ps[i])
+        out = []
+        for j in range(4):
+            true = base[i][done + j] if done + j < len(base[i]) else 0
+            out.append(true if rng.random() < 0.7 else int(rng.integers(0, cfg.vocab_size)))
+        return out
+
+    kv.reset()
+    inj, _ = greedy_run(model, kv, ps, n_new, injected)
+    assert inj == base
+    assert ctx.device_status() == 0
+
+
+def test_draft_chain_matches_stepwise_decode(ctx):
+    """kc_draft_chain (draft.rs:354-388) == gamma separate raw-argmax decode steps."""
+    cfg, model, kv, _, _ = load(ctx, "tiny-llama")
+    p = prompts(cfg, [30], 4)[0]
+    blocks = [7, 2, 9]
+    model.verify_step(api.StepBatch(p[:-1], [api.SeqStep(29, 0, 0, blocks)]), kv)
+    chain = model.draft_chain(kv, p[-1], 29, blocks, 5)
+    kv2 = api.PagedKv(ctx, model.kv_spec(64, BS))
+    model.verify_step(api.StepBatch(p[:-1], [api.SeqStep(29, 0, 0, blocks)]), kv2)
+    tok, step = p[-1], []
+    for j in range(5):
+        lg = model.forward_step(api.StepBatch([tok], [api.SeqStep(1, 29 + j, 1, blocks)]), kv2)
+        ctx.sync()
+        tok = int(api.greedy_rows(ctx, lg.clone(), normalize=False)[0])
+        step.append(tok)
+    assert chain == step
+
+
+def test_invalid_batches_are_rejected(ctx):
+    """Validation mirrors nn.rs:1309-1337; errors come back as status + message, never an abort."""
+    cfg, model, kv, _, _ = load(ctx, "tiny-llama")
+    with pytest.raises(api.KcError, match="sequence position"):
+        model.forward_step(api.StepBatch([1, 2, 3], [api.SeqStep(2, 0, 1, [0])]), kv)
+    with pytest.raises(api.KcError, match="samples 3 of its 2"):
+        model.forward_step(api.StepBatch([1, 2], [api.SeqStep(2, 0, 3, [0])]), kv)
+    with pytest.raises(api.KcError, match="pad rows"):
+        model.forward_step(api.StepBatch([1, 2], [api.SeqStep(2, 0, 1, [0])], pad_rows=2), kv)
+    with pytest.raises(api.KcError, match="block"):
+        model.forward_step(api.StepBatch([1] * 20, [api.SeqStep(20, 0, 1, [0])]), kv)
+    with pytest.raises(api.KcError, match="vocabulary"):
+        model.forward_step(api.StepBatch([cfg.vocab_size], [api.SeqStep(1, 0, 1, [0])]), kv)
+    assert model.forward_step(api.StepBatch([1, 2], [api.SeqStep(2, 0, 0, [0])]), kv) is None
+    g, kmax, w = model.envelope()
+    assert (g, kmax, w) == (7, 0, 32)
+
+
+def test_live_object_counter_returns_to_baseline(ctx):
+    """The leak gate of crates/kiln-mlx/src/debug.rs: every create has exactly one destroy."""
+    base = api.live_objects()
+    cfg = PRESETS["tiny-llama"]
+    m = api.CudaModel(ctx, cfg, synth_checkpoint(cfg, 0), 64, 4)
+    kv = api.PagedKv(ctx, m.kv_spec(8, BS))
+    assert api.live_objects() == base + 2
+    kv.close()
+    m.close()
+    assert api.live_objects() == base

@@ -1,0 +1,93 @@
+"""Row-wise ops and sampling kernels against the CPU oracle / plain restatements."""
+import numpy as np
+import pytest
+import torch
+
+from kiln_b200 import api
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("rows,dim", [(1, 256), (7, 2048), (192, 4096), (3, 3584)])
+def test_rms_norm(ctx, rows, dim):
+    g = torch.Generator().manual_seed(rows * 1000 + dim)
+    x = torch.empty(rows, dim).normal_(0, 1.5, generator=g).to(torch.bfloat16)
+    w = torch.empty(dim).normal_(1.0, 0.1, generator=g).to(torch.bfloat16)
+    want = O.rms_norm(x, w, 1e-5)
+    got = api.rms_norm(ctx, x.cuda(), w.cuda(), 1e-5).cpu()
+    # fp32 inside, one bf16 rounding: at most one bf16 ulp apart (summation order differs)
+    diff = (got.float() - want.float()).abs()
+    assert float((diff / want.float().abs().clamp_min(1e-3)).max()) <= 2 ** -7
+
+
+def test_greedy_rows_match_oracle_and_break_ties_low(ctx):
+    g = torch.Generator().manual_seed(3)
+    logits = torch.empty(9, 128256).normal_(0, 2.0, generator=g).to(torch.bfloat16)
+    # an exact tie in the raw logits and a tie created only by the logprob rounding
+    logits[1, 70000] = logits[1].max() + 1
+    logits[1, 300] = logits[1, 70000]
+    logits[2, 5] = 40.0
+    logits[2, 90000] = 40.125   # bf16(40.125 - lse) can equal bf16(40 - lse)
+    want_n = O.greedy_rows(logits, True)
+    want_r = O.greedy_rows(logits, False)
+    got_n = api.greedy_rows(ctx, logits.cuda(), True).cpu().numpy().astype(np.uint32)
+    got_r = api.greedy_rows(ctx, logits.cuda(), False).cpu().numpy().astype(np.uint32)
+    assert np.array_equal(got_n, want_n)
+    assert np.array_equal(got_r, want_r)
+    assert got_n[1] == 300 and got_r[1] == 300
+
+
+def test_verify_accept_walk(ctx):
+    """engine.rs:2336-2366 on four segments: full agreement (bonus), first-row mismatch, mid mismatch, plain decode."""
+    rows = torch.tensor([5, 6, 7, 8,   9, 1, 1,   4, 4, 9, 9,   3], dtype=torch.int32).cuda()
+    row_off = torch.tensor([0, 4, 7, 11], dtype=torch.int32).cuda()
+    draft = torch.tensor([5, 6, 7,   2, 1,   4, 4, 8,  0], dtype=torch.int32).cuda()
+    d_off = torch.tensor([0, 3, 5, 8], dtype=torch.int32).cuda()
+    d_len = torch.tensor([3, 2, 3, 0], dtype=torch.int32).cuda()
+    com, ncom, nacc = api.verify_accept(ctx, rows, row_off, draft, d_off, d_len, 4)
+    assert ncom.cpu().tolist() == [4, 1, 3, 1]
+    assert nacc.cpu().tolist() == [3, 0, 2, 0]
+    com = com.cpu()
+    assert com[0].tolist() == [5, 6, 7, 8] and com[1, 0].item() == 9 and com[2, :3].tolist() == [4, 4, 9] and com[3, 0].item() == 3
+
+
+def test_rope_kv_write_and_block_io(ctx):
+    """RoPE at per-sequence offsets + pool write (nn.rs:760-769, paged.rs:147-187), then the SSD payload
+    order of read_block_bytes (paged.rs:280-304) and copy_block (paged.rs:230-250)."""
+    hd, heads, kvh, bs = 64, 4, 2, 16
+    spec = api.KvSpec(2, kvh, hd, 6, bs)
+    kv = api.PagedKv(ctx, spec)
+    seqs = [api.SeqStep(5, 14, 5, [4, 1]), api.SeqStep(1, 3, 1, [2])]
+    n = 6
+    g = torch.Generator().manual_seed(5)
+    qkv = torch.empty(n, (heads + 2 * kvh) * hd).normal_(0, 1, generator=g).to(torch.bfloat16)
+    inv = (10000.0 ** (-torch.arange(0, hd, 2).float() / hd))
+    q = api.rope_kv_write(ctx, kv, 1, qkv.cuda(), inv.cuda(), heads, seqs).cpu()
+    pos = torch.tensor([14, 15, 16, 17, 18, 3]).float()
+
+    def rope(x):  # x [n, h, hd] fp32, split-halves pairing
+        th = pos[:, None, None] * inv[None, None, :]
+        c, s = th.cos(), th.sin()
+        a, b = x[..., : hd // 2], x[..., hd // 2:]
+        return torch.cat([a * c - b * s, a * s + b * c], -1)
+
+    x = qkv.float().view(n, heads + 2 * kvh, hd)
+    want_q = rope(x[:, :heads]).to(torch.bfloat16)
+    want_k = rope(x[:, heads:heads + kvh]).to(torch.bfloat16)
+    want_v = x[:, heads + kvh:].to(torch.bfloat16)
+    assert float((q.float() - want_q.float()).abs().max()) <= 2 ** -6
+    # token at position 15 of sequence 0 lives in block 4 row 15; position 16 in block 1 row 0
+    plane = kvh * bs * hd
+    blk4 = np.frombuffer(kv.read_block_bytes(4), dtype=np.int16).reshape(2, 2, kvh, bs, hd)   # [layer, K|V, head, row, d]
+    blk1 = np.frombuffer(kv.read_block_bytes(1), dtype=np.int16).reshape(2, 2, kvh, bs, hd)
+    k15 = torch.from_numpy(blk4[1, 0, :, 15].copy()).view(torch.bfloat16)
+    v16 = torch.from_numpy(blk1[1, 1, :, 0].copy()).view(torch.bfloat16)
+    assert float((k15.float() - want_k[1].float()).abs().max()) <= 2 ** -6
+    assert torch.equal(v16, want_v[2])
+    assert not blk4[0].any(), "layer 0 must stay untouched"
+    assert plane * 2 * 2 * 2 == kv.bytes_per_block()
+    kv.copy_block(4, 5)
+    assert kv.read_block_bytes(5) == kv.read_block_bytes(4)
+    kv.write_block_bytes(0, kv.read_block_bytes(1))
+    assert kv.read_block_bytes(0) == kv.read_block_bytes(1)

@@ -1,0 +1,74 @@
+"""Affine-dequant GEMM (kc_quantized_matmul) against the CPU oracle.
+
+Mirrors the reference's use of quantized_matmul (crates/kiln-models/src/nn.rs:79-102) and its
+row-stability probe (nn.rs:301-327): row r of Y(M) must carry the bits of Y(1).
+Tolerance is the north-star logits bar applied per layer: max-abs <= 2e-2, cosine >= 0.9999.
+"""
+import pytest
+import torch
+
+from kiln_b200 import api
+from kiln_b200.synth import quantize_affine
+from oracle import oracle as O
+from tests.conftest import cosine
+
+pytestmark = pytest.mark.gpu
+
+MAX_ABS, MIN_COS = 2e-2, 0.9999
+
+
+def make(n, k, bits, group, seed):
+    g = torch.Generator().manual_seed(seed)
+    w = torch.empty(n, k).normal_(0, 0.02, generator=g)
+    # outlier-heavy values like the reference's kernel probes (crates/kiln-engine/tests/paged_attn.rs:58-70)
+    w.view(-1)[::97] *= 8.0
+    return quantize_affine(w, bits, group)
+
+
+def acts(m, k, seed):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.empty(m, k).normal_(0, 1.0, generator=g)
+    x.view(-1)[::97] *= 16.0
+    return x.to(torch.bfloat16)
+
+
+CASES = [
+    # (N, K, bits, group, M)
+    (256, 256, 4, 64, 5),          # tiny: one k-split
+    (200, 512, 4, 64, 17),         # N not a multiple of the 128-row tile
+    (384, 1024, 4, 32, 33),        # two groups per k-block
+    (256, 1024, 4, 128, 6),        # a group spans two k-blocks
+    (256, 512, 8, 32, 48),         # 8-bit
+    (256, 448, 8, 64, 7),          # K = 7 k-blocks
+    (1024, 4096, 4, 64, 192),      # the 8B attention-output shape at verify width: split-K engaged
+    (2048, 2048, 4, 64, 320),      # two accumulator tiles (M > 256)
+    (512, 2048, 4, 64, 1),         # decode row
+]
+
+
+@pytest.mark.parametrize("n,k,bits,group,m", CASES)
+def test_matches_oracle(ctx, n, k, bits, group, m):
+    p, s, b = make(n, k, bits, group, 1)
+    x = acts(m, k, 2)
+    want = O.quantized_matmul(x, p, s, b, bits, group)
+    qw = api.QuantizedWeight(ctx, p.cuda(), s.cuda(), b.cuda(), bits, group)
+    got = qw.matmul(x.cuda()).cpu()
+    # 2e-2 absolute plus one bf16 spacing of the value itself (outputs here reach magnitudes of 20+)
+    excess = (got.float() - want.float()).abs() - (MAX_ABS + want.float().abs() * 2 ** -7)
+    assert float(excess.max()) <= 0, f"max-abs {float((got.float() - want.float()).abs().max())}"
+    assert cosine(got, want) >= MIN_COS
+    assert ctx.device_status() == 0
+
+
+@pytest.mark.parametrize("n,k,bits,group", [(1024, 4096, 4, 64), (256, 512, 8, 32), (4096, 1024, 4, 128)])
+def test_rows_do_not_depend_on_batch_width(ctx, n, k, bits, group):
+    """probe_row_stability (nn.rs:301-327) widened: every row of Y(M) is bit-identical to its M=1 result."""
+    p, s, b = make(n, k, bits, group, 3)
+    qw = api.QuantizedWeight(ctx, p.cuda(), s.cuda(), b.cuda(), bits, group)
+    x = acts(320, k, 4).cuda()
+    ref_rows = {r: qw.matmul(x[r:r + 1]).cpu() for r in (0, 1, 5, 31, 191, 319)}
+    for m in (2, 5, 6, 32, 192, 320):
+        y = qw.matmul(x[:m]).cpu()
+        for r, want in ref_rows.items():
+            if r < m:
+                assert torch.equal(y[r:r + 1].view(torch.int16), want.view(torch.int16)), f"row {r} differs at M={m}"
