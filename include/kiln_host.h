@@ -150,6 +150,7 @@ KH_API uint64_t kh_engine_num_running(kh_engine_t e);
 KH_API uint64_t kh_engine_num_waiting(kh_engine_t e);
 KH_API uint64_t kh_engine_iterations(kh_engine_t e);
 KH_API uint64_t kh_engine_forwards(kh_engine_t e);
+KH_API const char* kh_engine_last_error(kh_engine_t e);     /* message of the last failed step */
 /* Tokens emitted since the last call (SeqEvent::Token), plus the terminal state. finish_kind: 0 running,
  * 1 stop, 2 length, 3 error, 4 cancelled. */
 KH_API int kh_engine_take_output(kh_engine_t e, uint64_t arrival, uint32_t* out, uint64_t cap, uint64_t* n_out,

@@ -50,7 +50,9 @@ CASES = [
 def test_matches_oracle(ctx, n, k, bits, group, m):
     p, s, b = make(n, k, bits, group, 1)
     x = acts(m, k, 2)
+    O.set_weight_class(1)      # the tensor-core kernel's arithmetic class: w = bf16(q * scale + bias) first
     want = O.quantized_matmul(x, p, s, b, bits, group)
+    O.set_weight_class(0)
     qw = api.QuantizedWeight(ctx, p.cuda(), s.cuda(), b.cuda(), bits, group)
     got = qw.matmul(x.cuda()).cpu()
     # 2e-2 absolute plus one bf16 spacing of the value itself (outputs here reach magnitudes of 20+)
