@@ -88,6 +88,19 @@ KC_API void* kc_ctx_stream(kc_ctx_t ctx);
  * gave up. Reading clears it. */
 KC_API int kc_device_status(kc_ctx_t ctx, uint32_t* status);
 
+/* Kernel launches issued through this context since it was created (every kernel of this library
+ * is counted where it is launched). No counterpart in the reference. */
+KC_API int64_t kc_launch_count(kc_ctx_t ctx);
+
+/* Optional per-class device timing: while enabled, every launch is bracketed by CUDA events on the
+ * context's stream. kc_profile_read synchronises, returns milliseconds and launch counts per class
+ * since the previous read, and clears them. Classes: 0 quantised GEMM, 1 split-K reduction,
+ * 2 paged attention (partial + combine), 3 row-wise ops (embed, norms, rope + KV write, GLU,
+ * softcap, block copy), 4 sampling (greedy rows, acceptance walk). ms_out / launches_out: 5 entries.
+ * The reference's counterpart is its in-line timers (crates/kiln-engine/src/engine.rs:2377-2379). */
+KC_API int kc_profile_enable(kc_ctx_t ctx, int32_t on);
+KC_API int kc_profile_read(kc_ctx_t ctx, double* ms_out, int64_t* launches_out);
+
 /* ---- model ------------------------------------------------------------- */
 
 /* Geometry and switches; field meaning follows mlx-lm config.json as parsed by

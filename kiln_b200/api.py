@@ -211,6 +211,21 @@ class Context:
         check(L.lib().kc_device_status(self._h, C.byref(st)))
         return st.value
 
+    def launch_count(self) -> int:
+        return int(L.lib().kc_launch_count(self._h))
+
+    PROFILE_CLASSES = ("gemm", "gemm_reduce", "attention", "rowwise", "sampling")
+
+    def profile_enable(self, on: bool) -> None:
+        check(L.lib().kc_profile_enable(self._h, int(on)))
+
+    def profile_read(self) -> dict:
+        """{class: (milliseconds, launches)} since the previous read (synchronises the stream)."""
+        ms = (C.c_double * 5)()
+        n = (C.c_int64 * 5)()
+        check(L.lib().kc_profile_read(self._h, ms, n))
+        return {k: (ms[i], int(n[i])) for i, k in enumerate(self.PROFILE_CLASSES)}
+
     def close(self) -> None:
         if self._h:
             L.lib().kc_ctx_destroy(self._h)

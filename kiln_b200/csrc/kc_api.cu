@@ -55,6 +55,10 @@ static int fail(int code, const char* fmt, ...) {
                   cudaGetErrorString(e__));                                                  \
   } while (0)
 
+#define RC(call) do { int r__ = (call); if (r__) return r__; } while (0)
+
+enum { KC_PROF_GEMM = 0, KC_PROF_GEMM_REDUCE = 1, KC_PROF_ATTN = 2, KC_PROF_ROWWISE = 3, KC_PROF_SAMPLE = 4, KC_PROFILE_CLASSES = 5 };
+
 extern "C" const char* kc_last_error(void) { return g_err.c_str(); }
 extern "C" int64_t kc_live_objects(void) { return g_live.load(); }
 
@@ -69,7 +73,38 @@ struct kc_ctx {
   uint32_t* status = nullptr;  // device status word
   ncclComm_t comm = nullptr;
   int tp_rank = 0, tp_world = 1;
+  // launch accounting and optional per-class timing (kc_profile_*)
+  int64_t launches = 0;
+  int profile = 0;
+  struct Span { cudaEvent_t a, b; int cls; };
+  std::vector<Span> spans;
+  std::vector<cudaEvent_t> event_pool;
+  int64_t class_launches[KC_PROFILE_CLASSES] = {0, 0, 0, 0, 0};
+  cudaEvent_t take_event() {
+    if (!event_pool.empty()) { cudaEvent_t e = event_pool.back(); event_pool.pop_back(); return e; }
+    cudaEvent_t e = nullptr;
+    cudaEventCreate(&e);
+    return e;
+  }
 };
+
+// Runs `call` (a cudaError_t expression that launches `n` kernels of class `cls`); under kc_profile_enable the
+// launch is bracketed by events on the context's stream.
+#define LAUNCH(c, cls, n, call)                                                       \
+  do {                                                                                \
+    kc_ctx* c__ = (c);                                                                \
+    c__->launches += (n);                                                             \
+    c__->class_launches[cls] += (n);                                                  \
+    if (c__->profile) {                                                               \
+      kc_ctx::Span sp__{c__->take_event(), c__->take_event(), (cls)};                 \
+      cudaEventRecord(sp__.a, c__->stream);                                           \
+      CK(call);                                                                       \
+      cudaEventRecord(sp__.b, c__->stream);                                           \
+      c__->spans.push_back(sp__);                                                     \
+    } else {                                                                          \
+      CK(call);                                                                       \
+    }                                                                                 \
+  } while (0)
 
 struct kc_kv {
   kc_ctx* ctx = nullptr;
@@ -171,6 +206,8 @@ extern "C" void kc_ctx_destroy(kc_ctx_t c) {
   if (!c) return;
   cudaSetDevice(c->device);
   cudaStreamSynchronize(c->stream);
+  for (auto& sp : c->spans) { cudaEventDestroy(sp.a); cudaEventDestroy(sp.b); }
+  for (auto e : c->event_pool) cudaEventDestroy(e);
   if (c->comm) ncclCommDestroy(c->comm);
   cudaFree(c->status);
   cudaStreamDestroy(c->stream);
@@ -195,6 +232,28 @@ extern "C" int kc_device_status(kc_ctx_t c, uint32_t* status) {
     return fail(KC_ERR_TIMEOUT, "device status 0x%x: a bounded wait gave up (kernel 0x%x, wait %u)", *status,
                 *status & 0xff00u, *status & 0xffu);
   }
+  return KC_OK;
+}
+
+extern "C" int64_t kc_launch_count(kc_ctx_t c) { return c ? c->launches : 0; }
+
+extern "C" int kc_profile_enable(kc_ctx_t c, int32_t on) {
+  if (!c) return fail(KC_ERR_INVALID, "kc_profile_enable: NULL");
+  c->profile = on ? 1 : 0;
+  return KC_OK;
+}
+
+extern "C" int kc_profile_read(kc_ctx_t c, double* ms_out, int64_t* launches_out) {
+  if (!c || !ms_out || !launches_out) return fail(KC_ERR_INVALID, "kc_profile_read: NULL argument");
+  CK(cudaStreamSynchronize(c->stream));
+  for (int i = 0; i < KC_PROFILE_CLASSES; ++i) { ms_out[i] = 0.0; launches_out[i] = c->class_launches[i]; c->class_launches[i] = 0; }
+  for (auto& sp : c->spans) {
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, sp.a, sp.b) == cudaSuccess) ms_out[sp.cls] += ms;
+    c->event_pool.push_back(sp.a);
+    c->event_pool.push_back(sp.b);
+  }
+  c->spans.clear();
   return KC_OK;
 }
 
@@ -278,7 +337,7 @@ extern "C" int kc_kv_copy_block(kc_kv_t kv, uint32_t src, uint32_t dst) {
   if (src >= (uint32_t)kv->num_blocks || dst >= (uint32_t)kv->num_blocks)
     return fail(KC_ERR_INVALID, "kc_kv_copy_block: block %u -> %u of %d", src, dst, kv->num_blocks);
   if (src == dst) return KC_OK;
-  CK(launch_copy_block(kv->pool, kv->layers, kv->num_blocks, kv->block_elems, src, dst, kv->ctx->stream));
+  LAUNCH(kv->ctx, KC_PROF_ROWWISE, 1, launch_copy_block(kv->pool, kv->layers, kv->num_blocks, kv->block_elems, src, dst, kv->ctx->stream));
   return KC_OK;
 }
 
@@ -310,20 +369,17 @@ extern "C" int kc_kv_write_block(kc_kv_t kv, uint32_t block, const void* src, si
 // GEMM dispatch
 // ---------------------------------------------------------------------------
 
-static cudaError_t run_qlinear(kc_ctx* c, const QWeight& w, const ActOperand& x, int M, bf16* y, int ldy,
+static int run_qlinear(kc_ctx* c, const QWeight& w, const ActOperand& x, int M, bf16* y, int ldy,
                                float* partial) {
   for (int row0 = 0; row0 < M; row0 += QL_MAX_M) {
     QLinearLaunch l;
     l.w = &w; l.x = &x; l.row0 = row0; l.M = std::min(QL_MAX_M, M - row0);
     l.y = y; l.ldy = ldy; l.partial = partial; l.status = c->status;
-    cudaError_t e = qlinear_umma(l, c->stream);
-    if (e != cudaSuccess) return e;
-    if (w.splits > 1) {
-      e = qlinear_reduce_splits(partial, w.splits, l.M, w.N, y + (size_t)row0 * ldy, ldy, c->stream);
-      if (e != cudaSuccess) return e;
-    }
+    LAUNCH(c, KC_PROF_GEMM, 1, qlinear_umma(l, c->stream));
+    if (w.splits > 1)
+      LAUNCH(c, KC_PROF_GEMM_REDUCE, 1, qlinear_reduce_splits(partial, w.splits, l.M, w.N, y + (size_t)row0 * ldy, ldy, c->stream));
   }
-  return cudaSuccess;
+  return KC_OK;
 }
 
 // ---------------------------------------------------------------------------
@@ -396,7 +452,7 @@ extern "C" int kc_quantized_matmul(kc_ctx_t c, kc_qweight_t q, const void* x_dev
     if (!act_operand_init(&q->op, (const bf16*)x_dev, rows, q->w.K, &terr)) return fail(KC_ERR_CUDA, "kc_quantized_matmul: %s", terr);
     q->op_ptr = x_dev; q->op_rows = rows;
   }
-  CK(run_qlinear(c, q->w, q->op, m, (bf16*)y_dev, q->w.N, q->partial));
+  RC(run_qlinear(c, q->w, q->op, m, (bf16*)y_dev, q->w.N, q->partial));
   return KC_OK;
 }
 
@@ -405,7 +461,7 @@ extern "C" int kc_rms_norm(kc_ctx_t c, const void* x_dev, const void* weight_dev
   if (!c || !x_dev || !weight_dev || !y_dev) return fail(KC_ERR_INVALID, "kc_rms_norm: NULL argument");
   if (rows < 1 || dim < 2 || dim % 2 || dim > 12288) return fail(KC_ERR_INVALID, "kc_rms_norm: [%d, %d]", rows, dim);
   CK(cudaSetDevice(c->device));
-  CK(launch_add_rmsnorm((const bf16*)x_dev, nullptr, nullptr, (const bf16*)weight_dev, nullptr, rows, dim, eps, nullptr,
+  LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm((const bf16*)x_dev, nullptr, nullptr, (const bf16*)weight_dev, nullptr, rows, dim, eps, nullptr,
                         (bf16*)y_dev, c->stream));
   return KC_OK;
 }
@@ -912,33 +968,33 @@ int run_forward(kc_model* m, kc_kv* kv, const uint32_t* tokens_dev, const StepPl
   const int32_t* kv_slot = reinterpret_cast<const int32_t*>(m->meta_dev + p.lay.kv_slot);
   int rc;
   if ((rc = ensure_attn_ws(m, p))) return rc;
-  CK(launch_embed(m->emb_w, m->emb_s, m->emb_b, tokens_dev, n, H, d.bits, d.group_size, m->embed_scale, d.vocab_size, m->h, c->stream));
-  CK(launch_add_rmsnorm(m->h, nullptr, nullptr, m->layers[0].input_ln, nullptr, n, H, d.rms_norm_eps, nullptr, m->normed, c->stream));
+  LAUNCH(c, KC_PROF_ROWWISE, 1, launch_embed(m->emb_w, m->emb_s, m->emb_b, tokens_dev, n, H, d.bits, d.group_size, m->embed_scale, d.vocab_size, m->h, c->stream));
+  LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, nullptr, nullptr, m->layers[0].input_ln, nullptr, n, H, d.rms_norm_eps, nullptr, m->normed, c->stream));
   for (int l = 0; l < d.num_layers; ++l) {
     Layer& L = m->layers[l];
-    CK(run_qlinear(c, L.qkv, m->op_normed, n, m->qkv, m->n_qkv, m->partial));
-    CK(launch_rope_kv_write(m->qkv, L.qkv_bias, m->inv_freq, token_pos, kv_slot, n, m->Hq, m->Hkv, D, d.rope_traditional, l,
+    RC(run_qlinear(c, L.qkv, m->op_normed, n, m->qkv, m->n_qkv, m->partial));
+    LAUNCH(c, KC_PROF_ROWWISE, 1, launch_rope_kv_write(m->qkv, L.qkv_bias, m->inv_freq, token_pos, kv_slot, n, m->Hq, m->Hkv, D, d.rope_traditional, l,
                             kv->num_blocks, kv->block_size, kv->pool, m->q_rot, c->stream));
     const int window = (d.sliding_window > 0 && (l % 2 == 0)) ? d.sliding_window : 0;
     AttnParams a = attn_params(m, kv, p, l, m->q_rot, m->attn, m->attn_scale, gemma ? d.attn_logit_softcapping : 0.f, window, m->Hq);
-    CK(paged_attention(kv->map, a, D, p.tokens_per_item, p.n_work, p.max_chunks, n, c->stream));
-    CK(run_qlinear(c, L.o, m->op_attn, n, m->proj, H, m->partial));
+    LAUNCH(c, KC_PROF_ATTN, 2, paged_attention(kv->map, a, D, p.tokens_per_item, p.n_work, p.max_chunks, n, c->stream));
+    RC(run_qlinear(c, L.o, m->op_attn, n, m->proj, H, m->partial));
     if (d.tp_world > 1 && (rc = tp_allreduce(m, m->proj, n))) return rc;
-    if (gemma) CK(launch_add_rmsnorm(m->h, m->proj, L.post_attn_ln, L.pre_ffw_ln, nullptr, n, H, d.rms_norm_eps, m->h, m->normed, c->stream));
-    else CK(launch_add_rmsnorm(m->h, m->proj, nullptr, L.post_attn_ln, nullptr, n, H, d.rms_norm_eps, m->h, m->normed, c->stream));
-    CK(run_qlinear(c, L.gate_up, m->op_normed, n, m->gu, 2 * m->F, m->partial));
-    CK(launch_glu(m->gu, n, m->F, gemma ? 1 : 0, m->act, c->stream));
-    CK(run_qlinear(c, L.down, m->op_act, n, m->proj, H, m->partial));
+    if (gemma) LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, m->proj, L.post_attn_ln, L.pre_ffw_ln, nullptr, n, H, d.rms_norm_eps, m->h, m->normed, c->stream));
+    else LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, m->proj, nullptr, L.post_attn_ln, nullptr, n, H, d.rms_norm_eps, m->h, m->normed, c->stream));
+    RC(run_qlinear(c, L.gate_up, m->op_normed, n, m->gu, 2 * m->F, m->partial));
+    LAUNCH(c, KC_PROF_ROWWISE, 1, launch_glu(m->gu, n, m->F, gemma ? 1 : 0, m->act, c->stream));
+    RC(run_qlinear(c, L.down, m->op_act, n, m->proj, H, m->partial));
     if (d.tp_world > 1 && (rc = tp_allreduce(m, m->proj, n))) return rc;
     const bf16* next_ln = l + 1 < d.num_layers ? m->layers[l + 1].input_ln : nullptr;
-    CK(launch_add_rmsnorm(m->h, m->proj, gemma ? L.post_ffw_ln : nullptr, next_ln, nullptr, n, H, d.rms_norm_eps, m->h, m->normed, c->stream));
+    LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, m->proj, gemma ? L.post_ffw_ln : nullptr, next_ln, nullptr, n, H, d.rms_norm_eps, m->h, m->normed, c->stream));
   }
   if (want_logits && p.n_sampled > 0) {
     const int32_t* sampled = reinterpret_cast<const int32_t*>(m->meta_dev + p.lay.sampled);
-    CK(launch_add_rmsnorm(m->h, nullptr, nullptr, m->final_norm, sampled, p.n_sampled, H, d.rms_norm_eps, nullptr, m->hs, c->stream));
-    CK(run_qlinear(c, m->head, m->op_hs, p.n_sampled, m->logits, d.vocab_size, m->partial));
+    LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, nullptr, nullptr, m->final_norm, sampled, p.n_sampled, H, d.rms_norm_eps, nullptr, m->hs, c->stream));
+    RC(run_qlinear(c, m->head, m->op_hs, p.n_sampled, m->logits, d.vocab_size, m->partial));
     if (gemma && d.final_logit_softcapping > 0.f)
-      CK(launch_softcap(m->logits, (long long)p.n_sampled * d.vocab_size, d.final_logit_softcapping, c->stream));
+      LAUNCH(c, KC_PROF_ROWWISE, 1, launch_softcap(m->logits, (long long)p.n_sampled * d.vocab_size, d.final_logit_softcapping, c->stream));
   }
   return KC_OK;
 }
@@ -963,7 +1019,7 @@ extern "C" int kc_greedy_rows(kc_ctx_t c, const void* logits_dev, int32_t rows, 
   if (!c || !logits_dev || !tokens_out_dev) return fail(KC_ERR_INVALID, "kc_greedy_rows: NULL argument");
   if (rows < 1 || vocab < 1) return fail(KC_ERR_INVALID, "kc_greedy_rows: [%d, %d]", rows, vocab);
   CK(cudaSetDevice(c->device));
-  CK(launch_greedy_rows((const bf16*)logits_dev, rows, vocab, normalize, tokens_out_dev, c->stream));
+  LAUNCH(c, KC_PROF_SAMPLE, 1, launch_greedy_rows((const bf16*)logits_dev, rows, vocab, normalize, tokens_out_dev, c->stream));
   return KC_OK;
 }
 
@@ -976,7 +1032,7 @@ extern "C" int kc_verify_accept(kc_ctx_t c, const uint32_t* row_tokens_dev, cons
     return fail(KC_ERR_INVALID, "kc_verify_accept: NULL argument");
   if (n_seqs < 1 || max_commit < 1) return fail(KC_ERR_INVALID, "kc_verify_accept: n_seqs %d max_commit %d", n_seqs, max_commit);
   CK(cudaSetDevice(c->device));
-  CK(launch_verify_accept(row_tokens_dev, seq_row_offsets_dev, draft_dev, draft_offsets_dev, draft_len_dev, n_seqs,
+  LAUNCH(c, KC_PROF_SAMPLE, 1, launch_verify_accept(row_tokens_dev, seq_row_offsets_dev, draft_dev, draft_offsets_dev, draft_len_dev, n_seqs,
                           max_commit, committed_out_dev, n_committed_out_dev, n_accepted_out_dev, c->stream));
   return KC_OK;
 }
@@ -991,10 +1047,10 @@ extern "C" int kc_verify_step(kc_model_t m, kc_kv_t kv, const uint32_t* token_id
   if ((rc = upload_meta(m, kv, token_ids, seqs, p))) return rc;
   if ((rc = run_forward(m, kv, reinterpret_cast<const uint32_t*>(m->meta_dev + p.lay.tokens), p, true))) return rc;
   if (p.n_sampled > 0) {
-    CK(launch_greedy_rows(m->logits, p.n_sampled, m->d.vocab_size, 1, m->row_tokens, c->stream));
+    LAUNCH(c, KC_PROF_SAMPLE, 1, launch_greedy_rows(m->logits, p.n_sampled, m->d.vocab_size, 1, m->row_tokens, c->stream));
     const int max_commit = 1;  // the committed list is row_tokens[row_off .. row_off + n_committed): no second copy needed
     (void)max_commit;
-    CK(launch_verify_accept(m->row_tokens, reinterpret_cast<const int32_t*>(m->meta_dev + p.lay.v_row_off),
+    LAUNCH(c, KC_PROF_SAMPLE, 1, launch_verify_accept(m->row_tokens, reinterpret_cast<const int32_t*>(m->meta_dev + p.lay.v_row_off),
                             reinterpret_cast<const uint32_t*>(m->meta_dev + p.lay.v_draft),
                             reinterpret_cast<const int32_t*>(m->meta_dev + p.lay.v_draft_off),
                             reinterpret_cast<const int32_t*>(m->meta_dev + p.lay.v_draft_len), n_seqs, 0, m->committed,
@@ -1033,7 +1089,7 @@ extern "C" int kc_draft_chain(kc_model_t m, kc_kv_t kv, uint32_t first_token, in
     if ((rc = upload_meta(m, kv, &tok, &s, p))) return rc;
     const uint32_t* tokens_dev = j == 0 ? reinterpret_cast<const uint32_t*>(m->meta_dev + p.lay.tokens) : m->row_tokens + (j - 1);
     if ((rc = run_forward(m, kv, tokens_dev, p, true))) return rc;
-    CK(launch_greedy_rows(m->logits, 1, m->d.vocab_size, 0, m->row_tokens + j, c->stream));
+    LAUNCH(c, KC_PROF_SAMPLE, 1, launch_greedy_rows(m->logits, 1, m->d.vocab_size, 0, m->row_tokens + j, c->stream));
   }
   CK(cudaMemcpyAsync(m->result_host, m->row_tokens, (size_t)gamma * 4, cudaMemcpyDeviceToHost, c->stream));
   CK(cudaStreamSynchronize(c->stream));
