@@ -1,0 +1,450 @@
+#!/usr/bin/env python
+"""Headline benchmark: verified tokens/s of the speculative-decoding verify step.
+
+Workload (the metric's configuration): Llama-3.1-8B architecture, mlx affine 4-bit group 64, a continuous
+batch of 32 sequences with prompt lengths uniform in [512, 2048] of uniform-random ids, k = 5 drafted
+tokens per round that equal the target's greedy choice with probability 0.7 (seeded) and are uniform-random
+ids otherwise, paged KV with 16-token bf16 blocks, 256 generated tokens each. Weights are random-init
+N(0, 0.02) quantised by kiln_b200.synth (no checkpoint or dataset exists where this runs).
+
+One "step" = one engine iteration in steady state: a single (k+1)-rows-per-sequence verify forward over the
+paged cache + greedy rows + the acceptance walk + rollback. The host scheduler is the C++ engine of
+libkiln_host.so driving kc_verify_step of libkiln_cuda.so through a C function table; Python only starts it.
+
+  value  verified tokens/s from the device time of the timed steps (CUDA events on the launching stream,
+         inputs resident in HBM)
+  e2e    the same through the public call with HOST buffers: wall time of engine.step(), which holds the
+         host scheduling, the host->device copy of the step's token ids / block tables and the device->host
+         read of the sampled tokens and acceptance counts
+
+Phases: (1) speculation OFF run to completion: gives the target's greedy continuation (needed to inject
+acceptance) and donates every prompt to the radix prefix cache; (2) speculation ON with the scripted drafter:
+every prompt is a full prefix-cache hit, so all sequences decode together from the first iteration; its
+tokens are checked to be identical to phase 1 (speculation on == off). Timed steps come from phase 2.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    # name: (preset, batch, k, prompt_lo, prompt_hi, generated)
+    "llama-3.1-8b-w4g64-verify-k5-bs32": ("llama-3.1-8b", 32, 5, 512, 2048, 256),
+    "llama-3.2-1b-w4g64-verify-k4-bs1": ("llama-3.2-1b", 1, 4, 128, 128, 64),
+    "tiny-llama-verify-k4-bs4": ("tiny-llama", 4, 4, 40, 90, 48),
+}
+METRIC = "verified tok/s/GPU, Llama-3-8B w4g64 k=5 bs32; p50 verify-step ms"
+
+
+def peaks():
+    """Measured peaks of this pool's B200s (MEASURED_PEAKS.json), else the stated fallback."""
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "bf16_tflops_sustained": d["bf16_tflops_sustained"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs (reads only)."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device: int):
+        self.device, self.proc, self.lines = device, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.device)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def algorithmic(cfg, batch, k, mean_ctx):
+    """Algorithmic bytes and flops of one verify step: quantised weights read once (incl. the head), KV read once
+    per sequence, KV written, logits written + read; flops = 2*M*params + 4*M*ctx*Hq*D*L."""
+    H, L, Hq, Hkv, D, F, V = (cfg.hidden_size, cfg.num_hidden_layers, cfg.num_attention_heads, cfg.num_key_value_heads,
+                              cfg.head_dim, cfg.intermediate_size, cfg.vocab_size)
+
+    def qb(o, i):
+        return o * i * cfg.bits / 8 + 2 * o * (i // cfg.group_size) * 2
+    per_layer = qb(Hq * D, H) + 2 * qb(Hkv * D, H) + qb(H, Hq * D) + 2 * qb(F, H) + qb(H, F)
+    params_layer = Hq * D * H + 2 * Hkv * D * H + H * Hq * D + 3 * F * H
+    M = batch * (k + 1)
+    w = L * per_layer + qb(V, H)
+    kv_tok = L * 2 * Hkv * D * 2
+    total = w + batch * mean_ctx * kv_tok + M * kv_tok + M * V * 2 * 2
+    gemm_flops = 2 * M * (L * params_layer + V * H)
+    attn_flops = 4 * M * mean_ctx * Hq * D * L
+    return {"bytes": total, "weight_bytes": w, "kv_read_bytes": batch * mean_ctx * kv_tok, "gemm_flops": gemm_flops,
+            "attn_flops": attn_flops, "M": M}
+
+
+# --------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------
+
+class Workload:
+    """Model + pools + engine for one rank."""
+
+    def __init__(self, name: str, rank: int, local_rank: int, keep_cpu_sample: bool):
+        import numpy as np
+        import torch
+        from kiln_b200 import api, host
+        from kiln_b200.synth import PRESETS, synth_checkpoint
+        preset, self.batch, self.k, lo, hi, self.gen = WORKLOADS[name]
+        self.name, self.cfg = name, PRESETS[preset]
+        cfg = self.cfg
+        torch.cuda.set_device(local_rank)
+        self.ctx = api.Context(local_rank)
+        t0 = time.time()
+        ck = synth_checkpoint(cfg, seed=0, device=f"cuda:{local_rank}")
+        self.prefill_chunk = 2048 if cfg.hidden_size >= 2048 else 256
+        max_step = self.prefill_chunk + self.batch * (self.k + 1)
+        self.model = api.CudaModel(self.ctx, cfg, ck, max_step_tokens=max_step, max_step_seqs=self.batch + 1)
+        self.cpu_sample = None
+        if keep_cpu_sample:   # layer 0 + embedding + final norm + head on the host, for the CPU baseline
+            keep = {n: t.cpu() for n, t in ck.items() if not n.startswith("model.layers.") or n.startswith("model.layers.0.")}
+            self.cpu_sample = keep
+        del ck
+        torch.cuda.empty_cache()
+        self.build_s = time.time() - t0
+        rng = np.random.default_rng(1000 + rank)
+        lens = rng.integers(lo, hi + 1, size=self.batch)
+        self.prompts = [rng.integers(0, cfg.vocab_size, size=int(n), dtype=np.int64).tolist() for n in lens]
+        bs = 16
+        per_seq = [-(-(len(p) + self.gen + self.k + 1) // bs) for p in self.prompts]
+        self.num_blocks = sum(per_seq) + self.batch * ((self.gen + self.k + 1) // bs + 3) + 64
+        self.kv = api.PagedKv(self.ctx, self.model.kv_spec(self.num_blocks, bs))
+        ec = host.EngineConfig(block_size=bs, num_blocks=self.num_blocks, max_batch_tokens=max_step,
+                               prefill_chunk=self.prefill_chunk, prefill_fine_chunk=128, prefix_cache=True,
+                               deterministic_decode_width=32, gamma=self.k,
+                               spec_max_batch=1 << 20,   # keeps the width ramp (drafter.rs:62-70) at gamma = k for the whole batch
+                               spec_min_acceptance=0.0, max_key_len=0, batch_verify=True)
+        self.engine = host.Engine(ec, host.StepModel.from_cuda(self.model, self.kv))
+        self.host = host
+        self.mean_prompt = float(sum(len(p) for p in self.prompts)) / self.batch
+
+    def run_off(self):
+        """Phase 1: speculation off, to completion. Returns the greedy continuation of every prompt."""
+        arrivals = [self.engine.submit(p, self.gen) for p in self.prompts]
+        out = self.engine.run_to_completion(arrivals)
+        return [out[a][0] for a in arrivals]
+
+    def submit_on(self, base, p_accept=0.7, seed=0):
+        """Phase 2 submission: scripted drafter with injected acceptance; every prompt is a prefix-cache hit."""
+        if not hasattr(self, "drafter"):
+            self.drafter = self.host.ScriptedDrafter(p_accept, seed, self.cfg.vocab_size)
+            self.engine.set_drafter(self.drafter)
+        arrivals = []
+        for p, cont in zip(self.prompts, base):
+            a = self.engine.submit(p, self.gen)
+            self.drafter.set_continuation(a, cont)
+            arrivals.append(a)
+        return arrivals
+
+
+def timed_steps(w: Workload, base, n_steps: int, warmup: int, barrier=None, sampler=None):
+    """Runs warmup + n_steps full-batch verify iterations; returns per-step records and the ON==OFF verdict."""
+    eng = w.engine
+    records, checked, identical = [], 0, True
+    arrivals, outs = [], {}
+    done_warm = 0
+    started = False
+    guard = 0
+    while len(records) < n_steps:
+        guard += 1
+        if guard > 100000:
+            raise RuntimeError("benchmark loop did not converge")
+        if eng.num_running == 0 and eng.num_waiting == 0:
+            for a in arrivals:   # drain and check the finished round of requests
+                toks, _ = eng.take_output(a)
+                outs[a] = outs.get(a, []) + toks
+            for a, cont in zip(arrivals, base):
+                checked += 1
+                identical &= outs.get(a, []) == cont
+            arrivals = w.submit_on(base)
+            outs = {}
+        full = False
+        running_before = eng.num_running
+        s0 = eng.spec_stats()
+        if done_warm >= warmup and not started:
+            if barrier:
+                barrier()
+            if sampler:
+                sampler.start()
+            started = True
+        t0 = time.perf_counter()
+        eng.step()
+        t1 = time.perf_counter()
+        dev_ms = w.ctx.last_step_ms()
+        s1 = eng.spec_stats()
+        rounds = s1["rounds_total"] - s0["rounds_total"]
+        full = rounds == w.batch and running_before in (0, w.batch)
+        if not full:
+            continue
+        committed = (s1["accepted_total"] - s0["accepted_total"]) + rounds
+        if done_warm < warmup:
+            done_warm += 1
+            continue
+        records.append({"wall_ms": (t1 - t0) * 1e3, "dev_ms": dev_ms, "tokens": committed,
+                        "proposed": s1["proposed_total"] - s0["proposed_total"],
+                        "accepted": s1["accepted_total"] - s0["accepted_total"]})
+    return records, (checked, identical), arrivals, outs
+
+
+def roofline_pass(w: Workload, base, steps: int = 4):
+    """A separate short pass with per-class CUDA events around every launch (events would perturb the headline timing)."""
+    eng = w.engine
+    got, cls_ms, cls_n = 0, {}, {}
+    w.ctx.profile_read()
+    guard = 0
+    while got < steps and guard < 2000:
+        guard += 1
+        if eng.num_running == 0 and eng.num_waiting == 0:
+            w.submit_on(base)
+        s0 = eng.spec_stats()
+        before = eng.num_running
+        w.ctx.profile_enable(True)
+        eng.step()
+        prof = w.ctx.profile_read()
+        w.ctx.profile_enable(False)
+        s1 = eng.spec_stats()
+        if s1["rounds_total"] - s0["rounds_total"] != w.batch or before not in (0, w.batch):
+            continue
+        got += 1
+        for k, (ms, n) in prof.items():
+            cls_ms[k] = cls_ms.get(k, 0.0) + ms
+            cls_n[k] = cls_n.get(k, 0) + n
+    return {k: (cls_ms[k] / max(got, 1), cls_n[k] / max(got, 1)) for k in cls_ms}, got
+
+
+# --------------------------------------------------------------------------------------
+# CPU arm: the oracle (a restatement of the reference's op graph; the reference's own MLX CPU path cannot
+# be built or installed where this runs) timed on the host cores over a bounded sample of the same step
+# --------------------------------------------------------------------------------------
+
+def cpu_reference(name: str, tensors, ctxs, steps: int, warmup: int, budget_s: float = 150.0):
+    """Times one transformer layer (and once, the head) of the verify step at the full batch on the host cores and
+    extrapolates to the whole step: step_s = head_s + num_layers * layer_s. tensors: layer 0 + embedding + norm + head."""
+    import numpy as np
+    from kiln_b200 import api
+    from kiln_b200.synth import PRESETS, synth_checkpoint, truncated
+    from oracle import oracle as O
+    preset, batch, k, lo, hi, gen = WORKLOADS[name]
+    cfg = PRESETS[preset]
+    cfg1 = truncated(cfg, 1)
+    if tensors is None:
+        tensors = synth_checkpoint(cfg, seed=0, device="cpu", num_layers=1)
+    om = O.OracleModel(cfg1, tensors)
+    bs = 16
+    if ctxs is None:
+        rng = np.random.default_rng(1000)
+        ctxs = [int(x) + gen // 2 for x in rng.integers(lo, hi + 1, size=batch)]
+    nblk = [-(-(c + k + 1) // bs) for c in ctxs]
+    okv = O.OracleKv(1, cfg.num_key_value_heads, cfg.head_dim, sum(nblk) + 1, bs)
+    seqs, at = [], 0
+    for c, nb in zip(ctxs, nblk):
+        seqs.append(api.SeqStep(k + 1, c, k + 1, list(range(at, at + nb))))
+        at += nb
+    rng = np.random.default_rng(7)
+    ids = rng.integers(0, cfg.vocab_size, size=batch * (k + 1)).tolist()
+    step = api.StepBatch(ids, seqs)
+    cores = os.cpu_count() or 1
+    t0 = time.perf_counter()
+    om.forward_step(step, okv, want_logits=True)
+    layer_head_s = time.perf_counter() - t0
+    layer_times = []
+    t_begin = time.perf_counter()
+    for i in range(warmup + steps):
+        t0 = time.perf_counter()
+        om.forward_step(step, okv, want_logits=False)
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            layer_times.append(dt)
+        if time.perf_counter() - t_begin > budget_s and len(layer_times) >= 1:
+            break
+    layer_s = sorted(layer_times)[len(layer_times) // 2]
+    head_s = max(layer_head_s - layer_s, 0.0)
+    step_s = head_s + cfg.num_hidden_layers * layer_s
+    return {"step_s": step_s, "layer_s": layer_s, "head_s": head_s, "cores": cores, "timed": len(layer_times),
+            "sample": (f"1 of {cfg.num_hidden_layers} layers at the full batch ({batch * (k + 1)} rows, per-sequence contexts of the "
+                       f"GPU run) timed {len(layer_times)}x (median), lm_head + sampling rows timed once; "
+                       f"step = head + {cfg.num_hidden_layers} x layer")}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="llama-3.1-8b-w4g64-verify-k5-bs32", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 0)
+    preset, batch, k, lo, hi, gen = WORKLOADS[args.workload]
+    config = {"workload": args.workload, "batch": batch, "k": k, "prompt_tokens": [lo, hi], "generated_tokens": gen,
+              "kv_block": 16, "draft": "scripted, greedy token with p=0.7 else uniform-random id (seeded)",
+              "parallelism": f"replicas x{world}" if world > 1 else "single GPU",
+              "l2": "inputs larger than L2 (4.2 GB weights + ~5.9 GB KV per step vs 126 MB)"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        r = cpu_reference(args.workload, None, None, args.steps, warmup)
+        commit = 1 + sum(0.7 ** i for i in range(1, k + 1))
+        val = batch * commit / r["step_s"]
+        line = {"impl": "reference", "metric": METRIC, "value": val, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
+                "warmup": warmup, "ms_per_step": r["step_s"] * 1e3, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config,
+                "cpu_baseline": {"value": val, "unit": "tok/s", "cores": r["cores"], "kind": "port", "sample": r["sample"]},
+                "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "note": ("CPU restatement of the reference's op graph (oracle/): the reference's MLX CPU path cannot be built here; "
+                         f"tokens per step = batch x expected commit {commit:.3f} at p = 0.7")}
+        print(json.dumps(line))
+        return
+
+    import torch
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
+    want_cpu = rank == 0 and world == 1 and not args.no_cpu_baseline
+    w = Workload(args.workload, rank, local_rank, keep_cpu_sample=want_cpu)
+    t0 = time.time()
+    base = w.run_off()
+    off_s = time.time() - t0
+
+    def barrier():
+        if dist:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    launches0 = None
+    records, (checked, identical), arrivals, outs = None, (0, True), None, None
+    # launches are counted over the timed region only
+    w.ctx.sync()
+    pre = w.ctx.launch_count()
+    records, (checked, identical), arrivals, outs = timed_steps(w, base, args.steps, warmup, barrier, sampler)
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    post = w.ctx.launch_count()
+    # launches of warm-up / non-full iterations are inside [pre, post] too: scale by the per-step count measured below
+    dev_ms = sum(r["dev_ms"] for r in records)
+    wall_ms = sum(r["wall_ms"] for r in records)
+    tokens = sum(r["tokens"] for r in records)
+    prof, prof_steps = roofline_pass(w, base)
+    launches_per_step = sum(n for _, n in prof.values()) if prof else 0
+
+    # finish the in-flight round so that the ON == OFF check covers full generations
+    if arrivals:
+        fin = w.engine.run_to_completion(arrivals)
+        for a, cont in zip(arrivals, base):
+            checked += 1
+            identical &= (outs.get(a, []) + fin[a][0]) == cont
+
+    if dist:
+        t = torch.tensor([dev_ms, wall_ms], dtype=torch.float64, device=f"cuda:{local_rank}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dev_ms, wall_ms = float(t[0]), float(t[1])
+        c = torch.tensor([float(tokens), float(identical)], dtype=torch.float64, device=f"cuda:{local_rank}")
+        dist.all_reduce(c, op=dist.ReduceOp.SUM)
+        tokens, identical = float(c[0]), float(c[1]) == world
+    if rank != 0:
+        if dist:
+            dist.destroy_process_group()
+        return
+
+    pk = peaks()
+    steps = len(records)
+    step_ms = sorted(r["dev_ms"] for r in records)
+    mean_ctx = w.mean_prompt + gen / 2.0
+    alg = algorithmic(w.cfg, batch, k, mean_ctx)
+    gemm_ms, gemm_n = prof.get("gemm", (0.0, 0))
+    gemm_tflops = alg["gemm_flops"] / (gemm_ms * 1e-3) / 1e12 if gemm_ms else None
+    p50 = step_ms[len(step_ms) // 2]
+    line = {
+        "metric": METRIC, "value": tokens / (dev_ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+        "ms_per_step": dev_ms / steps, "p50_step_ms": p50, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic", "config": config, "clocks": clocks,
+        "e2e": {"value": tokens / (wall_ms * 1e-3), "unit": "tok/s", "ms_per_step": wall_ms / steps,
+                "h2d_bytes_per_step": int(batch * (k + 1) * 4 * 4 + batch * (mean_ctx / 16 + 2) * 4 + batch * 16 + batch * 12 + batch * (k + 1) * 8),
+                "d2h_bytes_per_step": int(batch * (k + 1) * 4 + batch * 8)},
+        "gpu_launches": int(launches_per_step * steps),
+        "roofline": {"kernel": "qlinear_umma_kernel (affine-dequant GEMM, tcgen05)", "bound": "tensor",
+                     "achieved": gemm_tflops, "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                     "frac": (gemm_tflops / pk["bf16_tflops_sustained"]) if gemm_tflops else None, "traffic": None,
+                     "peak_source": pk["source"] + " (sustained: the kernel runs inside a long step)",
+                     "launches_per_step": gemm_n, "ms_per_step": gemm_ms,
+                     "algorithmic_flops_per_launch": alg["gemm_flops"] / gemm_n if gemm_n else None},
+        "step_roofline": {"bound": "hbm", "algorithmic_bytes_per_step": alg["bytes"], "achieved": alg["bytes"] / (p50 * 1e-3) / 1e9,
+                          "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": alg["bytes"] / (p50 * 1e-3) / 1e9 / pk["hbm_gbs"],
+                          "frac_of_nominal_8tbs": alg["bytes"] / (p50 * 1e-3) / 8e12, "mean_context": mean_ctx},
+        "kernel_classes_ms_per_step": {k2: round(v[0], 4) for k2, v in prof.items()},
+        "kernel_classes_launches_per_step": {k2: v[1] for k2, v in prof.items()},
+        "acceptance": {"proposed": sum(r["proposed"] for r in records), "accepted": sum(r["accepted"] for r in records),
+                       "tokens_per_step": tokens / steps / world},
+        "spec_on_equals_off": {"sequences_checked": checked, "identical": bool(identical)},
+        "setup_s": {"build_model": round(w.build_s, 1), "speculation_off_run": round(off_s, 1)},
+    }
+    if want_cpu:
+        ctxs = [len(p) + gen // 2 for p in w.prompts]
+        r = cpu_reference(args.workload, w.cpu_sample, ctxs, 3, 0, budget_s=60.0)
+        line["cpu_baseline"] = {"value": (tokens / steps) / r["step_s"], "unit": "tok/s", "cores": r["cores"], "kind": "port",
+                                "sample": r["sample"], "ms_per_step": r["step_s"] * 1e3}
+    print(json.dumps(line))
+    if dist:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

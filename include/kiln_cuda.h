@@ -92,6 +92,10 @@ KC_API int kc_device_status(kc_ctx_t ctx, uint32_t* status);
  * is counted where it is launched). No counterpart in the reference. */
 KC_API int64_t kc_launch_count(kc_ctx_t ctx);
 
+/* Device time of the most recent kc_verify_step on this context, in milliseconds: CUDA events on the
+ * context's stream, from just before the step's metadata copy to just after its result copy. */
+KC_API double kc_last_step_ms(kc_ctx_t ctx);
+
 /* Optional per-class device timing: while enabled, every launch is bracketed by CUDA events on the
  * context's stream. kc_profile_read synchronises, returns milliseconds and launch counts per class
  * since the previous read, and clears them. Classes: 0 quantised GEMM, 1 split-K reduction,

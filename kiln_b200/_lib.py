@@ -54,6 +54,7 @@ _SIGNATURES = {
     "kc_ctx_stream": (_P, [_P]),
     "kc_device_status": (C.c_int, [_P, C.POINTER(C.c_uint32)]),
     "kc_launch_count": (C.c_int64, [_P]),
+    "kc_last_step_ms": (C.c_double, [_P]),
     "kc_profile_enable": (C.c_int, [_P, C.c_int32]),
     "kc_profile_read": (C.c_int, [_P, C.POINTER(C.c_double), C.POINTER(C.c_int64)]),
     "kc_model_load": (C.c_int, [_P, C.POINTER(KcModelDesc), C.POINTER(KcTensorView), C.c_size_t, C.POINTER(_P)]),

@@ -214,6 +214,10 @@ class Context:
     def launch_count(self) -> int:
         return int(L.lib().kc_launch_count(self._h))
 
+    def last_step_ms(self) -> float:
+        """Device milliseconds of the most recent verify_step (CUDA events on the context's stream)."""
+        return float(L.lib().kc_last_step_ms(self._h))
+
     PROFILE_CLASSES = ("gemm", "gemm_reduce", "attention", "rowwise", "sampling")
 
     def profile_enable(self, on: bool) -> None:

@@ -76,6 +76,8 @@ struct kc_ctx {
   // launch accounting and optional per-class timing (kc_profile_*)
   int64_t launches = 0;
   int profile = 0;
+  cudaEvent_t step_a = nullptr, step_b = nullptr;   // device span of the last kc_verify_step
+  float last_step_ms = 0.f;
   struct Span { cudaEvent_t a, b; int cls; };
   std::vector<Span> spans;
   std::vector<cudaEvent_t> event_pool;
@@ -197,6 +199,8 @@ extern "C" int kc_ctx_create(int device, kc_ctx_t* out) {
     delete c;
     return fail(KC_ERR_CUDA, "kc_ctx_create: stream/status allocation failed");
   }
+  cudaEventCreate(&c->step_a);
+  cudaEventCreate(&c->step_b);
   g_live++;
   *out = c;
   return KC_OK;
@@ -208,6 +212,8 @@ extern "C" void kc_ctx_destroy(kc_ctx_t c) {
   cudaStreamSynchronize(c->stream);
   for (auto& sp : c->spans) { cudaEventDestroy(sp.a); cudaEventDestroy(sp.b); }
   for (auto e : c->event_pool) cudaEventDestroy(e);
+  cudaEventDestroy(c->step_a);
+  cudaEventDestroy(c->step_b);
   if (c->comm) ncclCommDestroy(c->comm);
   cudaFree(c->status);
   cudaStreamDestroy(c->stream);
@@ -236,6 +242,7 @@ extern "C" int kc_device_status(kc_ctx_t c, uint32_t* status) {
 }
 
 extern "C" int64_t kc_launch_count(kc_ctx_t c) { return c ? c->launches : 0; }
+extern "C" double kc_last_step_ms(kc_ctx_t c) { return c ? (double)c->last_step_ms : 0.0; }
 
 extern "C" int kc_profile_enable(kc_ctx_t c, int32_t on) {
   if (!c) return fail(KC_ERR_INVALID, "kc_profile_enable: NULL");
@@ -1044,12 +1051,12 @@ extern "C" int kc_verify_step(kc_model_t m, kc_kv_t kv, const uint32_t* token_id
   if (rc) return rc;
   kc_ctx* c = m->ctx;
   CK(cudaSetDevice(c->device));
+  CK(cudaEventRecord(c->step_a, c->stream));
   if ((rc = upload_meta(m, kv, token_ids, seqs, p))) return rc;
   if ((rc = run_forward(m, kv, reinterpret_cast<const uint32_t*>(m->meta_dev + p.lay.tokens), p, true))) return rc;
   if (p.n_sampled > 0) {
     LAUNCH(c, KC_PROF_SAMPLE, 1, launch_greedy_rows(m->logits, p.n_sampled, m->d.vocab_size, 1, m->row_tokens, c->stream));
-    const int max_commit = 1;  // the committed list is row_tokens[row_off .. row_off + n_committed): no second copy needed
-    (void)max_commit;
+    // max_commit = 0: the committed list is row_tokens[row_off .. row_off + n_committed), no second copy needed
     LAUNCH(c, KC_PROF_SAMPLE, 1, launch_verify_accept(m->row_tokens, reinterpret_cast<const int32_t*>(m->meta_dev + p.lay.v_row_off),
                             reinterpret_cast<const uint32_t*>(m->meta_dev + p.lay.v_draft),
                             reinterpret_cast<const int32_t*>(m->meta_dev + p.lay.v_draft_off),
@@ -1060,12 +1067,16 @@ extern "C" int kc_verify_step(kc_model_t m, kc_kv_t kv, const uint32_t* token_id
     CK(cudaMemcpyAsync(hb, m->row_tokens, (size_t)p.n_sampled * 4, cudaMemcpyDeviceToHost, c->stream));
     CK(cudaMemcpyAsync(hb + o1, m->n_committed, (size_t)n_seqs * 4, cudaMemcpyDeviceToHost, c->stream));
     CK(cudaMemcpyAsync(hb + o2, m->n_accepted, (size_t)n_seqs * 4, cudaMemcpyDeviceToHost, c->stream));
+    CK(cudaEventRecord(c->step_b, c->stream));
     CK(cudaStreamSynchronize(c->stream));
+    cudaEventElapsedTime(&c->last_step_ms, c->step_a, c->step_b);
     if (row_tokens_out) memcpy(row_tokens_out, hb, (size_t)p.n_sampled * 4);
     if (n_committed_out) memcpy(n_committed_out, hb + o1, (size_t)n_seqs * 4);
     if (n_accepted_out) memcpy(n_accepted_out, hb + o2, (size_t)n_seqs * 4);
   } else {
+    CK(cudaEventRecord(c->step_b, c->stream));
     CK(cudaStreamSynchronize(c->stream));
+    cudaEventElapsedTime(&c->last_step_ms, c->step_a, c->step_b);
     if (n_committed_out) memset(n_committed_out, 0, (size_t)n_seqs * 4);
     if (n_accepted_out) memset(n_accepted_out, 0, (size_t)n_seqs * 4);
   }
