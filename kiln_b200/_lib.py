@@ -104,7 +104,10 @@ def lib() -> C.CDLL:
         if not LIB_PATH.exists():
             raise RuntimeError(f"{LIB_PATH} is missing: build it with `python -m kiln_b200.build` "
                                "(there is no CPU or PyTorch fallback for the verify path)")
-        handle = C.CDLL(str(LIB_PATH), mode=C.RTLD_GLOBAL)
+        # libkiln_cuda.so needs libnccl.so.2. torch bundles a newer NCCL under the same soname, so torch is
+        # imported first: whichever copy is loaded first serves both, and torch's own symbols need the newer one.
+        import torch  # noqa: F401
+        handle = C.CDLL(str(LIB_PATH))
         for name, (res, args) in _SIGNATURES.items():
             fn = getattr(handle, name)  # AttributeError here = header and library disagree
             fn.restype = res

@@ -376,16 +376,21 @@ extern "C" int kc_kv_write_block(kc_kv_t kv, uint32_t block, const void* src, si
 // GEMM dispatch
 // ---------------------------------------------------------------------------
 
-static int run_qlinear(kc_ctx* c, const QWeight& w, const ActOperand& x, int M, bf16* y, int ldy,
-                               float* partial) {
+// y = x . dequant(W)^T for M rows. When `fused` is given and the weight is split along K, the reduction is left
+// to the consumer kernel: *fused then describes the fp32 partials instead of y (one launch and one round trip
+// through memory less). Rows beyond one 512-row slab always go through the reduction kernel.
+static int run_qlinear(kc_ctx* c, const QWeight& w, const ActOperand& x, int M, bf16* y, int ldy, float* partial,
+                       SublayerOut* fused = nullptr) {
+  const bool defer = fused && w.splits > 1 && M <= QL_MAX_M;
   for (int row0 = 0; row0 < M; row0 += QL_MAX_M) {
     QLinearLaunch l;
     l.w = &w; l.x = &x; l.row0 = row0; l.M = std::min(QL_MAX_M, M - row0);
     l.y = y; l.ldy = ldy; l.partial = partial; l.status = c->status;
     LAUNCH(c, KC_PROF_GEMM, 1, qlinear_umma(l, c->stream));
-    if (w.splits > 1)
+    if (w.splits > 1 && !defer)
       LAUNCH(c, KC_PROF_GEMM_REDUCE, 1, qlinear_reduce_splits(partial, w.splits, l.M, w.N, y + (size_t)row0 * ldy, ldy, c->stream));
   }
+  if (fused) *fused = defer ? SublayerOut::partials(partial, w.splits, (size_t)M, w.N) : SublayerOut::dense(y, ldy);
   return KC_OK;
 }
 
@@ -468,7 +473,7 @@ extern "C" int kc_rms_norm(kc_ctx_t c, const void* x_dev, const void* weight_dev
   if (!c || !x_dev || !weight_dev || !y_dev) return fail(KC_ERR_INVALID, "kc_rms_norm: NULL argument");
   if (rows < 1 || dim < 2 || dim % 2 || dim > 12288) return fail(KC_ERR_INVALID, "kc_rms_norm: [%d, %d]", rows, dim);
   CK(cudaSetDevice(c->device));
-  LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm((const bf16*)x_dev, nullptr, nullptr, (const bf16*)weight_dev, nullptr, rows, dim, eps, nullptr,
+  LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm((const bf16*)x_dev, SublayerOut::none(), nullptr, (const bf16*)weight_dev, nullptr, rows, dim, eps, nullptr,
                         (bf16*)y_dev, c->stream));
   return KC_OK;
 }
@@ -976,29 +981,32 @@ int run_forward(kc_model* m, kc_kv* kv, const uint32_t* tokens_dev, const StepPl
   int rc;
   if ((rc = ensure_attn_ws(m, p))) return rc;
   LAUNCH(c, KC_PROF_ROWWISE, 1, launch_embed(m->emb_w, m->emb_s, m->emb_b, tokens_dev, n, H, d.bits, d.group_size, m->embed_scale, d.vocab_size, m->h, c->stream));
-  LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, nullptr, nullptr, m->layers[0].input_ln, nullptr, n, H, d.rms_norm_eps, nullptr, m->normed, c->stream));
+  LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, SublayerOut::none(), nullptr, m->layers[0].input_ln, nullptr, n, H, d.rms_norm_eps, nullptr, m->normed, c->stream));
   for (int l = 0; l < d.num_layers; ++l) {
     Layer& L = m->layers[l];
-    RC(run_qlinear(c, L.qkv, m->op_normed, n, m->qkv, m->n_qkv, m->partial));
-    LAUNCH(c, KC_PROF_ROWWISE, 1, launch_rope_kv_write(m->qkv, L.qkv_bias, m->inv_freq, token_pos, kv_slot, n, m->Hq, m->Hkv, D, d.rope_traditional, l,
+    SublayerOut so;
+    RC(run_qlinear(c, L.qkv, m->op_normed, n, m->qkv, m->n_qkv, m->partial, &so));
+    LAUNCH(c, KC_PROF_ROWWISE, 1, launch_rope_kv_write(so, L.qkv_bias, m->inv_freq, token_pos, kv_slot, n, m->Hq, m->Hkv, D, d.rope_traditional, l,
                             kv->num_blocks, kv->block_size, kv->pool, m->q_rot, c->stream));
     const int window = (d.sliding_window > 0 && (l % 2 == 0)) ? d.sliding_window : 0;
     AttnParams a = attn_params(m, kv, p, l, m->q_rot, m->attn, m->attn_scale, gemma ? d.attn_logit_softcapping : 0.f, window, m->Hq);
     LAUNCH(c, KC_PROF_ATTN, 2, paged_attention(kv->map, a, D, p.tokens_per_item, p.n_work, p.max_chunks, n, c->stream));
-    RC(run_qlinear(c, L.o, m->op_attn, n, m->proj, H, m->partial));
+    RC(run_qlinear(c, L.o, m->op_attn, n, m->proj, H, m->partial, d.tp_world > 1 ? nullptr : &so));
+    if (d.tp_world > 1) so = SublayerOut::dense(m->proj, H);
     if (d.tp_world > 1 && (rc = tp_allreduce(m, m->proj, n))) return rc;
-    if (gemma) LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, m->proj, L.post_attn_ln, L.pre_ffw_ln, nullptr, n, H, d.rms_norm_eps, m->h, m->normed, c->stream));
-    else LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, m->proj, nullptr, L.post_attn_ln, nullptr, n, H, d.rms_norm_eps, m->h, m->normed, c->stream));
+    if (gemma) LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, so, L.post_attn_ln, L.pre_ffw_ln, nullptr, n, H, d.rms_norm_eps, m->h, m->normed, c->stream));
+    else LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, so, nullptr, L.post_attn_ln, nullptr, n, H, d.rms_norm_eps, m->h, m->normed, c->stream));
     RC(run_qlinear(c, L.gate_up, m->op_normed, n, m->gu, 2 * m->F, m->partial));
     LAUNCH(c, KC_PROF_ROWWISE, 1, launch_glu(m->gu, n, m->F, gemma ? 1 : 0, m->act, c->stream));
-    RC(run_qlinear(c, L.down, m->op_act, n, m->proj, H, m->partial));
+    RC(run_qlinear(c, L.down, m->op_act, n, m->proj, H, m->partial, d.tp_world > 1 ? nullptr : &so));
+    if (d.tp_world > 1) so = SublayerOut::dense(m->proj, H);
     if (d.tp_world > 1 && (rc = tp_allreduce(m, m->proj, n))) return rc;
     const bf16* next_ln = l + 1 < d.num_layers ? m->layers[l + 1].input_ln : nullptr;
-    LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, m->proj, gemma ? L.post_ffw_ln : nullptr, next_ln, nullptr, n, H, d.rms_norm_eps, m->h, m->normed, c->stream));
+    LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, so, gemma ? L.post_ffw_ln : nullptr, next_ln, nullptr, n, H, d.rms_norm_eps, m->h, m->normed, c->stream));
   }
   if (want_logits && p.n_sampled > 0) {
     const int32_t* sampled = reinterpret_cast<const int32_t*>(m->meta_dev + p.lay.sampled);
-    LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, nullptr, nullptr, m->final_norm, sampled, p.n_sampled, H, d.rms_norm_eps, nullptr, m->hs, c->stream));
+    LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, SublayerOut::none(), nullptr, m->final_norm, sampled, p.n_sampled, H, d.rms_norm_eps, nullptr, m->hs, c->stream));
     RC(run_qlinear(c, m->head, m->op_hs, p.n_sampled, m->logits, d.vocab_size, m->partial));
     if (gemma && d.final_logit_softcapping > 0.f)
       LAUNCH(c, KC_PROF_ROWWISE, 1, launch_softcap(m->logits, (long long)p.n_sampled * d.vocab_size, d.final_logit_softcapping, c->stream));
@@ -1169,7 +1177,7 @@ extern "C" int kc_rope_kv_write(kc_ctx_t c, kc_kv_t kv, int32_t layer, const voi
   rc = validate_step(m, kv, ids.data(), n, seqs, n_seqs, 0, &p);
   if (!rc) rc = upload_meta(m, kv, ids.data(), seqs, p);
   if (!rc) {
-    cudaError_t e = launch_rope_kv_write((const bf16*)qkv_dev, (const bf16*)qkv_bias_dev, inv_freq_dev,
+    cudaError_t e = launch_rope_kv_write(SublayerOut::dense((const bf16*)qkv_dev, (num_heads + 2 * kv->kv_heads) * kv->head_dim), (const bf16*)qkv_bias_dev, inv_freq_dev,
                                          reinterpret_cast<const int32_t*>(m->meta_dev + p.lay.token_pos),
                                          reinterpret_cast<const int32_t*>(m->meta_dev + p.lay.kv_slot), n, num_heads,
                                          kv->kv_heads, kv->head_dim, traditional, layer, kv->num_blocks, kv->block_size,

@@ -131,7 +131,7 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap kvmap, const AttnParams 
       tma_prefetch_desc(&kvmap);
       const int32_t* tbl = p.block_tables + (size_t)seq * p.max_blocks;
       for (int t = 0; t < ntiles; ++t) {
-        const int st = t % ATT_STAGES; const uint32_t ph = (t / ATT_STAGES) & 1;
+        const int st = t & (ATT_STAGES - 1); const uint32_t ph = (t / ATT_STAGES) & 1;   // ATT_STAGES is a power of two
         if (!mbar_wait(&empty[st], ph ^ 1, p.status, KC_DEV_ATTN | 1)) break;
         const int key0 = key_base + t * 16;
         const int blk = tbl[key0 / p.BS];
@@ -166,7 +166,7 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap kvmap, const AttnParams 
     const uint32_t q_base = smem_u32(sQ) + (mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * S::Q_LD + (lane >> 4) * 16;
     bool ok = true;
     for (int t = ks; t < ntiles; t += KS) {
-      const int st = t % ATT_STAGES; const uint32_t ph = (t / ATT_STAGES) & 1;
+      const int st = t & (ATT_STAGES - 1); const uint32_t ph = (t / ATT_STAGES) & 1;
       ok = __all_sync(0xffffffffu, mbar_wait(&full[st], ph, p.status, KC_DEV_ATTN | 2));
       if (!ok) break;
       const uint32_t kt = smem_u32(ring + (size_t)st * S::STAGE_BYTES);

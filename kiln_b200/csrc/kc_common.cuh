@@ -55,16 +55,44 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
                "r"(bytes)
                : "memory");
 }
+// One try_wait: the thread may be suspended by the hardware until the phase completes or the hinted time
+// (nanoseconds) has passed, so a waiting warp does not burn issue slots spinning.
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(20000u)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(smem_u32(bar)), "r"(parity)
       : "memory");
   return ok != 0;
+}
+// Bounded busy-poll (no hardware suspend): lowest wake-up latency, costs issue slots.
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, uint32_t* status, uint32_t code) {
+  if (mbar_test_wait(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (!mbar_test_wait(bar, parity)) {
+    if ((++spins & 0xfff) == 0) {
+      if (globaltimer_ns() - t0 > KC_SPIN_LIMIT_NS) {
+        if (status) atomicOr(status, code);
+        return false;
+      }
+    }
+  }
+  return true;
 }
 // Bounded wait. On timeout: ORs `code` into *status (if non-null) and returns
 // false; the caller must then leave its pipeline loop.
@@ -74,7 +102,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32
   const unsigned long long t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 0x3ff) == 0) {
+    if ((++spins & 0x3f) == 0) {
       if (globaltimer_ns() - t0 > KC_SPIN_LIMIT_NS) {
         if (status) atomicOr(status, code);
         return false;
@@ -136,5 +164,14 @@ __device__ __forceinline__ float warp_max(float v) {
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
   return v;
 }
+
+// A ring position: stage index and phase bit, advanced without division.
+struct RingPos {
+  int stage = 0;
+  uint32_t phase = 0;
+  __device__ __forceinline__ void advance(int n_stages) {
+    if (++stage == n_stages) { stage = 0; phase ^= 1u; }
+  }
+};
 
 }  // namespace kc

@@ -50,6 +50,42 @@ __global__ void embed_kernel(const uint32_t* __restrict__ w, const bf16* __restr
   }
 }
 
+// A sublayer output as its consumer reads it: either bf16 [rows, N], or the fp32 split-K partials
+// [splits][rows][N] of the GEMM that produced it, summed in split order and rounded to bf16 once here
+// (the rounding the GEMM's own output would have had).
+struct RowSource {
+  const bf16* y;        // bf16 form, or null
+  const float* part;    // partial form, or null
+  int splits;
+  size_t split_stride;  // rows * N
+  int ld;               // row pitch in elements (N)
+};
+__device__ __forceinline__ void load8(const RowSource& s, size_t row, int col, float (&v)[8]) {
+  if (s.part) {
+    const float* p0 = s.part + row * s.ld + col;
+    float4 a = *reinterpret_cast<const float4*>(p0), b = *reinterpret_cast<const float4*>(p0 + 4);
+    for (int k = 1; k < s.splits; ++k) {
+      const float4 c = *reinterpret_cast<const float4*>(p0 + k * s.split_stride);
+      const float4 d = *reinterpret_cast<const float4*>(p0 + k * s.split_stride + 4);
+      a.x += c.x; a.y += c.y; a.z += c.z; a.w += c.w; b.x += d.x; b.y += d.y; b.z += d.z; b.w += d.w;
+    }
+    v[0] = bf16_round(a.x); v[1] = bf16_round(a.y); v[2] = bf16_round(a.z); v[3] = bf16_round(a.w);
+    v[4] = bf16_round(b.x); v[5] = bf16_round(b.y); v[6] = bf16_round(b.z); v[7] = bf16_round(b.w);
+  } else {
+    const uint4 u = *reinterpret_cast<const uint4*>(s.y + row * s.ld + col);
+    const float2 a = unpack_bf162(u.x), b = unpack_bf162(u.y), c = unpack_bf162(u.z), d = unpack_bf162(u.w);
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
+  }
+}
+__device__ __forceinline__ void load8_bf16(const bf16* p, float (&v)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const float2 a = unpack_bf162(u.x), b = unpack_bf162(u.y), c = unpack_bf162(u.z), d = unpack_bf162(u.w);
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
+}
+__device__ __forceinline__ void store8_bf16(bf16* p, const float (&v)[8]) {
+  *reinterpret_cast<uint4*>(p) = make_uint4(pack_bf162(v[0], v[1]), pack_bf162(v[2], v[3]), pack_bf162(v[4], v[5]), pack_bf162(v[6], v[7]));
+}
+
 // ---------------------------------------------------------------------------
 // Residual add + RMSNorm (Block::forward_step / Block::finish, nn.rs:969-1019;
 // fast::rms_norm, crates/kiln-mlx/src/fast.rs:36-41).
@@ -57,56 +93,68 @@ __global__ void embed_kernel(const uint32_t* __restrict__ w, const bf16* __restr
 //   h = y ? bf16(x + t) : x                       (plain bf16 add, nn.rs:984, 987)
 //   normed = w_out ? rms_norm(h, w_out) : (none)
 // row_map (optional) selects input rows (the sampled-row `take`, nn.rs:1376-1381).
+// One CTA per row, 8 elements per thread per pass; the row lives in shared memory between passes.
 // ---------------------------------------------------------------------------
-template <int VEC>
 __global__ void __launch_bounds__(256)
-add_rmsnorm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ y, const bf16* __restrict__ w_pre,
+add_rmsnorm_kernel(const bf16* __restrict__ x, RowSource y, const bf16* __restrict__ w_pre,
                    const bf16* __restrict__ w_out, const int32_t* __restrict__ row_map, int H, float eps,
                    bf16* __restrict__ h_out, bf16* __restrict__ normed) {
   extern __shared__ float srow[];   // H floats
   __shared__ float red[32];
   const int row = blockIdx.x;
-  const int src = row_map ? row_map[row] : row;
-  const bf16* xr = x + (size_t)src * H;
-  const bf16* yr = y ? y + (size_t)src * H : nullptr;
+  const size_t src = row_map ? row_map[row] : row;
+  const bf16* xr = x + src * H;
+  const bool has_y = y.y || y.part;
   float ss = 0.f;
-  if (yr && w_pre) {
-    for (int i = threadIdx.x * 2; i < H; i += blockDim.x * 2) {
-      const float2 v = __bfloat1622float2(*reinterpret_cast<const bf162*>(yr + i));
-      ss += v.x * v.x + v.y * v.y;
+  if (has_y && w_pre) {
+    for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+      float v[8];
+      load8(y, src, i, v);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) { srow[i + k] = v[k]; ss += v[k] * v[k]; }
     }
     ss = block_sum(ss, red);
     const float inv = rsqrtf(ss / (float)H + eps);
     ss = 0.f;
-    for (int i = threadIdx.x * 2; i < H; i += blockDim.x * 2) {
-      const float2 v = __bfloat1622float2(*reinterpret_cast<const bf162*>(yr + i));
-      const float2 wv = __bfloat1622float2(*reinterpret_cast<const bf162*>(w_pre + i));
-      const float2 xv = __bfloat1622float2(*reinterpret_cast<const bf162*>(xr + i));
-      const float t0 = bf16_round(wv.x * (v.x * inv)), t1 = bf16_round(wv.y * (v.y * inv));
-      const float h0 = bf16_round(xv.x + t0), h1 = bf16_round(xv.y + t1);
-      srow[i] = h0; srow[i + 1] = h1;
-      ss += h0 * h0 + h1 * h1;
+    for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+      float xv[8], wv[8];
+      load8_bf16(xr + i, xv);
+      load8_bf16(w_pre + i, wv);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float t = bf16_round(wv[k] * (srow[i + k] * inv));
+        const float h = bf16_round(xv[k] + t);
+        srow[i + k] = h;
+        ss += h * h;
+      }
     }
   } else {
-    for (int i = threadIdx.x * 2; i < H; i += blockDim.x * 2) {
-      const float2 xv = __bfloat1622float2(*reinterpret_cast<const bf162*>(xr + i));
-      float h0 = xv.x, h1 = xv.y;
-      if (yr) {
-        const float2 v = __bfloat1622float2(*reinterpret_cast<const bf162*>(yr + i));
-        h0 = bf16_round(h0 + v.x); h1 = bf16_round(h1 + v.y);
+    for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+      float xv[8];
+      load8_bf16(xr + i, xv);
+      if (has_y) {
+        float v[8];
+        load8(y, src, i, v);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) xv[k] = bf16_round(xv[k] + v[k]);
       }
-      srow[i] = h0; srow[i + 1] = h1;
-      ss += h0 * h0 + h1 * h1;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) { srow[i + k] = xv[k]; ss += xv[k] * xv[k]; }
     }
   }
   ss = block_sum(ss, red);
   const float inv = rsqrtf(ss / (float)H + eps);
-  for (int i = threadIdx.x * 2; i < H; i += blockDim.x * 2) {
-    const float h0 = srow[i], h1 = srow[i + 1];
-    if (h_out) *reinterpret_cast<bf162*>(h_out + (size_t)row * H + i) = __floats2bfloat162_rn(h0, h1);
+  for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
+    float h[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) h[k] = srow[i + k];
+    if (h_out) store8_bf16(h_out + (size_t)row * H + i, h);
     if (w_out) {
-      const float2 wv = __bfloat1622float2(*reinterpret_cast<const bf162*>(w_out + i));
-      *reinterpret_cast<bf162*>(normed + (size_t)row * H + i) = __floats2bfloat162_rn(wv.x * (h0 * inv), wv.y * (h1 * inv));
+      float wv[8];
+      load8_bf16(w_out + i, wv);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) h[k] = wv[k] * (h[k] * inv);
+      store8_bf16(normed + (size_t)row * H + i, h);
     }
   }
 }
@@ -116,8 +164,17 @@ add_rmsnorm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ y, const
 // fast::rope, crates/kiln-mlx/src/fast.rs:45-104). One CTA per token; K is
 // rotated, V copied, both land in the pool rows of the token's slot.
 // ---------------------------------------------------------------------------
+__device__ __forceinline__ float src_val(const RowSource& s, size_t row, int col) {
+  if (s.part) {
+    float a = s.part[row * s.ld + col];
+    for (int k = 1; k < s.splits; ++k) a += s.part[k * s.split_stride + row * s.ld + col];
+    return bf16_round(a);
+  }
+  return __bfloat162float(s.y[row * s.ld + col]);
+}
+
 __global__ void __launch_bounds__(256)
-rope_kv_write_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ bias, const float* __restrict__ inv_freq,
+rope_kv_write_kernel(RowSource qkv, const bf16* __restrict__ bias, const float* __restrict__ inv_freq,
                      const int32_t* __restrict__ token_pos, const int32_t* __restrict__ kv_slot, int Hq, int Hkv,
                      int D, int traditional, int layer, int NB, int BS, bf16* __restrict__ pool,
                      bf16* __restrict__ q_out) {
@@ -127,11 +184,10 @@ rope_kv_write_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ bias
   const float pos = (float)token_pos[tok];
   const int slot = kv_slot[tok];
   const int blk = slot / BS, r = slot % BS;
-  const bf16* src = qkv + (size_t)tok * heads * D;
   for (int i = threadIdx.x; i < heads * half; i += blockDim.x) {
-    const int h = i / half, j = i % half;
+    const int h = i / half, j = i - h * half;
     const int i0 = traditional ? 2 * j : j, i1 = traditional ? 2 * j + 1 : j + half;
-    float a = __bfloat162float(src[h * D + i0]), b = __bfloat162float(src[h * D + i1]);
+    float a = src_val(qkv, tok, h * D + i0), b = src_val(qkv, tok, h * D + i1);
     if (bias) {
       a = bf16_round(a + __bfloat162float(bias[h * D + i0]));
       b = bf16_round(b + __bfloat162float(bias[h * D + i1]));
@@ -173,18 +229,17 @@ __device__ __forceinline__ float act_gelu_mul(float g, float u) {
   return bf16_round(act * u);
 }
 
-__global__ void glu_kernel(const bf16* __restrict__ gu, int n, int F, int gelu, bf16* __restrict__ out) {
-  const long long total = (long long)n * F / 2;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
-       i += (long long)gridDim.x * blockDim.x) {
-    const long long e = i * 2;
-    const int row = (int)(e / F), col = (int)(e % F);
-    const float2 g = __bfloat1622float2(*reinterpret_cast<const bf162*>(gu + (size_t)row * 2 * F + col));
-    const float2 u = __bfloat1622float2(*reinterpret_cast<const bf162*>(gu + (size_t)row * 2 * F + F + col));
-    float2 r;
-    if (gelu) { r.x = act_gelu_mul(g.x, u.x); r.y = act_gelu_mul(g.y, u.y); }
-    else { r.x = act_silu_mul(g.x, u.x); r.y = act_silu_mul(g.y, u.y); }
-    *reinterpret_cast<bf162*>(out + (size_t)row * F + col) = __floats2bfloat162_rn(r.x, r.y);
+__global__ void __launch_bounds__(256) glu_kernel(const bf16* __restrict__ gu, int n, int F, int gelu, bf16* __restrict__ out) {
+  const int per_row = F / 8;
+  const int total = n * per_row;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const int row = i / per_row, col = (i - row * per_row) * 8;
+    float g[8], u[8];
+    load8_bf16(gu + (size_t)row * 2 * F + col, g);
+    load8_bf16(gu + (size_t)row * 2 * F + F + col, u);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) g[k] = gelu ? act_gelu_mul(g[k], u[k]) : act_silu_mul(g[k], u[k]);
+    store8_bf16(out + (size_t)row * F + col, g);
   }
 }
 
@@ -219,24 +274,32 @@ cudaError_t launch_embed(const uint32_t* w, const bf16* scales, const bf16* bias
   return cudaGetLastError();
 }
 
-cudaError_t launch_add_rmsnorm(const bf16* x, const bf16* y, const bf16* w_pre, const bf16* w_out,
+static RowSource row_source(const SublayerOut& y) {
+  RowSource r;
+  r.y = y.y; r.part = y.part; r.splits = y.splits; r.split_stride = y.split_stride; r.ld = y.ld;
+  return r;
+}
+
+cudaError_t launch_add_rmsnorm(const bf16* x, const SublayerOut& y, const bf16* w_pre, const bf16* w_out,
                                const int32_t* row_map, int rows, int H, float eps, bf16* h_out, bf16* normed,
                                cudaStream_t s) {
   if (rows <= 0) return cudaSuccess;
-  add_rmsnorm_kernel<2><<<rows, 256, H * sizeof(float), s>>>(x, y, w_pre, w_out, row_map, H, eps, h_out, normed);
+  if (H % 8) return cudaErrorInvalidValue;
+  add_rmsnorm_kernel<<<rows, 256, H * sizeof(float), s>>>(x, row_source(y), w_pre, w_out, row_map, H, eps, h_out, normed);
   return cudaGetLastError();
 }
 
-cudaError_t launch_rope_kv_write(const bf16* qkv, const bf16* bias, const float* inv_freq, const int32_t* token_pos,
+cudaError_t launch_rope_kv_write(const SublayerOut& qkv, const bf16* bias, const float* inv_freq, const int32_t* token_pos,
                                  const int32_t* kv_slot, int n, int Hq, int Hkv, int D, int traditional, int layer,
                                  int NB, int BS, bf16* pool, bf16* q_out, cudaStream_t s) {
-  rope_kv_write_kernel<<<n, 256, 0, s>>>(qkv, bias, inv_freq, token_pos, kv_slot, Hq, Hkv, D, traditional, layer, NB,
+  rope_kv_write_kernel<<<n, 256, 0, s>>>(row_source(qkv), bias, inv_freq, token_pos, kv_slot, Hq, Hkv, D, traditional, layer, NB,
                                          BS, pool, q_out);
   return cudaGetLastError();
 }
 
 cudaError_t launch_glu(const bf16* gu, int n, int F, int gelu, bf16* out, cudaStream_t s) {
-  const long long total = (long long)n * F / 2;
+  if (F % 8) return cudaErrorInvalidValue;
+  const long long total = (long long)n * (F / 8);
   const int blocks = (int)std::min<long long>((total + 255) / 256, 148LL * 8);
   glu_kernel<<<blocks, 256, 0, s>>>(gu, n, F, gelu, out);
   return cudaGetLastError();

@@ -8,13 +8,28 @@ namespace kc {
 cudaError_t launch_embed(const uint32_t* w, const bf16* scales, const bf16* biases, const uint32_t* ids, int n, int H,
                          int bits, int group, float embed_scale, int vocab, bf16* out, cudaStream_t s);
 
+// A GEMM output as its consumer reads it: bf16 [rows, ld], or the GEMM's fp32 split-K partials
+// [splits][rows][ld] (summed in split order and rounded to bf16 by the consumer), or nothing.
+struct SublayerOut {
+  const bf16* y = nullptr;
+  const float* part = nullptr;
+  int splits = 0;
+  size_t split_stride = 0;
+  int ld = 0;
+  static SublayerOut none() { return SublayerOut{}; }
+  static SublayerOut dense(const bf16* y, int ld) { SublayerOut s; s.y = y; s.ld = ld; return s; }
+  static SublayerOut partials(const float* part, int splits, size_t rows, int ld) {
+    SublayerOut s; s.part = part; s.splits = splits; s.split_stride = rows * (size_t)ld; s.ld = ld; return s;
+  }
+};
+
 // h = y ? bf16(x + (w_pre ? rms_norm(y, w_pre) : y)) : x ; normed = w_out ? rms_norm(h, w_out) : unused.
 // row_map (optional) picks the input rows. h_out / normed may be null when not wanted.
-cudaError_t launch_add_rmsnorm(const bf16* x, const bf16* y, const bf16* w_pre, const bf16* w_out,
+cudaError_t launch_add_rmsnorm(const bf16* x, const SublayerOut& y, const bf16* w_pre, const bf16* w_out,
                                const int32_t* row_map, int rows, int H, float eps, bf16* h_out, bf16* normed,
                                cudaStream_t s);
 
-cudaError_t launch_rope_kv_write(const bf16* qkv, const bf16* bias, const float* inv_freq, const int32_t* token_pos,
+cudaError_t launch_rope_kv_write(const SublayerOut& qkv, const bf16* bias, const float* inv_freq, const int32_t* token_pos,
                                  const int32_t* kv_slot, int n, int Hq, int Hkv, int D, int traditional, int layer,
                                  int NB, int BS, bf16* pool, bf16* q_out, cudaStream_t s);
 

@@ -16,6 +16,7 @@
 #include <algorithm>
 #include <cstdio>
 #include <cstring>
+#include <cstdlib>
 
 namespace kc {
 
@@ -91,6 +92,7 @@ cudaError_t qweight_build(QWeight* out, const uint32_t* w, const bf16* scales, c
   q.packed_bytes = QL_TILE_N * (QL_KB * bits / 8);
   q.record_bytes = q.packed_bytes + QL_TILE_N * q.gpk * 4;
   q.splits = qlinear_plan_splits(q.n_tiles, q.kblocks, sm_count);
+  q.sm_count = sm_count;
   cudaError_t e = cudaMalloc(&q.records, q.bytes());
   if (e != cudaSuccess) return e;
   const long long total = (long long)q.n_tiles * q.kblocks * (q.record_bytes / 4);
@@ -217,7 +219,7 @@ __device__ __forceinline__ uint32_t umma_idesc_bf16(int m, int n) {
   return d;
 }
 
-__device__ __forceinline__ void umma_f16_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+__device__ __forceinline__ void umma_bf16_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
                                              uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
@@ -255,35 +257,46 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 constexpr int QL_THREADS = 384;        // 12 warps
 constexpr int QL_DQ_WARP0 = 4;         // first dequant/epilogue warp
 constexpr int QL_DQ_WARPS = 8;
-constexpr int QL_A_BYTES = QL_TILE_N * 128;  // one A stage
+constexpr int QL_A_BYTES = QL_TILE_N * 128;  // one 128-row A tile of one stage
 
 struct QlKernelParams {
   const uint8_t* records;
-  uint32_t record_bytes, packed_bytes;
-  int N, n_tiles, kblocks, bits, gpk;
+  uint32_t record_bytes;
+  int N, n_tiles, kblocks;
   int M, m_pad;          // live rows, rows rounded up to 16
   int row0;              // first activation row
   int splits, kb_per_split;
   int a_stages, r_stages;
   uint32_t raw_stride;   // record_bytes rounded up to 128
-  uint32_t tmem_cols;    // power of two >= max(32, m_pad)
+  uint32_t tmem_cols;    // power of two >= max(32, NT * m_pad)
   bf16* y; int ldy;
   float* partial;
   uint32_t* status;
+  int dbg;   // experiment switches (KC_QL_DEBUG), 0 in normal operation
 };
 
+// BITS: 4 or 8. GPK: scale/bias pairs per row per k-block (1 or 2). NT: 128-row weight tiles per CTA, all
+// multiplied against the same activation k-block (NT * m_pad TMEM columns), which divides the activation
+// traffic from L2 by NT. NT is free to depend on the row count: it changes which CTA computes an output
+// element, never the order in which that element's k-blocks are accumulated.
+#define QWAIT(bar, par, code) ((p.dbg & 16) ? mbar_wait_spin(bar, par, p.status, code) : mbar_wait(bar, par, p.status, code))
+
+template <int BITS, int GPK, int NT>
 __global__ void __launch_bounds__(QL_THREADS, 1)
 qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_constant__ CUtensorMap map64,
                     const QlKernelParams p) {
+  constexpr uint32_t PACKED = QL_TILE_N * (QL_KB * BITS / 8);
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment for the swizzled tiles.
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int AS = p.a_stages, RS = p.r_stages;
   const uint32_t b_bytes = (uint32_t)p.m_pad * 128u;
+  const uint32_t a_stage = NT * QL_A_BYTES;
+  const uint32_t r_stage = NT * p.raw_stride;
   uint8_t* sA = smem;
-  uint8_t* sB = sA + (size_t)AS * QL_A_BYTES;
+  uint8_t* sB = sA + (size_t)AS * a_stage;
   uint8_t* sR = sB + (size_t)AS * b_bytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sR + (size_t)RS * p.raw_stride);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sR + (size_t)RS * r_stage);
   uint64_t* raw_full = bars;
   uint64_t* raw_empty = raw_full + RS;
   uint64_t* b_full = raw_empty + RS;
@@ -293,7 +306,8 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile = blockIdx.x, split = blockIdx.y;
+  const int tile0 = blockIdx.x * NT, split = blockIdx.y;
+  const int nt_live = min(NT, p.n_tiles - tile0);   // tiles this CTA really owns
   const int kb0 = split * p.kb_per_split;
   const int nkb = p.kb_per_split;
 
@@ -316,24 +330,27 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    // ---- weight record producer ----
+    // ---- weight record producer: one bulk copy per owned tile per k-block ----
     if (lane == 0) {
-      const uint8_t* src = p.records + ((size_t)tile * p.kblocks + kb0) * p.record_bytes;
-      for (int i = 0; i < nkb; ++i) {
-        const int rs = i % RS; const uint32_t ph = (i / RS) & 1;
-        if (!mbar_wait(&raw_empty[rs], ph ^ 1, p.status, KC_DEV_QLINEAR | 1)) break;
-        mbar_arrive_expect_tx(&raw_full[rs], p.record_bytes);
-        bulk_g2s(sR + (size_t)rs * p.raw_stride, src + (size_t)i * p.record_bytes, p.record_bytes,
-                 &raw_full[rs]);
+      RingPos rp;
+      for (int i = 0; i < nkb; ++i, rp.advance(RS)) {
+        const int rs = rp.stage; const uint32_t ph = rp.phase;
+        if (!QWAIT(&raw_empty[rs], ph ^ 1, KC_DEV_QLINEAR | 1)) break;
+        mbar_arrive_expect_tx(&raw_full[rs], p.record_bytes * nt_live);
+        for (int t = 0; t < nt_live; ++t)
+          bulk_g2s(sR + (size_t)rs * r_stage + (size_t)t * p.raw_stride,
+                   p.records + ((size_t)(tile0 + t) * p.kblocks + kb0 + i) * p.record_bytes, p.record_bytes, &raw_full[rs]);
       }
     }
   } else if (warp == 1) {
     // ---- activation producer ----
     if (lane == 0) {
       const int n64 = p.m_pad / 64, n16 = (p.m_pad % 64) / 16;
-      for (int i = 0; i < nkb; ++i) {
-        const int as = i % AS; const uint32_t ph = (i / AS) & 1;
-        if (!mbar_wait(&ab_empty[as], ph ^ 1, p.status, KC_DEV_QLINEAR | 2)) break;
+      RingPos ap;
+      for (int i = 0; i < nkb; ++i, ap.advance(AS)) {
+        const int as = ap.stage; const uint32_t ph = ap.phase;
+        if (!QWAIT(&ab_empty[as], ph ^ 1, KC_DEV_QLINEAR | 2)) break;
+        if (p.dbg & 2) { mbar_arrive(&b_full[as]); continue; }
         mbar_arrive_expect_tx(&b_full[as], b_bytes);
         uint8_t* dst = sB + (size_t)as * b_bytes;
         const int x = (kb0 + i) * QL_KB;
@@ -346,78 +363,98 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
     // ---- MMA issuer ----
     if (lane == 0) {
       const int n0 = p.m_pad > 256 ? 256 : p.m_pad;
-      const int n1 = p.m_pad - n0;
+      const int n1 = p.m_pad - n0;   // a second accumulator only when NT == 1 and m_pad > 256
       const uint32_t idesc0 = umma_idesc_bf16(QL_TILE_N, n0);
       const uint32_t idesc1 = n1 ? umma_idesc_bf16(QL_TILE_N, n1) : 0;
+      const uint32_t col_stride = (uint32_t)(p.m_pad + 31) & ~31u;   // accumulators start on 32-column boundaries
       bool ok = true;
-      for (int i = 0; i < nkb && ok; ++i) {
-        const int as = i % AS; const uint32_t ph = (i / AS) & 1;
-        ok = mbar_wait(&a_ready[as], ph, p.status, KC_DEV_QLINEAR | 3) &&
-             mbar_wait(&b_full[as], ph, p.status, KC_DEV_QLINEAR | 4);
+      RingPos ap;
+      for (int i = 0; i < nkb && ok; ++i, ap.advance(AS)) {
+        const int as = ap.stage; const uint32_t ph = ap.phase;
+        ok = QWAIT(&a_ready[as], ph, KC_DEV_QLINEAR | 3) &&
+             QWAIT(&b_full[as], ph, KC_DEV_QLINEAR | 4);
         if (!ok) break;
         tc_fence_after();
-        const uint64_t da = umma_smem_desc_sw128(smem_u32(sA + (size_t)as * QL_A_BYTES));
         const uint64_t db = umma_smem_desc_sw128(smem_u32(sB + (size_t)as * b_bytes));
 #pragma unroll
-        for (int ks = 0; ks < QL_KB / 16; ++ks) {
-          const uint32_t acc = (i > 0 || ks > 0) ? 1u : 0u;
-          // advancing K by 16 bf16 = 32 bytes inside the swizzle row: +2 in the address field
-          umma_f16_ss(tmem_base, da + 2 * ks, db + 2 * ks, idesc0, acc);
-          if (n1) umma_f16_ss(tmem_base + 256, da + 2 * ks, db + (256 * 128 >> 4) + 2 * ks, idesc1, acc);
+        for (int t = 0; t < NT; ++t) {
+          if (t < nt_live && !(p.dbg & 4)) {
+            const uint64_t da = umma_smem_desc_sw128(smem_u32(sA + (size_t)as * a_stage + (size_t)t * QL_A_BYTES));
+#pragma unroll
+            for (int ks = 0; ks < QL_KB / 16; ++ks) {
+              const uint32_t acc = (i > 0 || ks > 0) ? 1u : 0u;
+              // advancing K by 16 bf16 = 32 bytes inside the swizzle row: +2 in the address field
+              umma_bf16_ss(tmem_base + t * col_stride, da + 2 * ks, db + 2 * ks, idesc0, acc);
+              if (NT == 1 && n1) umma_bf16_ss(tmem_base + 256, da + 2 * ks, db + (256 * 128 >> 4) + 2 * ks, idesc1, acc);
+            }
+          }
         }
-        umma_commit(&ab_empty[as]);
+        if (p.dbg & 32) mbar_arrive(&ab_empty[as]); else umma_commit(&ab_empty[as]);
       }
       umma_commit(acc_full);
     }
   } else if (warp >= QL_DQ_WARP0) {
-    // ---- dequantisers ----
+    // ---- dequantisers: thread = (row pair r0 / r0 + 64, chunk pair 2c', 2c' + 1) of every owned tile ----
     const int td = threadIdx.x - QL_DQ_WARP0 * 32;  // 0..255
-    const int c = td & 7, r0 = td >> 3;
-    const int gi = (p.gpk == 2) ? (c >> 2) : 0;
+    const int cp = td & 3, r0 = td >> 2;            // chunk pair 0..3, row 0..63
+    const int gi = (GPK == 2) ? (cp >> 1) : 0;
+    // shared-memory offsets that do not change with the k-block
+    uint32_t a_off[2][2], raw_off[2], sb_off[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = r0 + 64 * h;
+      raw_off[h] = r * (QL_KB * BITS / 8) + cp * (2 * BITS);          // 8 (w4) or 16 (w8) bytes per chunk pair
+      sb_off[h] = PACKED + (r * GPK + gi) * 4;
+      a_off[h][0] = r * 128 + (((2 * cp) ^ (r & 7)) << 4);
+      a_off[h][1] = r * 128 + (((2 * cp + 1) ^ (r & 7)) << 4);
+    }
     bool ok = true;
-    for (int i = 0; i < nkb && ok; ++i) {
-      const int rs = i % RS; const uint32_t rph = (i / RS) & 1;
-      const int as = i % AS; const uint32_t aph = (i / AS) & 1;
-      ok = __all_sync(0xffffffffu, mbar_wait(&raw_full[rs], rph, p.status, KC_DEV_QLINEAR | 5));
+    RingPos rp, ap;
+    for (int i = 0; i < nkb && ok; ++i, rp.advance(RS), ap.advance(AS)) {
+      const int rs = rp.stage; const uint32_t rph = rp.phase;
+      const int as = ap.stage; const uint32_t aph = ap.phase;
+      ok = __all_sync(0xffffffffu, QWAIT(&raw_full[rs], rph, KC_DEV_QLINEAR | 5));
       if (!ok) break;
-      const uint8_t* rec = sR + (size_t)rs * p.raw_stride;
-      const bf162* sb = reinterpret_cast<const bf162*>(rec + p.packed_bytes);
-      uint32_t u[4][2]; bf162 sbv[4];
-      if (p.bits == 4) {
-        const uint32_t* pk = reinterpret_cast<const uint32_t*>(rec);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) { const int r = r0 + 32 * k; u[k][0] = pk[r * 8 + c]; u[k][1] = 0; sbv[k] = sb[r * p.gpk + gi]; }
-      } else {
-        const uint2* pk = reinterpret_cast<const uint2*>(rec);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) { const int r = r0 + 32 * k; uint2 v = pk[r * 8 + c]; u[k][0] = v.x; u[k][1] = v.y; sbv[k] = sb[r * p.gpk + gi]; }
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&raw_empty[rs]);
-      ok = __all_sync(0xffffffffu, mbar_wait(&ab_empty[as], aph ^ 1, p.status, KC_DEV_QLINEAR | 6));
+      ok = __all_sync(0xffffffffu, QWAIT(&ab_empty[as], aph ^ 1, KC_DEV_QLINEAR | 6));
       if (!ok) break;
-      uint8_t* a = sA + (size_t)as * QL_A_BYTES;
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const int r = r0 + 32 * k;
-        const uint4 v = (p.bits == 4) ? dequant8_w4(u[k][0], sbv[k]) : dequant8_w8(u[k][0], u[k][1], sbv[k]);
-        *reinterpret_cast<uint4*>(a + r * 128 + ((c ^ (r & 7)) << 4)) = v;
+      for (int t = 0; t < NT; ++t) {
+        if (t < nt_live && !(p.dbg & 1)) {
+          const uint8_t* rec = sR + (size_t)rs * r_stage + (size_t)t * p.raw_stride;
+          uint8_t* a = sA + (size_t)as * a_stage + (size_t)t * QL_A_BYTES;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const bf162 sb = *reinterpret_cast<const bf162*>(rec + sb_off[h]);
+            uint4 v0, v1;
+            if (BITS == 4) {
+              const uint2 u = *reinterpret_cast<const uint2*>(rec + raw_off[h]);
+              v0 = dequant8_w4(u.x, sb); v1 = dequant8_w4(u.y, sb);
+            } else {
+              const uint4 u = *reinterpret_cast<const uint4*>(rec + raw_off[h]);
+              v0 = dequant8_w8(u.x, u.y, sb); v1 = dequant8_w8(u.z, u.w, sb);
+            }
+            *reinterpret_cast<uint4*>(a + a_off[h][0]) = v0;
+            *reinterpret_cast<uint4*>(a + a_off[h][1]) = v1;
+          }
+        }
       }
-      fence_proxy_async_smem();
+      if (!(p.dbg & 8)) fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&a_ready[as]);
+      if (lane == 0) { mbar_arrive(&raw_empty[rs]); mbar_arrive(&a_ready[as]); }
     }
     // ---- epilogue: TMEM -> global ----
-    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(acc_full, 0, p.status, KC_DEV_QLINEAR | 7));
+    if (ok) ok = __all_sync(0xffffffffu, QWAIT(acc_full, 0, KC_DEV_QLINEAR | 7));
     if (ok) {
       tc_fence_after();
       const int q = warp & 3;                       // TMEM lane quarter this warp may read
-      const int half = (warp - QL_DQ_WARP0) >> 2;   // two warps share a quarter: split the columns
-      const int n = tile * QL_TILE_N + q * 32 + lane;
+      const int half = (warp - QL_DQ_WARP0) >> 2;   // two warps share a quarter: split the column chunks
       const int chunks = p.m_pad / 16;
-      for (int ch = half; ch < chunks; ch += 2) {
+      for (int item = half; item < nt_live * chunks; item += 2) {
+        const int t = item / chunks, ch = item % chunks;
+        const int n = (tile0 + t) * QL_TILE_N + q * 32 + lane;
+        const int col = (NT == 1) ? ch * 16 : t * ((p.m_pad + 31) & ~31) + ch * 16;   // NT == 1: columns are m directly (incl. the 256+ tile)
         uint32_t v[16];
-        tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + ch * 16, v);
+        tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + col, v);
         if (n < p.N) {
           if (p.splits == 1) {
 #pragma unroll
@@ -447,40 +484,73 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
   }
 }
 
+template <int BITS, int GPK, int NT>
+static cudaError_t launch_umma(const QLinearLaunch& l, QlKernelParams& p, cudaStream_t s) {
+  const QWeight& w = *l.w;
+  uint32_t cols = 32;
+  while ((int)cols < (NT == 1 ? p.m_pad : NT * ((p.m_pad + 31) & ~31))) cols <<= 1;
+  p.tmem_cols = cols;
+  // Shared memory plan: the A+B ring first (2..4 stages), what is left goes to the raw-record ring.
+  static const int env_kb = getenv("KC_QL_SMEM_KB") ? atoi(getenv("KC_QL_SMEM_KB")) : 212;
+  const size_t budget = (size_t)env_kb * 1024;
+  const size_t ab = (size_t)NT * QL_A_BYTES + (size_t)p.m_pad * 128;
+  const size_t rstage = (size_t)NT * p.raw_stride;
+  static const int env_as = getenv("KC_QL_AS") ? atoi(getenv("KC_QL_AS")) : 4;
+  int as = (int)std::min<size_t>(env_as, (budget - 3 * rstage) / ab);
+  if (as < 2) as = 2;
+  as = std::min(as, std::max(2, p.kb_per_split));
+  const size_t left = budget > (size_t)as * ab ? budget - (size_t)as * ab : 0;
+  int rs = (int)std::min<size_t>(24, left / rstage);
+  if (rs < 2) rs = 2;
+  p.a_stages = as; p.r_stages = rs;
+  const size_t smem = 1024 + (size_t)as * ab + (size_t)rs * rstage + (2 * rs + 3 * as + 1) * 8 + 16;
+  if (smem > 227 * 1024) return cudaErrorInvalidValue;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(qlinear_umma_kernel<BITS, GPK, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  dim3 grid((w.n_tiles + NT - 1) / NT, w.splits);
+  qlinear_umma_kernel<BITS, GPK, NT><<<grid, QL_THREADS, smem, s>>>(l.x->map16, l.x->map64, p);
+  return cudaGetLastError();
+}
+
+template <int BITS, int GPK>
+static cudaError_t launch_umma_nt(const QLinearLaunch& l, QlKernelParams& p, int nt, cudaStream_t s) {
+  switch (nt) {
+    case 4: return launch_umma<BITS, GPK, 4>(l, p, s);
+    case 2: return launch_umma<BITS, GPK, 2>(l, p, s);
+    default: return launch_umma<BITS, GPK, 1>(l, p, s);
+  }
+}
+
+// Weight tiles per CTA: as many as TMEM holds for this row count, but never so many that the grid drops
+// under about one CTA per SM.
+static int plan_tiles_per_cta(const QWeight& w, int m_pad, int sm_count) {
+  int nt = m_pad <= 128 ? 4 : (m_pad <= 256 ? 2 : 1);
+  while (nt > 1 && ((w.n_tiles + nt - 1) / nt) * w.splits < sm_count) nt >>= 1;
+  return nt;
+}
+
 cudaError_t qlinear_umma(const QLinearLaunch& l, cudaStream_t s) {
   const QWeight& w = *l.w;
   if (l.M < 1 || l.M > QL_MAX_M) return cudaErrorInvalidValue;
   QlKernelParams p;
-  p.records = w.records; p.record_bytes = w.record_bytes; p.packed_bytes = w.packed_bytes;
-  p.N = w.N; p.n_tiles = w.n_tiles; p.kblocks = w.kblocks; p.bits = w.bits; p.gpk = w.gpk;
+  p.records = w.records; p.record_bytes = w.record_bytes;
+  p.N = w.N; p.n_tiles = w.n_tiles; p.kblocks = w.kblocks;
   p.M = l.M; p.m_pad = (l.M + 15) & ~15; p.row0 = l.row0;
   if (l.row0 % 16 || l.row0 + p.m_pad > l.x->rows) return cudaErrorInvalidValue;
   p.splits = w.splits; p.kb_per_split = w.kblocks / w.splits;
   p.raw_stride = (w.record_bytes + 127) & ~127u;
-  uint32_t cols = 32; while ((int)cols < p.m_pad) cols <<= 1;
-  p.tmem_cols = cols;
   p.y = l.y; p.ldy = l.ldy; p.partial = l.partial; p.status = l.status;
-  // Shared memory plan: A+B ring (2..4 stages), the rest for the raw ring (<= 16).
-  const size_t budget = 200 * 1024;
-  const size_t ab = QL_A_BYTES + (size_t)p.m_pad * 128;
-  int as = (int)std::min<size_t>(4, (budget - 4 * p.raw_stride) / ab);
-  if (as < 2) as = 2;
-  as = std::min(as, std::max(2, p.kb_per_split));
-  size_t left = budget - (size_t)as * ab;
-  int rs = (int)std::min<size_t>(16, left / p.raw_stride);
-  if (rs < 2) rs = 2;
-  p.a_stages = as; p.r_stages = rs;
-  const size_t smem = 1024 + (size_t)as * ab + (size_t)rs * p.raw_stride + (2 * rs + 3 * as + 1) * 8 + 16;
-  static size_t configured = 0;
-  if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(qlinear_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)std::max<size_t>(smem, 227 * 1024 - 1024));
-    if (e != cudaSuccess) return e;
-    configured = std::max<size_t>(smem, 227 * 1024 - 1024);
-  }
-  dim3 grid(w.n_tiles, w.splits);
-  qlinear_umma_kernel<<<grid, QL_THREADS, smem, s>>>(l.x->map16, l.x->map64, p);
-  return cudaGetLastError();
+  static const int env_dbg = getenv("KC_QL_DEBUG") ? atoi(getenv("KC_QL_DEBUG")) : 0;
+  static const int env_nt = getenv("KC_QL_NT") ? atoi(getenv("KC_QL_NT")) : 0;
+  p.dbg = env_dbg;
+  int nt = plan_tiles_per_cta(w, p.m_pad, w.sm_count);
+  if (env_nt) nt = std::min(env_nt, p.m_pad <= 128 ? 4 : (p.m_pad <= 256 ? 2 : 1));
+  if (w.bits == 4) return w.gpk == 2 ? launch_umma_nt<4, 2>(l, p, nt, s) : launch_umma_nt<4, 1>(l, p, nt, s);
+  return w.gpk == 2 ? launch_umma_nt<8, 2>(l, p, nt, s) : launch_umma_nt<8, 1>(l, p, nt, s);
 }
 
 // ---------------------------------------------------------------------------

@@ -37,6 +37,7 @@ struct QWeight {
   uint32_t packed_bytes = 0;   // per record
   uint32_t record_bytes = 0;
   int splits = 1;              // fixed function of (N, K): never of M
+  int sm_count = 148;
   size_t bytes() const { return (size_t)n_tiles * kblocks * record_bytes; }
   // Algorithmic bytes of the mlx tensors this weight was built from.
   size_t mlx_bytes() const { return (size_t)N * K * bits / 8 + (size_t)2 * N * (K / group) * 2; }
