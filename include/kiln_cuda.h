@@ -283,6 +283,26 @@ KC_API void kc_qweight_free(kc_qweight_t w);
 KC_API int kc_quantized_matmul(kc_ctx_t ctx, kc_qweight_t w, const void* x_dev, int32_t m,
                                void* y_dev);
 
+/* kc_quantized_matmul without any allocation behind it. No counterpart in the
+ * reference (MLX owns every buffer there); added for callers that cannot let a
+ * library allocate: the split-K fp32 partials go to a fixed 16 MiB device array
+ * that is part of this library's image instead of a cudaMalloc'ed buffer owned
+ * by the weight handle, and the call itself makes no device or pinned-host
+ * allocation. Same kernels, same bits as kc_quantized_matmul.
+ *  - splits x min(m, 512) x out_features x 4 bytes must fit
+ *    kc_static_scratch_bytes(); a larger request fails with KC_ERR_UNSUPPORTED
+ *    before anything is launched (weights that are not split along K need no
+ *    scratch and always fit).
+ *  - The first call on a device looks the array up (this loads the library's
+ *    module on that device if nothing has yet) and sets the kernel attributes:
+ *    make it before any stream capture starts.
+ *  - The array is shared by all contexts and weights on a device and keeps the
+ *    last call's partials; calls overlapping in time on one device race on it. */
+KC_API int kc_quantized_matmul_static(kc_ctx_t ctx, kc_qweight_t w, const void* x_dev, int32_t m,
+                                      void* y_dev);
+/* Size of that array in bytes (a compile-time constant of the library). */
+KC_API int64_t kc_static_scratch_bytes(void);
+
 /* fast::rms_norm (crates/kiln-mlx/src/fast.rs:36-41): bf16 [rows, dim]. */
 KC_API int kc_rms_norm(kc_ctx_t ctx, const void* x_dev, const void* weight_dev, int32_t rows,
                        int32_t dim, float eps, void* y_dev);

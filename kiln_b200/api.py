@@ -457,6 +457,14 @@ class QuantizedWeight:
         self.ctx.sync()
         return y
 
+    def matmul_static(self, xp: torch.Tensor, m: int, y: torch.Tensor) -> None:
+        """kc_quantized_matmul_static on caller-owned buffers: xp bf16 [round_up(m, 16), in], y bf16 [m, out], both
+        on the device. This wrapper allocates nothing either; the caller synchronises (Context.sync)."""
+        assert xp.is_cuda and xp.dtype == torch.bfloat16 and xp.is_contiguous() and xp.shape[1] == self.in_features
+        assert xp.shape[0] >= (m + 15) // 16 * 16 and y.is_cuda and y.dtype == torch.bfloat16 and y.is_contiguous()
+        assert tuple(y.shape) == (m, self.out_features)
+        check(L.lib().kc_quantized_matmul_static(self.ctx._h, self._h, xp.data_ptr(), m, y.data_ptr()))
+
     def close(self) -> None:
         if self._h:
             L.lib().kc_qweight_free(self._h)

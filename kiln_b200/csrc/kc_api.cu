@@ -22,6 +22,7 @@
 
 #include "kc_attn.cuh"
 #include "kc_fused.cuh"
+#include "kc_internal.cuh"
 #include "kc_qlinear.cuh"
 
 using namespace kc;
@@ -125,6 +126,13 @@ struct kc_qweight {
   const void* op_ptr = nullptr;
   int op_rows = 0;
 };
+
+namespace kc {
+CtxView ctx_view(kc_ctx* c) { return CtxView{c->device, c->stream, c->status}; }
+const QWeight* qweight_view(kc_qweight* q) { return &q->w; }
+void ctx_count_launches(kc_ctx* c, int cls, int n) { c->launches += n; c->class_launches[cls] += n; }
+int api_fail(int code, const char* msg) { return fail(code, "%s", msg); }
+}  // namespace kc
 
 struct Layer {
   QWeight qkv, o, gate_up, down;
