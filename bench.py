@@ -188,6 +188,7 @@ class Workload:
 
 def timed_steps(w: Workload, base, n_steps: int, warmup: int, barrier=None, sampler=None):
     """Runs warmup + n_steps full-batch verify iterations; returns per-step records and the ON==OFF verdict."""
+    import torch
     eng = w.engine
     records, checked, identical = [], 0, True
     arrivals, outs = [], {}
@@ -215,6 +216,7 @@ def timed_steps(w: Workload, base, n_steps: int, warmup: int, barrier=None, samp
                 barrier()
             if sampler:
                 sampler.start()
+            torch.cuda.profiler.start()   # lets `ncu --profile-from-start off` list the timed region's launches only
             started = True
         t0 = time.perf_counter()
         eng.step()
@@ -232,6 +234,7 @@ def timed_steps(w: Workload, base, n_steps: int, warmup: int, barrier=None, samp
         records.append({"wall_ms": (t1 - t0) * 1e3, "dev_ms": dev_ms, "tokens": committed,
                         "proposed": s1["proposed_total"] - s0["proposed_total"],
                         "accepted": s1["accepted_total"] - s0["accepted_total"]})
+    torch.cuda.profiler.stop()
     return records, (checked, identical), arrivals, outs
 
 
