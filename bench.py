@@ -133,6 +133,7 @@ class Workload:
         import numpy as np
         import torch
         from kiln_b200 import api, host
+        from kiln_b200.replicas import rank_seed
         from kiln_b200.synth import PRESETS, synth_checkpoint
         preset, self.batch, self.k, lo, hi, self.gen = WORKLOADS[name]
         self.name, self.cfg = name, PRESETS[preset]
@@ -151,7 +152,7 @@ class Workload:
         del ck
         torch.cuda.empty_cache()
         self.build_s = time.time() - t0
-        rng = np.random.default_rng(1000 + rank)
+        rng = np.random.default_rng(rank_seed(1000, rank))
         lens = rng.integers(lo, hi + 1, size=self.batch)
         self.prompts = [rng.integers(0, cfg.vocab_size, size=int(n), dtype=np.int64).tolist() for n in lens]
         bs = 16
@@ -395,13 +396,9 @@ def main():
             checked += 1
             identical &= (outs.get(a, []) + fin[a][0]) == cont
 
-    if dist:
-        t = torch.tensor([dev_ms, wall_ms], dtype=torch.float64, device=f"cuda:{local_rank}")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dev_ms, wall_ms = float(t[0]), float(t[1])
-        c = torch.tensor([float(tokens), float(identical)], dtype=torch.float64, device=f"cuda:{local_rank}")
-        dist.all_reduce(c, op=dist.ReduceOp.SUM)
-        tokens, identical = float(c[0]), float(c[1]) == world
+    from kiln_b200.replicas import combine_over_ranks
+    tot = combine_over_ranks(dist, f"cuda:{local_rank}", dev_ms, wall_ms, tokens, identical, world)
+    dev_ms, wall_ms, tokens, identical = tot.device_ms, tot.wall_ms, tot.tokens, tot.all_identical
     if rank != 0:
         if dist:
             dist.destroy_process_group()

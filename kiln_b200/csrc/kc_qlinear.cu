@@ -273,12 +273,16 @@ struct QlKernelParams {
   float* partial;
   uint32_t* status;
   int dbg;   // experiment switches (KC_QL_DEBUG), 0 in normal operation
+  int pf_dist;
 };
 
 // BITS: 4 or 8. GPK: scale/bias pairs per row per k-block (1 or 2). NT: 128-row weight tiles per CTA, all
 // multiplied against the same activation k-block (NT * m_pad TMEM columns), which divides the activation
 // traffic from L2 by NT. NT is free to depend on the row count: it changes which CTA computes an output
 // element, never the order in which that element's k-blocks are accumulated.
+// TEMPORARY instrumentation (KC_QL_DEBUG & 256): per-CTA phase timestamps.
+__device__ unsigned long long g_ql_trace[1024 * 12];
+#define TR(k) do { if (p.dbg & 256) g_ql_trace[(blockIdx.y * gridDim.x + blockIdx.x) * 12 + (k)] = (k) == 0 || (k) == 9 ? globaltimer_ns() : (unsigned long long)clock64(); } while (0)
 #define QWAIT(bar, par, code) ((p.dbg & 16) ? mbar_wait_spin(bar, par, p.status, code) : mbar_wait(bar, par, p.status, code))
 
 template <int BITS, int GPK, int NT>
@@ -311,6 +315,7 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
   const int kb0 = split * p.kb_per_split;
   const int nkb = p.kb_per_split;
 
+  if (threadIdx.x == 0) { TR(0); TR(1); }
   if (threadIdx.x == 0) {
     for (int i = 0; i < RS; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], QL_DQ_WARPS); }
     for (int i = 0; i < AS; ++i) { mbar_init(&b_full[i], 1); mbar_init(&a_ready[i], QL_DQ_WARPS); mbar_init(&ab_empty[i], 1); }
@@ -328,6 +333,7 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) TR(2);
 
   if (warp == 0) {
     // ---- weight record producer: one bulk copy per owned tile per k-block ----
@@ -336,6 +342,9 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
       for (int i = 0; i < nkb; ++i, rp.advance(RS)) {
         const int rs = rp.stage; const uint32_t ph = rp.phase;
         if (!QWAIT(&raw_empty[rs], ph ^ 1, KC_DEV_QLINEAR | 1)) break;
+        if ((p.dbg & 128) && i + p.pf_dist < nkb)
+          for (int t = 0; t < nt_live; ++t)
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.records + ((size_t)(tile0 + t) * p.kblocks + kb0 + i + p.pf_dist) * p.record_bytes), "r"(p.record_bytes) : "memory");
         mbar_arrive_expect_tx(&raw_full[rs], p.record_bytes * nt_live);
         for (int t = 0; t < nt_live; ++t)
           bulk_g2s(sR + (size_t)rs * r_stage + (size_t)t * p.raw_stride,
@@ -374,6 +383,7 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
         ok = QWAIT(&a_ready[as], ph, KC_DEV_QLINEAR | 3) &&
              QWAIT(&b_full[as], ph, KC_DEV_QLINEAR | 4);
         if (!ok) break;
+        if (i == 0) TR(4);
         tc_fence_after();
         const uint64_t db = umma_smem_desc_sw128(smem_u32(sB + (size_t)as * b_bytes));
 #pragma unroll
@@ -392,6 +402,7 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
         if (p.dbg & 32) mbar_arrive(&ab_empty[as]); else umma_commit(&ab_empty[as]);
       }
       umma_commit(acc_full);
+      TR(5);
     }
   } else if (warp >= QL_DQ_WARP0) {
     // ---- dequantisers: thread = (row pair r0 / r0 + 64, chunk pair 2c', 2c' + 1) of every owned tile ----
@@ -415,6 +426,7 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
       const int as = ap.stage; const uint32_t aph = ap.phase;
       ok = __all_sync(0xffffffffu, QWAIT(&raw_full[rs], rph, KC_DEV_QLINEAR | 5));
       if (!ok) break;
+      if (i == 0 && td == 0) TR(3);
       ok = __all_sync(0xffffffffu, QWAIT(&ab_empty[as], aph ^ 1, KC_DEV_QLINEAR | 6));
       if (!ok) break;
 #pragma unroll
@@ -443,8 +455,10 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
       if (lane == 0) { mbar_arrive(&raw_empty[rs]); mbar_arrive(&a_ready[as]); }
     }
     // ---- epilogue: TMEM -> global ----
+    if (td == 0) TR(10);
     if (ok) ok = __all_sync(0xffffffffu, QWAIT(acc_full, 0, KC_DEV_QLINEAR | 7));
-    if (ok) {
+    if (td == 0) TR(6);
+    if (ok && !(p.dbg & 64)) {
       tc_fence_after();
       const int q = warp & 3;                       // TMEM lane quarter this warp may read
       const int half = (warp - QL_DQ_WARP0) >> 2;   // two warps share a quarter: split the column chunks
@@ -474,9 +488,11 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
       }
     }
   }
+  if (threadIdx.x == QL_DQ_WARP0 * 32) TR(7);
   __syncwarp();
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) { TR(8); TR(9); }
   if (warp == 2) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(p.tmem_cols)
@@ -547,6 +563,8 @@ cudaError_t qlinear_umma(const QLinearLaunch& l, cudaStream_t s) {
   static const int env_dbg = getenv("KC_QL_DEBUG") ? atoi(getenv("KC_QL_DEBUG")) : 0;
   static const int env_nt = getenv("KC_QL_NT") ? atoi(getenv("KC_QL_NT")) : 0;
   p.dbg = env_dbg;
+  static const int env_pf = getenv("KC_QL_PF") ? atoi(getenv("KC_QL_PF")) : 16;
+  p.pf_dist = env_pf;
   int nt = plan_tiles_per_cta(w, p.m_pad, w.sm_count);
   if (env_nt) nt = std::min(env_nt, p.m_pad <= 128 ? 4 : (p.m_pad <= 256 ? 2 : 1));
   if (w.bits == 4) return w.gpk == 2 ? launch_umma_nt<4, 2>(l, p, nt, s) : launch_umma_nt<4, 1>(l, p, nt, s);
@@ -583,3 +601,8 @@ cudaError_t qlinear_reduce_splits(const float* partial, int splits, int M, int N
 }
 
 }  // namespace kc
+
+// TEMPORARY: copies the per-CTA phase trace to the host.
+extern "C" __attribute__((visibility("default"))) int kc_debug_ql_trace(unsigned long long* out, int n) {
+  return (int)cudaMemcpyFromSymbol(out, kc::g_ql_trace, sizeof(unsigned long long) * n);
+}
