@@ -164,33 +164,38 @@ add_rmsnorm_kernel(const bf16* __restrict__ x, RowSource y, const bf16* __restri
 // fast::rope, crates/kiln-mlx/src/fast.rs:45-104). One CTA per token; K is
 // rotated, V copied, both land in the pool rows of the token's slot.
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ float src_val(const RowSource& s, size_t row, int col) {
-  if (s.part) {
-    float a = s.part[row * s.ld + col];
-    for (int k = 1; k < s.splits; ++k) a += s.part[k * s.split_stride + row * s.ld + col];
-    return bf16_round(a);
-  }
-  return __bfloat162float(s.y[row * s.ld + col]);
-}
-
+// sin/cos of the token's angles are computed once per CTA and shared by all heads; every thread then moves
+// 8 consecutive features of each half with 16-byte loads and stores.
 __global__ void __launch_bounds__(256)
 rope_kv_write_kernel(RowSource qkv, const bf16* __restrict__ bias, const float* __restrict__ inv_freq,
                      const int32_t* __restrict__ token_pos, const int32_t* __restrict__ kv_slot, int Hq, int Hkv,
                      int D, int traditional, int layer, int NB, int BS, bf16* __restrict__ pool,
                      bf16* __restrict__ q_out) {
+  __shared__ float s_cs[128], s_sn[128];   // head_dim <= 256
   const int tok = blockIdx.x;
   const int heads = Hq + 2 * Hkv;
   const int half = D / 2;
   const float pos = (float)token_pos[tok];
   const int slot = kv_slot[tok];
   const int blk = slot / BS, r = slot % BS;
-  for (int i = threadIdx.x; i < heads * half; i += blockDim.x) {
-    const int h = i / half, j = i - h * half;
-    const int i0 = traditional ? 2 * j : j, i1 = traditional ? 2 * j + 1 : j + half;
-    float a = src_val(qkv, tok, h * D + i0), b = src_val(qkv, tok, h * D + i1);
+  for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf(pos * inv_freq[j], &s_sn[j], &s_cs[j]);
+  __syncthreads();
+  const int per_head = D / 16;             // work items per head: 8 features of each half, or 16 interleaved ones
+  for (int it = threadIdx.x; it < heads * per_head; it += blockDim.x) {
+    const int h = it / per_head, c = it - h * per_head;
+    // features [e0, e0 + 8) and [e1, e1 + 8) of head h; the rotation pairs are (e0 + k, e1 + k) for split
+    // halves and (e0 + 2k, e0 + 2k + 1), (e1 + 2k, e1 + 2k + 1) for the interleaved convention
+    const int e0 = traditional ? 16 * c : 8 * c;
+    const int e1 = traditional ? 16 * c + 8 : half + 8 * c;
+    float a[8], b[8];
+    load8(qkv, tok, h * D + e0, a);
+    load8(qkv, tok, h * D + e1, b);
     if (bias) {
-      a = bf16_round(a + __bfloat162float(bias[h * D + i0]));
-      b = bf16_round(b + __bfloat162float(bias[h * D + i1]));
+      float ba[8], bb[8];
+      load8_bf16(bias + h * D + e0, ba);
+      load8_bf16(bias + h * D + e1, bb);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) { a[k] = bf16_round(a[k] + ba[k]); b[k] = bf16_round(b[k] + bb[k]); }
     }
     bf16* dst;
     if (h < Hq) {
@@ -200,13 +205,27 @@ rope_kv_write_kernel(RowSource qkv, const bf16* __restrict__ bias, const float* 
       dst = pool + (((((size_t)layer * 2 + kvsel) * NB + blk) * Hkv + kh) * BS + r) * D;
     }
     if (h < Hq + Hkv) {
-      float sn, cs;
-      sincosf(pos * inv_freq[j], &sn, &cs);
-      const float ra = a * cs - b * sn, rb = a * sn + b * cs;
-      a = ra; b = rb;
+      if (!traditional) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float cs = s_cs[8 * c + k], sn = s_sn[8 * c + k];
+          const float ra = a[k] * cs - b[k] * sn, rb = a[k] * sn + b[k] * cs;
+          a[k] = ra; b[k] = rb;
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          float cs = s_cs[8 * c + k], sn = s_sn[8 * c + k];
+          float ra = a[2 * k] * cs - a[2 * k + 1] * sn, rb = a[2 * k] * sn + a[2 * k + 1] * cs;
+          a[2 * k] = ra; a[2 * k + 1] = rb;
+          cs = s_cs[8 * c + 4 + k]; sn = s_sn[8 * c + 4 + k];
+          ra = b[2 * k] * cs - b[2 * k + 1] * sn; rb = b[2 * k] * sn + b[2 * k + 1] * cs;
+          b[2 * k] = ra; b[2 * k + 1] = rb;
+        }
+      }
     }
-    dst[i0] = __float2bfloat16_rn(a);
-    dst[i1] = __float2bfloat16_rn(b);
+    store8_bf16(dst + e0, a);
+    store8_bf16(dst + e1, b);
   }
 }
 
@@ -292,6 +311,7 @@ cudaError_t launch_add_rmsnorm(const bf16* x, const SublayerOut& y, const bf16* 
 cudaError_t launch_rope_kv_write(const SublayerOut& qkv, const bf16* bias, const float* inv_freq, const int32_t* token_pos,
                                  const int32_t* kv_slot, int n, int Hq, int Hkv, int D, int traditional, int layer,
                                  int NB, int BS, bf16* pool, bf16* q_out, cudaStream_t s) {
+  if (D % 16 || D > 256) return cudaErrorInvalidValue;
   rope_kv_write_kernel<<<n, 256, 0, s>>>(row_source(qkv), bias, inv_freq, token_pos, kv_slot, Hq, Hkv, D, traditional, layer, NB,
                                          BS, pool, q_out);
   return cudaGetLastError();

@@ -254,10 +254,14 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 // The kernel
 // ---------------------------------------------------------------------------
 
-constexpr int QL_THREADS = 384;        // 12 warps
 constexpr int QL_DQ_WARP0 = 4;         // first dequant/epilogue warp
-constexpr int QL_DQ_WARPS = 8;
+constexpr int QL_DQ_GROUPS = 2;        // dequant groups; group g converts k-blocks g, g + G, g + 2G, ...
+constexpr int QL_DQ_GROUP_WARPS = 8;
+constexpr int QL_DQ_GROUP_THREADS = QL_DQ_GROUP_WARPS * 32;
+constexpr int QL_DQ_WARPS = QL_DQ_GROUPS * QL_DQ_GROUP_WARPS;
+constexpr int QL_THREADS = (QL_DQ_WARP0 + QL_DQ_WARPS) * 32;   // 20 warps
 constexpr int QL_A_BYTES = QL_TILE_N * 128;  // one 128-row A tile of one stage
+constexpr int QL_EPI_STAGE_BYTES = 32 * 32 * 4;   // per-warp transpose buffer of the epilogue
 
 struct QlKernelParams {
   const uint8_t* records;
@@ -273,18 +277,34 @@ struct QlKernelParams {
   float* partial;
   uint32_t* status;
   int dbg;   // experiment switches (KC_QL_DEBUG), 0 in normal operation
-  int pf_dist;
 };
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// TEMPORARY instrumentation (KC_QL_DEBUG & 256): per-CTA phase timestamps.
+__device__ unsigned long long g_ql_trace[1024 * 32];
+#define TR(k) do { if (p.dbg & 256) g_ql_trace[(blockIdx.y * gridDim.x + blockIdx.x) * 32 + (k)] = (k) == 0 || (k) == 9 ? globaltimer_ns() : (unsigned long long)clock64(); } while (0)
 
 // BITS: 4 or 8. GPK: scale/bias pairs per row per k-block (1 or 2). NT: 128-row weight tiles per CTA, all
 // multiplied against the same activation k-block (NT * m_pad TMEM columns), which divides the activation
 // traffic from L2 by NT. NT is free to depend on the row count: it changes which CTA computes an output
 // element, never the order in which that element's k-blocks are accumulated.
-// TEMPORARY instrumentation (KC_QL_DEBUG & 256): per-CTA phase timestamps.
-__device__ unsigned long long g_ql_trace[1024 * 12];
-#define TR(k) do { if (p.dbg & 256) g_ql_trace[(blockIdx.y * gridDim.x + blockIdx.x) * 12 + (k)] = (k) == 0 || (k) == 9 ? globaltimer_ns() : (unsigned long long)clock64(); } while (0)
-#define QWAIT(bar, par, code) ((p.dbg & 16) ? mbar_wait_spin(bar, par, p.status, code) : mbar_wait(bar, par, p.status, code))
-
+//
+// Warp roles: 0 = weight-record producer (bulk copies), 1 = activation producer (TMA), 2 = MMA issuer and
+// TMEM owner, 3 idle, 4..19 = two dequantiser groups of eight warps that take alternate k-blocks (the waits,
+// the proxy fence and the barrier round trip of one group hide behind the other group's arithmetic), then
+// all sixteen drain TMEM.
 template <int BITS, int GPK, int NT>
 __global__ void __launch_bounds__(QL_THREADS, 1)
 qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_constant__ CUtensorMap map64,
@@ -317,8 +337,8 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
 
   if (threadIdx.x == 0) { TR(0); TR(1); }
   if (threadIdx.x == 0) {
-    for (int i = 0; i < RS; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], QL_DQ_WARPS); }
-    for (int i = 0; i < AS; ++i) { mbar_init(&b_full[i], 1); mbar_init(&a_ready[i], QL_DQ_WARPS); mbar_init(&ab_empty[i], 1); }
+    for (int i = 0; i < RS; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], QL_DQ_GROUP_WARPS); }
+    for (int i = 0; i < AS; ++i) { mbar_init(&b_full[i], 1); mbar_init(&a_ready[i], QL_DQ_GROUP_WARPS); mbar_init(&ab_empty[i], 1); }
     mbar_init(acc_full, 1);
     mbar_fence_init();
   }
@@ -341,10 +361,8 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
       RingPos rp;
       for (int i = 0; i < nkb; ++i, rp.advance(RS)) {
         const int rs = rp.stage; const uint32_t ph = rp.phase;
-        if (!QWAIT(&raw_empty[rs], ph ^ 1, KC_DEV_QLINEAR | 1)) break;
-        if ((p.dbg & 128) && i + p.pf_dist < nkb)
-          for (int t = 0; t < nt_live; ++t)
-            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p.records + ((size_t)(tile0 + t) * p.kblocks + kb0 + i + p.pf_dist) * p.record_bytes), "r"(p.record_bytes) : "memory");
+        if (!mbar_wait(&raw_empty[rs], ph ^ 1, p.status, KC_DEV_QLINEAR | 1)) break;
+        if (i == 8) TR(16);
         mbar_arrive_expect_tx(&raw_full[rs], p.record_bytes * nt_live);
         for (int t = 0; t < nt_live; ++t)
           bulk_g2s(sR + (size_t)rs * r_stage + (size_t)t * p.raw_stride,
@@ -358,8 +376,9 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
       RingPos ap;
       for (int i = 0; i < nkb; ++i, ap.advance(AS)) {
         const int as = ap.stage; const uint32_t ph = ap.phase;
-        if (!QWAIT(&ab_empty[as], ph ^ 1, KC_DEV_QLINEAR | 2)) break;
+        if (!mbar_wait(&ab_empty[as], ph ^ 1, p.status, KC_DEV_QLINEAR | 2)) break;
         if (p.dbg & 2) { mbar_arrive(&b_full[as]); continue; }
+        if (i == 8) TR(20);
         mbar_arrive_expect_tx(&b_full[as], b_bytes);
         uint8_t* dst = sB + (size_t)as * b_bytes;
         const int x = (kb0 + i) * QL_KB;
@@ -380,9 +399,11 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
       RingPos ap;
       for (int i = 0; i < nkb && ok; ++i, ap.advance(AS)) {
         const int as = ap.stage; const uint32_t ph = ap.phase;
-        ok = QWAIT(&a_ready[as], ph, KC_DEV_QLINEAR | 3) &&
-             QWAIT(&b_full[as], ph, KC_DEV_QLINEAR | 4);
+        ok = mbar_wait(&a_ready[as], ph, p.status, KC_DEV_QLINEAR | 3);
+        if (i == 8) TR(18);
+        ok = ok && mbar_wait(&b_full[as], ph, p.status, KC_DEV_QLINEAR | 4);
         if (!ok) break;
+        if (i == 8) TR(21);
         if (i == 0) TR(4);
         tc_fence_after();
         const uint64_t db = umma_smem_desc_sw128(smem_u32(sB + (size_t)as * b_bytes));
@@ -399,15 +420,19 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
             }
           }
         }
-        if (p.dbg & 32) mbar_arrive(&ab_empty[as]); else umma_commit(&ab_empty[as]);
+        umma_commit(&ab_empty[as]);
+        if (i == 8) TR(19);
+        if (i >= 4 && i <= 7) TR(18 + i);   // 22..25: commits of k-blocks 4..7
       }
       umma_commit(acc_full);
       TR(5);
     }
   } else if (warp >= QL_DQ_WARP0) {
     // ---- dequantisers: thread = (row pair r0 / r0 + 64, chunk pair 2c', 2c' + 1) of every owned tile ----
-    const int td = threadIdx.x - QL_DQ_WARP0 * 32;  // 0..255
-    const int cp = td & 3, r0 = td >> 2;            // chunk pair 0..3, row 0..63
+    const int td = threadIdx.x - QL_DQ_WARP0 * 32;  // 0..511
+    const int grp = td / QL_DQ_GROUP_THREADS;
+    const int tg = td - grp * QL_DQ_GROUP_THREADS;  // 0..255 inside the group
+    const int cp = tg & 3, r0 = tg >> 2;            // chunk pair 0..3, row 0..63
     const int gi = (GPK == 2) ? (cp >> 1) : 0;
     // shared-memory offsets that do not change with the k-block
     uint32_t a_off[2][2], raw_off[2], sb_off[2];
@@ -421,14 +446,18 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
     }
     bool ok = true;
     RingPos rp, ap;
-    for (int i = 0; i < nkb && ok; ++i, rp.advance(RS), ap.advance(AS)) {
+    for (int g = 0; g < grp; ++g) { rp.advance(RS); ap.advance(AS); }
+    for (int i = grp; i < nkb && ok; i += QL_DQ_GROUPS) {
       const int rs = rp.stage; const uint32_t rph = rp.phase;
       const int as = ap.stage; const uint32_t aph = ap.phase;
-      ok = __all_sync(0xffffffffu, QWAIT(&raw_full[rs], rph, KC_DEV_QLINEAR | 5));
+      if (i == 8 && td == 0) TR(11);
+      ok = __all_sync(0xffffffffu, mbar_wait(&raw_full[rs], rph, p.status, KC_DEV_QLINEAR | 5));
       if (!ok) break;
-      if (i == 0 && td == 0) TR(3);
-      ok = __all_sync(0xffffffffu, QWAIT(&ab_empty[as], aph ^ 1, KC_DEV_QLINEAR | 6));
+      if (i == 8 && td == 0) TR(17);
+      ok = __all_sync(0xffffffffu, mbar_wait(&ab_empty[as], aph ^ 1, p.status, KC_DEV_QLINEAR | 6));
       if (!ok) break;
+      if (i == 8 && td == 0) TR(12);
+      if (i == grp && tg == 0 && grp == 0) TR(3);
 #pragma unroll
       for (int t = 0; t < NT; ++t) {
         if (t < nt_live && !(p.dbg & 1)) {
@@ -450,38 +479,61 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
           }
         }
       }
-      if (!(p.dbg & 8)) fence_proxy_async_smem();
+      if (i == 8 && td == 0) TR(13);
+      fence_proxy_async_smem();
+      if (i == 8 && td == 0) TR(14);
       __syncwarp();
       if (lane == 0) { mbar_arrive(&raw_empty[rs]); mbar_arrive(&a_ready[as]); }
+      if (i == 8 && td == 0) TR(15);
+#pragma unroll
+      for (int g = 0; g < QL_DQ_GROUPS; ++g) { rp.advance(RS); ap.advance(AS); }
     }
-    // ---- epilogue: TMEM -> global ----
+    // ---- epilogue: TMEM -> per-warp transpose in shared memory -> row-contiguous vector stores ----
     if (td == 0) TR(10);
-    if (ok) ok = __all_sync(0xffffffffu, QWAIT(acc_full, 0, KC_DEV_QLINEAR | 7));
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(acc_full, 0, p.status, KC_DEV_QLINEAR | 7));
     if (td == 0) TR(6);
     if (ok && !(p.dbg & 64)) {
       tc_fence_after();
-      const int q = warp & 3;                       // TMEM lane quarter this warp may read
-      const int half = (warp - QL_DQ_WARP0) >> 2;   // two warps share a quarter: split the column chunks
-      const int chunks = p.m_pad / 16;
-      for (int item = half; item < nt_live * chunks; item += 2) {
-        const int t = item / chunks, ch = item % chunks;
-        const int n = (tile0 + t) * QL_TILE_N + q * 32 + lane;
-        const int col = (NT == 1) ? ch * 16 : t * ((p.m_pad + 31) & ~31) + ch * 16;   // NT == 1: columns are m directly (incl. the 256+ tile)
-        uint32_t v[16];
-        tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + col, v);
-        if (n < p.N) {
-          if (p.splits == 1) {
+      // every MMA has completed and every copy into the rings has been consumed: the ring memory is free
+      float* stage = reinterpret_cast<float*>(smem + (size_t)(warp - QL_DQ_WARP0) * QL_EPI_STAGE_BYTES);
+      const int q = warp & 3;                        // TMEM lane quarter this warp may read
+      const int eg = (warp - QL_DQ_WARP0) >> 2;      // warps of one quarter split the 32-column chunks
+      const int chunks = (p.m_pad + 31) >> 5;
+      const int col_stride = (p.m_pad + 31) & ~31;
+      const bool vec_ok = p.splits == 1 ? ((p.ldy & 3) == 0 && (reinterpret_cast<uintptr_t>(p.y) & 7) == 0)
+                                        : ((p.N & 3) == 0 && (reinterpret_cast<uintptr_t>(p.partial) & 15) == 0);
+      const int nl = 4 * (lane & 7), mr0 = lane >> 3;
+      for (int item = eg; item < nt_live * chunks; item += QL_DQ_WARPS / 4) {
+        const int t = item / chunks, ch = item - t * chunks;
+        const int col = (NT == 1 ? 0 : t * col_stride) + ch * 32;   // NT == 1: columns are m directly (incl. the 256+ accumulator)
+        uint32_t v[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + col, v);
+        __syncwarp();                                // the previous item's reads of the buffer are done
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int m = ch * 16 + j;
-              if (m < p.M) p.y[(size_t)(p.row0 + m) * p.ldy + n] = __float2bfloat16_rn(__uint_as_float(v[j]));
+        for (int j = 0; j < 32; ++j) stage[j * 32 + lane] = __uint_as_float(v[j]);   // stage[m][n]
+        __syncwarp();
+        const int n = (tile0 + t) * QL_TILE_N + q * 32 + nl;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int mr = 4 * k + mr0;
+          const int m = ch * 32 + mr;
+          if (m >= p.M || n >= p.N) continue;
+          const float4 f = *reinterpret_cast<const float4*>(stage + mr * 32 + nl);
+          if (p.splits == 1) {
+            bf16* dst = p.y + (size_t)(p.row0 + m) * p.ldy + n;
+            if (vec_ok && n + 3 < p.N) {
+              *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf162(f.x, f.y), pack_bf162(f.z, f.w));
+            } else {
+              const float e[4] = {f.x, f.y, f.z, f.w};
+              for (int c = 0; c < 4 && n + c < p.N; ++c) dst[c] = __float2bfloat16_rn(e[c]);
             }
           } else {
-            float* dst = p.partial + (size_t)split * p.M * p.N;
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int m = ch * 16 + j;
-              if (m < p.M) dst[(size_t)m * p.N + n] = __uint_as_float(v[j]);
+            float* dst = p.partial + ((size_t)split * p.M + m) * p.N + n;
+            if (vec_ok && n + 3 < p.N) {
+              *reinterpret_cast<float4*>(dst) = f;
+            } else {
+              const float e[4] = {f.x, f.y, f.z, f.w};
+              for (int c = 0; c < 4 && n + c < p.N; ++c) dst[c] = e[c];
             }
           }
         }
@@ -563,8 +615,6 @@ cudaError_t qlinear_umma(const QLinearLaunch& l, cudaStream_t s) {
   static const int env_dbg = getenv("KC_QL_DEBUG") ? atoi(getenv("KC_QL_DEBUG")) : 0;
   static const int env_nt = getenv("KC_QL_NT") ? atoi(getenv("KC_QL_NT")) : 0;
   p.dbg = env_dbg;
-  static const int env_pf = getenv("KC_QL_PF") ? atoi(getenv("KC_QL_PF")) : 16;
-  p.pf_dist = env_pf;
   int nt = plan_tiles_per_cta(w, p.m_pad, w.sm_count);
   if (env_nt) nt = std::min(env_nt, p.m_pad <= 128 ? 4 : (p.m_pad <= 256 ? 2 : 1));
   if (w.bits == 4) return w.gpk == 2 ? launch_umma_nt<4, 2>(l, p, nt, s) : launch_umma_nt<4, 1>(l, p, nt, s);
