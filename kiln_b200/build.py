@@ -52,7 +52,7 @@ def build_cuda(force: bool = False, verbose: bool = False) -> Path:
         objs.append(obj)
         if not force and not _stale(obj, [src] + deps[len(cu):]):
             continue
-        cmd = [_nvcc(), *NVCC_FLAGS, "-c", str(src), "-o", str(obj)]
+        cmd = [_nvcc(), *NVCC_FLAGS, *os.environ.get("KILN_B200_NVCC_FLAGS", "").split(), "-c", str(src), "-o", str(obj)]
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")

@@ -1161,8 +1161,10 @@ extern "C" int kc_paged_attention(kc_ctx_t c, kc_kv_t kv, int32_t layer, const v
   if (!rc) rc = ensure_attn_ws(m, p);
   if (!rc) {
     AttnParams a = attn_params(m, kv, p, layer, (const bf16*)q_dev, (bf16*)out_dev, scale, softcap, window, num_heads);
-    cudaError_t e = paged_attention(kv->map, a, kv->head_dim, p.tokens_per_item, p.n_work, p.max_chunks, n, c->stream);
-    if (e != cudaSuccess) rc = fail(KC_ERR_CUDA, "kc_paged_attention: %s", cudaGetErrorString(e));
+    rc = [&]() -> int {
+      LAUNCH(c, KC_PROF_ATTN, 2, paged_attention(kv->map, a, kv->head_dim, p.tokens_per_item, p.n_work, p.max_chunks, n, c->stream));
+      return KC_OK;
+    }();
   }
   cudaStreamSynchronize(c->stream);
   std::string keep = g_err;

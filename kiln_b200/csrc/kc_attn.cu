@@ -32,6 +32,15 @@ namespace {
 // A multiple of every key-split count, so one ring slot is always drained by the same
 // consumer warps and each warp meets a slot's barrier phases strictly in order.
 constexpr int ATT_STAGES = 8;
+#ifndef ATT_Q_REGS
+#define ATT_Q_REGS 0
+#endif
+#ifndef ATT_COND_RESCALE
+#define ATT_COND_RESCALE 1
+#endif
+#ifndef ATT_MINB
+#define ATT_MINB 3
+#endif
 
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -74,7 +83,7 @@ struct AttnSmem {
 };
 
 template <int D, int MT>
-__global__ void __launch_bounds__((MT * KeySplit<MT>::value + 1) * 32)
+__global__ void __launch_bounds__((MT * KeySplit<MT>::value + 1) * 32, (D <= 128 && MT <= 2) ? ATT_MINB : 1)
 attn_partial_kernel(const __grid_constant__ CUtensorMap kvmap, const AttnParams p) {
   using S = AttnSmem<D, MT>;
   constexpr int KS = S::KS;
@@ -82,6 +91,8 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap kvmap, const AttnParams 
   constexpr int NT_D = D / 8;   // PV n-tiles
   constexpr int KSTEPS = D / 16;
 
+  pdl_launch_dependents();
+  pdl_wait();   // everything below reads step data (work items, q, block tables, this layer's K/V rows)
   const int chunk = p.chunk_lo_grid + blockIdx.x;
   const int kvh = blockIdx.y;
   const int4 wk = p.work[blockIdx.z];   // {seq, first token row in the step, tokens, position of first token}
@@ -126,17 +137,24 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap kvmap, const AttnParams 
   __syncthreads();
 
   if (warp == CW) {
-    // ---- producer: one TMA per 64-feature slab of a K or V tile ----
-    if (lane == 0) {
-      tma_prefetch_desc(&kvmap);
-      const int32_t* tbl = p.block_tables + (size_t)seq * p.max_blocks;
-      for (int t = 0; t < ntiles; ++t) {
-        const int st = t & (ATT_STAGES - 1); const uint32_t ph = (t / ATT_STAGES) & 1;   // ATT_STAGES is a power of two
-        if (!mbar_wait(&empty[st], ph ^ 1, p.status, KC_DEV_ATTN | 1)) break;
-        const int key0 = key_base + t * 16;
-        const int blk = tbl[key0 / p.BS];
-        const long long rowK = ((((long long)p.layer * 2 + 0) * p.NB + blk) * p.Hkv + kvh) * p.BS + (key0 % p.BS);
-        const long long rowV = ((((long long)p.layer * 2 + 1) * p.NB + blk) * p.Hkv + kvh) * p.BS + (key0 % p.BS);
+    // ---- producer: one TMA per 64-feature slab of a K or V tile. The chunk's block-table entries (at most
+    //      ATT_CHUNK / 16 = 32) are fetched once, one per lane, so the per-tile loop has no global load in it ----
+    if (lane == 0) tma_prefetch_desc(&kvmap);
+    const int32_t* tbl = p.block_tables + (size_t)seq * p.max_blocks;
+    const int blk0 = key_base / p.BS;
+    const int nblk = (keys_here + p.BS - 1) / p.BS;
+    const int my_blk = lane < nblk ? tbl[blk0 + lane] : 0;   // block_size is a power of two >= 16: chunks start on block edges
+    bool alive = true;                                        // lane 0 only: false after a bounded wait gave up
+    for (int t = 0; t < ntiles; ++t) {
+      const int st = t & (ATT_STAGES - 1); const uint32_t ph = (t / ATT_STAGES) & 1;   // ATT_STAGES is a power of two
+      const int koff = t * 16;
+      const int blk = __shfl_sync(0xffffffffu, my_blk, koff / p.BS);
+      if (lane == 0 && alive) {
+        alive = mbar_wait(&empty[st], ph ^ 1, p.status, KC_DEV_ATTN | 1);
+        if (!alive) continue;
+        const int in_blk = (key_base + koff) % p.BS;
+        const long long rowK = ((((long long)p.layer * 2 + 0) * p.NB + blk) * p.Hkv + kvh) * p.BS + in_blk;
+        const long long rowV = ((((long long)p.layer * 2 + 1) * p.NB + blk) * p.Hkv + kvh) * p.BS + in_blk;
         mbar_arrive_expect_tx(&full[st], S::STAGE_BYTES);
         uint8_t* dst = ring + (size_t)st * S::STAGE_BYTES;
 #pragma unroll
@@ -164,6 +182,13 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap kvmap, const AttnParams 
     float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
 
     const uint32_t q_base = smem_u32(sQ) + (mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * S::Q_LD + (lane >> 4) * 16;
+    // The Q fragments do not change over the key loop: keep them in registers when head_dim leaves room.
+    constexpr bool Q_IN_REGS = ATT_Q_REGS && D <= 128;
+    uint32_t qf[Q_IN_REGS ? KSTEPS : 1][4];
+    if (Q_IN_REGS) {
+#pragma unroll
+      for (int kk = 0; kk < KSTEPS; ++kk) ldsm_x4(qf[kk], q_base + kk * 32);
+    }
     bool ok = true;
     for (int t = ks; t < ntiles; t += KS) {
       const int st = t & (ATT_STAGES - 1); const uint32_t ph = (t / ATT_STAGES) & 1;
@@ -177,7 +202,8 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap kvmap, const AttnParams 
 #pragma unroll
       for (int kk = 0; kk < KSTEPS; ++kk) {
         uint32_t a[4], b[4];
-        ldsm_x4(a, q_base + kk * 32);
+        if (Q_IN_REGS) { a[0] = qf[kk][0]; a[1] = qf[kk][1]; a[2] = qf[kk][2]; a[3] = qf[kk][3]; }
+        else ldsm_x4(a, q_base + kk * 32);
         {
           const int mi = lane >> 3;
           const int key = (mi >> 1) * 8 + (lane & 7);
@@ -236,11 +262,14 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap kvmap, const AttnParams 
       pa[2] = pack_bf162(s[1][0], s[1][1]);
       pa[3] = pack_bf162(s[1][2], s[1][3]);
 
-      // O = O * alpha + P V
+      // O = O * alpha + P V. Multiplying by exactly 1 changes no bit, so the rescale is skipped when no row of
+      // the warp moved its maximum (the common case once the running maximum has settled).
+      if (!ATT_COND_RESCALE || !__all_sync(0xffffffffu, al_lo == 1.f && al_hi == 1.f)) {
+#pragma unroll
+        for (int dn = 0; dn < NT_D; ++dn) { o[dn][0] *= al_lo; o[dn][1] *= al_lo; o[dn][2] *= al_hi; o[dn][3] *= al_hi; }
+      }
 #pragma unroll
       for (int dn = 0; dn < NT_D; dn += 2) {
-        o[dn][0] *= al_lo; o[dn][1] *= al_lo; o[dn][2] *= al_hi; o[dn][3] *= al_hi;
-        o[dn + 1][0] *= al_lo; o[dn + 1][1] *= al_lo; o[dn + 1][2] *= al_hi; o[dn + 1][3] *= al_hi;
         uint32_t b[4];
         const int mi = lane >> 3;
         const int key = (mi & 1) * 8 + (lane & 7);
@@ -323,6 +352,8 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap kvmap, const AttnParams 
 // out[token, head, :] = sum_c w_c o_c / sum_c w_c l_c over the row's own chunks, in chunk order.
 template <int D>
 __global__ void attn_combine_kernel(const AttnParams p, int n_rows) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= n_rows) return;
@@ -361,8 +392,7 @@ cudaError_t launch_partial(const CUtensorMap& map, const AttnParams& p, int n_wo
     configured = true;
   }
   dim3 grid(grid_chunks, p.Hkv, n_work);
-  attn_partial_kernel<D, MT><<<grid, (S::CW + 1) * 32, S::TOTAL, s>>>(map, p);
-  return cudaGetLastError();
+  return launch_k(attn_partial_kernel<D, MT>, grid, dim3((S::CW + 1) * 32), S::TOTAL, s, map, p);
 }
 
 template <int D>
@@ -377,8 +407,7 @@ cudaError_t launch_d(const CUtensorMap& map, const AttnParams& p, int mt, int n_
   }
   if (e != cudaSuccess) return e;
   const int n_rows = n_tokens * p.Hq;
-  attn_combine_kernel<D><<<(n_rows + 7) / 8, 256, 0, s>>>(p, n_rows);
-  return cudaGetLastError();
+  return launch_k(attn_combine_kernel<D>, dim3((n_rows + 7) / 8), dim3(256), 0, s, p, n_rows);
 }
 
 }  // namespace

@@ -10,6 +10,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #ifndef __CUDA_ARCH_FEAT_SM100_ALL
 #if defined(__CUDA_ARCH__)
@@ -163,6 +164,39 @@ __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
   return v;
+}
+
+// ---- programmatic dependent launch ---------------------------------------
+// Every kernel of the step is launched with programmatic stream serialization: it may become resident while
+// its predecessor in the stream is still running, executes whatever touches no step data (barrier set-up,
+// TMEM allocation, descriptor prefetch, loads of WEIGHTS, which no kernel writes), and calls pdl_wait() before
+// its first access to memory that an earlier kernel of the stream writes or reads. pdl_wait() returns once the
+// predecessor grid has completed and its writes are visible; since every kernel calls it before it ends, a
+// kernel's completion implies the completion of everything queued before it. pdl_launch_dependents() lets the
+// successor start being scheduled; it is issued first thing, so the successor fills SMs as they drain.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+#ifndef __CUDA_ARCH__
+// KILN_PDL=0 in the environment launches every kernel with plain stream ordering (the device-side calls above are
+// then no-ops).
+inline bool pdl_enabled() {
+  static const bool on = [] { const char* e = getenv("KILN_PDL"); return !(e && e[0] == '0'); }();
+  return on;
+}
+#endif
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+#ifndef __CUDA_ARCH__
+  if (pdl_enabled()) { cfg.attrs = attr; cfg.numAttrs = 1; }
+#endif
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
 // A ring position: stage index and phase bit, advanced without division.

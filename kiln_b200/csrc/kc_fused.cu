@@ -28,6 +28,8 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 __global__ void embed_kernel(const uint32_t* __restrict__ w, const bf16* __restrict__ scales,
                              const bf16* __restrict__ biases, const uint32_t* __restrict__ ids, int H, int bits,
                              int group, float embed_scale, int vocab, bf16* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int tok = blockIdx.x;
   uint32_t id = ids[tok];
   if (id >= (uint32_t)vocab) id = 0;  // ids are validated on the host; never index out of the table
@@ -99,6 +101,8 @@ __global__ void __launch_bounds__(256)
 add_rmsnorm_kernel(const bf16* __restrict__ x, RowSource y, const bf16* __restrict__ w_pre,
                    const bf16* __restrict__ w_out, const int32_t* __restrict__ row_map, int H, float eps,
                    bf16* __restrict__ h_out, bf16* __restrict__ normed) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ float srow[];   // H floats
   __shared__ float red[32];
   const int row = blockIdx.x;
@@ -171,6 +175,8 @@ rope_kv_write_kernel(RowSource qkv, const bf16* __restrict__ bias, const float* 
                      const int32_t* __restrict__ token_pos, const int32_t* __restrict__ kv_slot, int Hq, int Hkv,
                      int D, int traditional, int layer, int NB, int BS, bf16* __restrict__ pool,
                      bf16* __restrict__ q_out) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float s_cs[128], s_sn[128];   // head_dim <= 256
   const int tok = blockIdx.x;
   const int heads = Hq + 2 * Hkv;
@@ -249,6 +255,8 @@ __device__ __forceinline__ float act_gelu_mul(float g, float u) {
 }
 
 __global__ void __launch_bounds__(256) glu_kernel(const bf16* __restrict__ gu, int n, int F, int gelu, bf16* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int per_row = F / 8;
   const int total = n * per_row;
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
@@ -264,6 +272,8 @@ __global__ void __launch_bounds__(256) glu_kernel(const bf16* __restrict__ gu, i
 
 // CausalLm::softcap_logits (nn.rs:1158-1169): tanh(l / cap) * cap, each op rounded to bf16.
 __global__ void softcap_kernel(bf16* __restrict__ x, long long total, float cap) {
+  pdl_launch_dependents();
+  pdl_wait();
   const float capb = bf16_round(cap);
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
@@ -276,6 +286,8 @@ __global__ void softcap_kernel(bf16* __restrict__ x, long long total, float cap)
 // PagedKv::copy_block (paged.rs:230-250): rows of `src` into `dst` in every layer, K and V.
 __global__ void copy_block_kernel(bf16* __restrict__ pool, int planes, int NB, size_t block_elems, uint32_t src,
                                   uint32_t dst) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int plane = blockIdx.y;  // layer * 2 + kv
   if (plane >= planes) return;
   uint4* base = reinterpret_cast<uint4*>(pool + ((size_t)plane * NB) * block_elems);
@@ -289,8 +301,7 @@ __global__ void copy_block_kernel(bf16* __restrict__ pool, int planes, int NB, s
 
 cudaError_t launch_embed(const uint32_t* w, const bf16* scales, const bf16* biases, const uint32_t* ids, int n, int H,
                          int bits, int group, float embed_scale, int vocab, bf16* out, cudaStream_t s) {
-  embed_kernel<<<n, 256, 0, s>>>(w, scales, biases, ids, H, bits, group, embed_scale, vocab, out);
-  return cudaGetLastError();
+  return launch_k(embed_kernel, dim3(n), dim3(256), 0, s, w, scales, biases, ids, H, bits, group, embed_scale, vocab, out);
 }
 
 static RowSource row_source(const SublayerOut& y) {
@@ -304,38 +315,33 @@ cudaError_t launch_add_rmsnorm(const bf16* x, const SublayerOut& y, const bf16* 
                                cudaStream_t s) {
   if (rows <= 0) return cudaSuccess;
   if (H % 8) return cudaErrorInvalidValue;
-  add_rmsnorm_kernel<<<rows, 256, H * sizeof(float), s>>>(x, row_source(y), w_pre, w_out, row_map, H, eps, h_out, normed);
-  return cudaGetLastError();
+  return launch_k(add_rmsnorm_kernel, dim3(rows), dim3(256), H * sizeof(float), s, x, row_source(y), w_pre, w_out, row_map, H, eps, h_out, normed);
 }
 
 cudaError_t launch_rope_kv_write(const SublayerOut& qkv, const bf16* bias, const float* inv_freq, const int32_t* token_pos,
                                  const int32_t* kv_slot, int n, int Hq, int Hkv, int D, int traditional, int layer,
                                  int NB, int BS, bf16* pool, bf16* q_out, cudaStream_t s) {
   if (D % 16 || D > 256) return cudaErrorInvalidValue;
-  rope_kv_write_kernel<<<n, 256, 0, s>>>(row_source(qkv), bias, inv_freq, token_pos, kv_slot, Hq, Hkv, D, traditional, layer, NB,
-                                         BS, pool, q_out);
-  return cudaGetLastError();
+  return launch_k(rope_kv_write_kernel, dim3(n), dim3(256), 0, s, row_source(qkv), bias, inv_freq, token_pos, kv_slot, Hq, Hkv, D,
+                  traditional, layer, NB, BS, pool, q_out);
 }
 
 cudaError_t launch_glu(const bf16* gu, int n, int F, int gelu, bf16* out, cudaStream_t s) {
   if (F % 8) return cudaErrorInvalidValue;
   const long long total = (long long)n * (F / 8);
   const int blocks = (int)std::min<long long>((total + 255) / 256, 148LL * 8);
-  glu_kernel<<<blocks, 256, 0, s>>>(gu, n, F, gelu, out);
-  return cudaGetLastError();
+  return launch_k(glu_kernel, dim3(blocks), dim3(256), 0, s, gu, n, F, gelu, out);
 }
 
 cudaError_t launch_softcap(bf16* x, long long total, float cap, cudaStream_t s) {
   const int blocks = (int)std::min<long long>((total + 255) / 256, 148LL * 8);
-  softcap_kernel<<<blocks, 256, 0, s>>>(x, total, cap);
-  return cudaGetLastError();
+  return launch_k(softcap_kernel, dim3(blocks), dim3(256), 0, s, x, total, cap);
 }
 
 cudaError_t launch_copy_block(bf16* pool, int layers, int NB, size_t block_elems, uint32_t src, uint32_t dst,
                               cudaStream_t s) {
   dim3 grid((unsigned)std::max<size_t>(1, std::min<size_t>(block_elems / 8 / 256, 16)), layers * 2);
-  copy_block_kernel<<<grid, 256, 0, s>>>(pool, layers * 2, NB, block_elems, src, dst);
-  return cudaGetLastError();
+  return launch_k(copy_block_kernel, grid, dim3(256), 0, s, pool, layers * 2, NB, block_elems, src, dst);
 }
 
 }  // namespace kc

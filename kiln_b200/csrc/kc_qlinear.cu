@@ -228,6 +228,18 @@ __device__ __forceinline__ void umma_bf16_ss(uint32_t tmem_d, uint64_t desc_a, u
       ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Same instruction with the two shared-memory descriptors given as (low word, shared high word).
+__device__ __forceinline__ void umma_bf16_ss2(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t d_hi,
+                                              uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %3};\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
+      ::"r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(d_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                    smem_u32(bar))
@@ -276,7 +288,6 @@ struct QlKernelParams {
   bf16* y; int ldy;
   float* partial;
   uint32_t* status;
-  int dbg;   // experiment switches (KC_QL_DEBUG), 0 in normal operation
 };
 
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -293,8 +304,11 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 
 // TEMPORARY instrumentation (KC_QL_DEBUG & 256): per-CTA phase timestamps.
-__device__ unsigned long long g_ql_trace[1024 * 32];
-#define TR(k) do { if (p.dbg & 256) g_ql_trace[(blockIdx.y * gridDim.x + blockIdx.x) * 32 + (k)] = (k) == 0 || (k) == 9 ? globaltimer_ns() : (unsigned long long)clock64(); } while (0)
+__device__ unsigned long long g_ql_trace[1024 * 48];
+#ifndef KC_QL_TRACE
+#define KC_QL_TRACE 0
+#endif
+#define TR(k) do { if (KC_QL_TRACE) g_ql_trace[(blockIdx.y * gridDim.x + blockIdx.x) * 48 + (k)] = (k) == 0 || (k) == 9 ? globaltimer_ns() : (unsigned long long)clock64(); } while (0)
 
 // BITS: 4 or 8. GPK: scale/bias pairs per row per k-block (1 or 2). NT: 128-row weight tiles per CTA, all
 // multiplied against the same activation k-block (NT * m_pad TMEM columns), which divides the activation
@@ -335,6 +349,7 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
   const int kb0 = split * p.kb_per_split;
   const int nkb = p.kb_per_split;
 
+  pdl_launch_dependents();
   if (threadIdx.x == 0) { TR(0); TR(1); }
   if (threadIdx.x == 0) {
     for (int i = 0; i < RS; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], QL_DQ_GROUP_WARPS); }
@@ -370,14 +385,14 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
       }
     }
   } else if (warp == 1) {
-    // ---- activation producer ----
+    // ---- activation producer: the first access of this kernel to memory written by earlier kernels ----
     if (lane == 0) {
+      pdl_wait();
       const int n64 = p.m_pad / 64, n16 = (p.m_pad % 64) / 16;
       RingPos ap;
       for (int i = 0; i < nkb; ++i, ap.advance(AS)) {
         const int as = ap.stage; const uint32_t ph = ap.phase;
         if (!mbar_wait(&ab_empty[as], ph ^ 1, p.status, KC_DEV_QLINEAR | 2)) break;
-        if (p.dbg & 2) { mbar_arrive(&b_full[as]); continue; }
         if (i == 8) TR(20);
         mbar_arrive_expect_tx(&b_full[as], b_bytes);
         uint8_t* dst = sB + (size_t)as * b_bytes;
@@ -388,38 +403,49 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
       }
     }
   } else if (warp == 2) {
-    // ---- MMA issuer ----
+    // ---- MMA issuer: one thread; its per-k-block instruction count is the serial part of the pipeline, so
+    //      descriptors are kept as 32-bit halves (only the 14-bit start-address field changes) ----
     if (lane == 0) {
       const int n0 = p.m_pad > 256 ? 256 : p.m_pad;
       const int n1 = p.m_pad - n0;   // a second accumulator only when NT == 1 and m_pad > 256
       const uint32_t idesc0 = umma_idesc_bf16(QL_TILE_N, n0);
       const uint32_t idesc1 = n1 ? umma_idesc_bf16(QL_TILE_N, n1) : 0;
       const uint32_t col_stride = (uint32_t)(p.m_pad + 31) & ~31u;   // accumulators start on 32-column boundaries
-      bool ok = true;
+      const uint64_t proto = umma_smem_desc_sw128(0);
+      const uint32_t d_hi = (uint32_t)(proto >> 32), d_lo = (uint32_t)proto;
+      const uint32_t a_lo0 = d_lo | ((smem_u32(sA) >> 4) & 0x3FFF), b_lo0 = d_lo | ((smem_u32(sB) >> 4) & 0x3FFF);
+      const uint32_t a_step = a_stage >> 4, b_step = b_bytes >> 4;
+      uint32_t acc = 0;
       RingPos ap;
-      for (int i = 0; i < nkb && ok; ++i, ap.advance(AS)) {
+      // The barrier tests for k-block i + 1 are issued before the MMAs of k-block i and read after them, so
+      // their latency hides behind the issue of the current k-block instead of idling the tensor pipe.
+      bool a_ok = mbar_test_wait(&a_ready[0], 0), b_ok = mbar_test_wait(&b_full[0], 0);
+      for (int i = 0; i < nkb; ++i) {
         const int as = ap.stage; const uint32_t ph = ap.phase;
-        ok = mbar_wait(&a_ready[as], ph, p.status, KC_DEV_QLINEAR | 3);
+        if (!a_ok && !mbar_wait(&a_ready[as], ph, p.status, KC_DEV_QLINEAR | 3)) break;
         if (i == 8) TR(18);
-        ok = ok && mbar_wait(&b_full[as], ph, p.status, KC_DEV_QLINEAR | 4);
-        if (!ok) break;
+        if (!b_ok && !mbar_wait(&b_full[as], ph, p.status, KC_DEV_QLINEAR | 4)) break;
         if (i == 8) TR(21);
         if (i == 0) TR(4);
         tc_fence_after();
-        const uint64_t db = umma_smem_desc_sw128(smem_u32(sB + (size_t)as * b_bytes));
+        const uint32_t a_lo = a_lo0 + as * a_step, b_lo = b_lo0 + as * b_step;
+        ap.advance(AS);
+        if (i + 1 < nkb) { a_ok = mbar_test_wait(&a_ready[ap.stage], ap.phase); b_ok = mbar_test_wait(&b_full[ap.stage], ap.phase); }
 #pragma unroll
         for (int t = 0; t < NT; ++t) {
-          if (t < nt_live && !(p.dbg & 4)) {
-            const uint64_t da = umma_smem_desc_sw128(smem_u32(sA + (size_t)as * a_stage + (size_t)t * QL_A_BYTES));
+          if (t < nt_live) {
 #pragma unroll
             for (int ks = 0; ks < QL_KB / 16; ++ks) {
-              const uint32_t acc = (i > 0 || ks > 0) ? 1u : 0u;
               // advancing K by 16 bf16 = 32 bytes inside the swizzle row: +2 in the address field
-              umma_bf16_ss(tmem_base + t * col_stride, da + 2 * ks, db + 2 * ks, idesc0, acc);
-              if (NT == 1 && n1) umma_bf16_ss(tmem_base + 256, da + 2 * ks, db + (256 * 128 >> 4) + 2 * ks, idesc1, acc);
+              umma_bf16_ss2(tmem_base + t * col_stride, a_lo + t * (QL_A_BYTES >> 4) + 2 * ks, b_lo + 2 * ks, d_hi, idesc0,
+                            ks == 0 ? acc : 1u);
+              if (NT == 1 && n1)
+                umma_bf16_ss2(tmem_base + 256, a_lo + 2 * ks, b_lo + (256 * 128 >> 4) + 2 * ks, d_hi, idesc1, ks == 0 ? acc : 1u);
+              if (i == 8 && t < 2) TR(26 + t * 4 + ks);
             }
           }
         }
+        acc = 1u;
         umma_commit(&ab_empty[as]);
         if (i == 8) TR(19);
         if (i >= 4 && i <= 7) TR(18 + i);   // 22..25: commits of k-blocks 4..7
@@ -460,7 +486,7 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
       if (i == grp && tg == 0 && grp == 0) TR(3);
 #pragma unroll
       for (int t = 0; t < NT; ++t) {
-        if (t < nt_live && !(p.dbg & 1)) {
+        if (t < nt_live) {
           const uint8_t* rec = sR + (size_t)rs * r_stage + (size_t)t * p.raw_stride;
           uint8_t* a = sA + (size_t)as * a_stage + (size_t)t * QL_A_BYTES;
 #pragma unroll
@@ -490,9 +516,10 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
     }
     // ---- epilogue: TMEM -> per-warp transpose in shared memory -> row-contiguous vector stores ----
     if (td == 0) TR(10);
+    pdl_wait();   // the stores below may overwrite what an earlier kernel still reads
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(acc_full, 0, p.status, KC_DEV_QLINEAR | 7));
     if (td == 0) TR(6);
-    if (ok && !(p.dbg & 64)) {
+    if (ok) {
       tc_fence_after();
       // every MMA has completed and every copy into the rings has been consumed: the ring memory is free
       float* stage = reinterpret_cast<float*>(smem + (size_t)(warp - QL_DQ_WARP0) * QL_EPI_STAGE_BYTES);
@@ -580,8 +607,7 @@ static cudaError_t launch_umma(const QLinearLaunch& l, QlKernelParams& p, cudaSt
     configured = true;
   }
   dim3 grid((w.n_tiles + NT - 1) / NT, w.splits);
-  qlinear_umma_kernel<BITS, GPK, NT><<<grid, QL_THREADS, smem, s>>>(l.x->map16, l.x->map64, p);
-  return cudaGetLastError();
+  return launch_k(qlinear_umma_kernel<BITS, GPK, NT>, grid, dim3(QL_THREADS), smem, s, l.x->map16, l.x->map64, p);
 }
 
 template <int BITS, int GPK>
@@ -612,9 +638,7 @@ cudaError_t qlinear_umma(const QLinearLaunch& l, cudaStream_t s) {
   p.splits = w.splits; p.kb_per_split = w.kblocks / w.splits;
   p.raw_stride = (w.record_bytes + 127) & ~127u;
   p.y = l.y; p.ldy = l.ldy; p.partial = l.partial; p.status = l.status;
-  static const int env_dbg = getenv("KC_QL_DEBUG") ? atoi(getenv("KC_QL_DEBUG")) : 0;
   static const int env_nt = getenv("KC_QL_NT") ? atoi(getenv("KC_QL_NT")) : 0;
-  p.dbg = env_dbg;
   int nt = plan_tiles_per_cta(w, p.m_pad, w.sm_count);
   if (env_nt) nt = std::min(env_nt, p.m_pad <= 128 ? 4 : (p.m_pad <= 256 ? 2 : 1));
   if (w.bits == 4) return w.gpk == 2 ? launch_umma_nt<4, 2>(l, p, nt, s) : launch_umma_nt<4, 1>(l, p, nt, s);
@@ -627,6 +651,8 @@ cudaError_t qlinear_umma(const QLinearLaunch& l, cudaStream_t s) {
 
 __global__ void qlinear_reduce_kernel(const float* __restrict__ partial, int splits, int M, int N,
                                       bf16* __restrict__ y, int ldy) {
+  pdl_launch_dependents();
+  pdl_wait();
   const long long total = (long long)M * N / 2;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
@@ -646,8 +672,7 @@ cudaError_t qlinear_reduce_splits(const float* partial, int splits, int M, int N
   const long long total = (long long)M * N / 2;
   const int threads = 256;
   const int blocks = (int)std::min<long long>((total + threads - 1) / threads, 148LL * 8);
-  qlinear_reduce_kernel<<<blocks, threads, 0, s>>>(partial, splits, M, N, y, ldy);
-  return cudaGetLastError();
+  return launch_k(qlinear_reduce_kernel, dim3(blocks), dim3(threads), 0, s, partial, splits, M, N, y, ldy);
 }
 
 }  // namespace kc

@@ -21,6 +21,8 @@ __device__ __forceinline__ ArgMax better(ArgMax a, ArgMax b) {
 // normalize == 0: argmax of the raw row (crates/kiln-models/src/draft.rs:379-381).
 __global__ void __launch_bounds__(1024)
 greedy_rows_kernel(const bf16* __restrict__ logits, int vocab, int normalize, uint32_t* __restrict__ tokens) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float red_m[32], red_s[32];
   __shared__ ArgMax red_a[32];
   __shared__ float s_lse;
@@ -90,6 +92,8 @@ __global__ void verify_accept_kernel(const uint32_t* __restrict__ row_tokens, co
                                      const int32_t* __restrict__ draft_len, int n_seqs, int max_commit,
                                      uint32_t* __restrict__ committed, int32_t* __restrict__ n_committed,
                                      int32_t* __restrict__ n_accepted) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n_seqs) return;
   const int dl = draft_len[i];
@@ -114,18 +118,15 @@ __global__ void verify_accept_kernel(const uint32_t* __restrict__ row_tokens, co
 cudaError_t launch_greedy_rows(const bf16* logits, int rows, int vocab, int normalize, uint32_t* tokens,
                                cudaStream_t s) {
   if (rows <= 0) return cudaSuccess;
-  greedy_rows_kernel<<<rows, 1024, 0, s>>>(logits, vocab, normalize, tokens);
-  return cudaGetLastError();
+  return launch_k(greedy_rows_kernel, dim3(rows), dim3(1024), 0, s, logits, vocab, normalize, tokens);
 }
 
 cudaError_t launch_verify_accept(const uint32_t* row_tokens, const int32_t* seq_row_offsets, const uint32_t* draft,
                                  const int32_t* draft_offsets, const int32_t* draft_len, int n_seqs, int max_commit,
                                  uint32_t* committed, int32_t* n_committed, int32_t* n_accepted, cudaStream_t s) {
   if (n_seqs <= 0) return cudaSuccess;
-  verify_accept_kernel<<<(n_seqs + 127) / 128, 128, 0, s>>>(row_tokens, seq_row_offsets, draft, draft_offsets,
-                                                            draft_len, n_seqs, max_commit, committed, n_committed,
-                                                            n_accepted);
-  return cudaGetLastError();
+  return launch_k(verify_accept_kernel, dim3((n_seqs + 127) / 128), dim3(128), 0, s, row_tokens, seq_row_offsets, draft,
+                  draft_offsets, draft_len, n_seqs, max_commit, committed, n_committed, n_accepted);
 }
 
 }  // namespace kc
