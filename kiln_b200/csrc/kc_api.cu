@@ -966,6 +966,7 @@ AttnParams attn_params(kc_model* m, kc_kv* kv, const StepPlan& p, int layer, con
   a.layer = layer; a.NB = kv->num_blocks; a.BS = kv->block_size;
   a.max_chunks = p.max_chunks; a.chunk_lo_grid = 0;
   a.scale = scale; a.softcap = softcap; a.window = window;
+  a.pool = kv->pool;
   return a;
 }
 

@@ -26,6 +26,7 @@ struct AttnParams {
   float scale;                 // softmax scale (applied to fp32 scores)
   float softcap;               // 0 = off
   int window;                  // 0 = global
+  const bf16* pool;            // K/V pools: [layers][2][NB][Hkv][BS][head_dim]
 };
 
 // Tokens of one sequence that share a CTA (their rows x gqa must fit 64 rows).

@@ -301,7 +301,10 @@ __global__ void copy_block_kernel(bf16* __restrict__ pool, int planes, int NB, s
 
 cudaError_t launch_embed(const uint32_t* w, const bf16* scales, const bf16* biases, const uint32_t* ids, int n, int H,
                          int bits, int group, float embed_scale, int vocab, bf16* out, cudaStream_t s) {
-  return launch_k(embed_kernel, dim3(n), dim3(256), 0, s, w, scales, biases, ids, H, bits, group, embed_scale, vocab, out);
+  // The first kernel of a step follows the copy of the step's metadata: it is launched with plain stream order so
+  // that its dependency on that copy is the ordinary one; the kernels after it chain from it.
+  embed_kernel<<<n, 256, 0, s>>>(w, scales, biases, ids, H, bits, group, embed_scale, vocab, out);
+  return cudaGetLastError();
 }
 
 static RowSource row_source(const SublayerOut& y) {

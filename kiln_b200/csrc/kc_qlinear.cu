@@ -32,14 +32,19 @@ __global__ void qweight_retile_kernel(uint8_t* __restrict__ records, const uint3
   const int words_per_rec = QL_TILE_N * words_per_row_kb;
   const int sb_per_rec = QL_TILE_N * gpk;
   const long long per_rec = words_per_rec + sb_per_rec;
-  const long long total = (long long)n_tiles * kblocks * per_rec;
+  const long long total = (long long)((n_tiles + QL_TILE_GROUP - 1) / QL_TILE_GROUP) * QL_TILE_GROUP * kblocks * per_rec;
   const int src_words_per_row = K * bits / 32;
   const int groups_per_row = K / group;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
     const long long rec = i / per_rec;
     const int e = (int)(i % per_rec);
-    const int tile = (int)(rec / kblocks), kb = (int)(rec % kblocks);
+    // record order: [tile group][k-block][tile in group], so the records of 1, 2 or 4 neighbouring tiles for
+    // one k-block are contiguous and one bulk copy fetches them
+    const int tig = (int)(rec % QL_TILE_GROUP);
+    const long long gk = rec / QL_TILE_GROUP;
+    const int kb = (int)(gk % kblocks);
+    const int tile = (int)(gk / kblocks) * QL_TILE_GROUP + tig;
     uint8_t* base = records + rec * (long long)record_bytes;
     if (e < words_per_rec) {
       const int r = e / words_per_row_kb, c = e % words_per_row_kb;
@@ -95,7 +100,7 @@ cudaError_t qweight_build(QWeight* out, const uint32_t* w, const bf16* scales, c
   q.sm_count = sm_count;
   cudaError_t e = cudaMalloc(&q.records, q.bytes());
   if (e != cudaSuccess) return e;
-  const long long total = (long long)q.n_tiles * q.kblocks * (q.record_bytes / 4);
+  const long long total = (long long)(q.bytes() / 4);
   const int threads = 256;
   const int blocks = (int)std::min<long long>((total + threads - 1) / threads, 148LL * 16);
   qweight_retile_kernel<<<blocks, threads, 0, s>>>(q.records, w, scales, biases, N, K, bits, group,
@@ -149,8 +154,19 @@ bool make_tmap_bf16_2d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64
   return true;
 }
 
+// The map whose box covers `m_pad` rows (<= 256), so that one TMA operation brings a whole activation k-block.
+// Re-encoded only when the row count changes (a host-side encode, no device work).
+static const CUtensorMap* act_operand_rows_map(const ActOperand* op, int m_pad) {
+  if (op->rows_map_n != m_pad) {
+    const char* err = "";
+    if (!make_tmap_bf16_2d(&op->rows_map, op->ptr, op->K, op->rows, QL_KB, m_pad, &err)) return nullptr;
+    op->rows_map_n = m_pad;
+  }
+  return &op->rows_map;
+}
+
 bool act_operand_init(ActOperand* op, const bf16* ptr, int rows, int K, const char** err) {
-  op->ptr = ptr; op->rows = rows; op->K = K;
+  op->ptr = ptr; op->rows = rows; op->K = K; op->rows_map_n = 0;
   if (K % QL_KB) { *err = "activation width must be a multiple of 64"; return false; }
   if (!make_tmap_bf16_2d(&op->map16, ptr, K, rows, QL_KB, 16, err)) return false;
   if (!make_tmap_bf16_2d(&op->map64, ptr, K, rows, QL_KB, 64, err)) return false;
@@ -283,7 +299,8 @@ struct QlKernelParams {
   int row0;              // first activation row
   int splits, kb_per_split;
   int a_stages, r_stages;
-  uint32_t raw_stride;   // record_bytes rounded up to 128
+  uint32_t raw_stride;   // distance between the records of neighbouring tiles in a raw stage (= record_bytes)
+  int b_single;          // 1: the first tensor map's box spans all m_pad rows (one TMA operation per k-block)
   uint32_t tmem_cols;    // power of two >= max(32, NT * m_pad)
   bf16* y; int ldy;
   float* partial;
@@ -305,6 +322,9 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 
 // TEMPORARY instrumentation (KC_QL_DEBUG & 256): per-CTA phase timestamps.
 __device__ unsigned long long g_ql_trace[1024 * 48];
+#ifndef KC_QL_LOOP_FENCE
+#define KC_QL_LOOP_FENCE 0
+#endif
 #ifndef KC_QL_TRACE
 #define KC_QL_TRACE 0
 #endif
@@ -316,7 +336,7 @@ __device__ unsigned long long g_ql_trace[1024 * 48];
 // element, never the order in which that element's k-blocks are accumulated.
 //
 // Warp roles: 0 = weight-record producer (bulk copies), 1 = activation producer (TMA), 2 = MMA issuer and
-// TMEM owner, 3 idle, 4..19 = two dequantiser groups of eight warps that take alternate k-blocks (the waits,
+// TMEM owner, 3 = second MMA issuer when the CTA owns several tiles, 4..19 = two dequantiser groups of eight warps that take alternate k-blocks (the waits,
 // the proxy fence and the barrier round trip of one group hide behind the other group's arithmetic), then
 // all sixteen drain TMEM.
 template <int BITS, int GPK, int NT>
@@ -348,13 +368,17 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
   const int nt_live = min(NT, p.n_tiles - tile0);   // tiles this CTA really owns
   const int kb0 = split * p.kb_per_split;
   const int nkb = p.kb_per_split;
+  // MMA issue is split by tile between warps 2 and 3 (independent accumulators, so no ordering between them):
+  // one thread's issue rate, sharing its scheduler with dequantiser warps, does not keep the tensor pipe fed.
+  constexpr int T_SPLIT = (NT + 1) / 2;
+  const int n_issuers = nt_live > T_SPLIT ? 2 : 1;
 
   pdl_launch_dependents();
   if (threadIdx.x == 0) { TR(0); TR(1); }
   if (threadIdx.x == 0) {
     for (int i = 0; i < RS; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], QL_DQ_GROUP_WARPS); }
-    for (int i = 0; i < AS; ++i) { mbar_init(&b_full[i], 1); mbar_init(&a_ready[i], QL_DQ_GROUP_WARPS); mbar_init(&ab_empty[i], 1); }
-    mbar_init(acc_full, 1);
+    for (int i = 0; i < AS; ++i) { mbar_init(&b_full[i], 1); mbar_init(&a_ready[i], QL_DQ_GROUP_WARPS); mbar_init(&ab_empty[i], n_issuers); }
+    mbar_init(acc_full, n_issuers);
     mbar_fence_init();
   }
   if (warp == 2) {
@@ -378,10 +402,11 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
         const int rs = rp.stage; const uint32_t ph = rp.phase;
         if (!mbar_wait(&raw_empty[rs], ph ^ 1, p.status, KC_DEV_QLINEAR | 1)) break;
         if (i == 8) TR(16);
+        // the records of this CTA's tiles for one k-block are neighbours in memory: one copy
         mbar_arrive_expect_tx(&raw_full[rs], p.record_bytes * nt_live);
-        for (int t = 0; t < nt_live; ++t)
-          bulk_g2s(sR + (size_t)rs * r_stage + (size_t)t * p.raw_stride,
-                   p.records + ((size_t)(tile0 + t) * p.kblocks + kb0 + i) * p.record_bytes, p.record_bytes, &raw_full[rs]);
+        bulk_g2s(sR + (size_t)rs * r_stage,
+                 p.records + (((size_t)(tile0 / QL_TILE_GROUP) * p.kblocks + kb0 + i) * QL_TILE_GROUP + tile0 % QL_TILE_GROUP) * p.record_bytes,
+                 p.record_bytes * nt_live, &raw_full[rs]);
       }
     }
   } else if (warp == 1) {
@@ -397,15 +422,20 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
         mbar_arrive_expect_tx(&b_full[as], b_bytes);
         uint8_t* dst = sB + (size_t)as * b_bytes;
         const int x = (kb0 + i) * QL_KB;
-        int row = 0;
-        for (int j = 0; j < n64; ++j, row += 64) tma_load_2d(dst + row * 128, &map64, x, p.row0 + row, &b_full[as]);
-        for (int j = 0; j < n16; ++j, row += 16) tma_load_2d(dst + row * 128, &map16, x, p.row0 + row, &b_full[as]);
+        if (p.b_single) {
+          tma_load_2d(dst, &map16, x, p.row0, &b_full[as]);   // map16 then is the map whose box spans all m_pad rows
+        } else {
+          int row = 0;
+          for (int j = 0; j < n64; ++j, row += 64) tma_load_2d(dst + row * 128, &map64, x, p.row0 + row, &b_full[as]);
+          for (int j = 0; j < n16; ++j, row += 16) tma_load_2d(dst + row * 128, &map16, x, p.row0 + row, &b_full[as]);
+        }
       }
     }
-  } else if (warp == 2) {
-    // ---- MMA issuer: one thread; its per-k-block instruction count is the serial part of the pipeline, so
-    //      descriptors are kept as 32-bit halves (only the 14-bit start-address field changes) ----
-    if (lane == 0) {
+  } else if (warp == 2 || warp == 3) {
+    // ---- MMA issuers: one thread each; the per-k-block instruction count is the serial part of the pipeline,
+    //      so descriptors are kept as 32-bit halves (only the 14-bit start-address field changes) ----
+    const int t_lo = warp == 2 ? 0 : T_SPLIT, t_hi = warp == 2 ? min(T_SPLIT, nt_live) : nt_live;
+    if (lane == 0 && t_lo < t_hi) {
       const int n0 = p.m_pad > 256 ? 256 : p.m_pad;
       const int n1 = p.m_pad - n0;   // a second accumulator only when NT == 1 and m_pad > 256
       const uint32_t idesc0 = umma_idesc_bf16(QL_TILE_N, n0);
@@ -427,13 +457,16 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
         if (!b_ok && !mbar_wait(&b_full[as], ph, p.status, KC_DEV_QLINEAR | 4)) break;
         if (i == 8) TR(21);
         if (i == 0) TR(4);
-        tc_fence_after();
+        // No tcgen05 fence here: the operands are ordinary shared memory made visible to the async proxy by the
+        // writers' proxy fence and the mbarrier hand-off; a tcgen05.fence would only order this batch of MMAs
+        // behind the completion of the previous one.
+        if (KC_QL_LOOP_FENCE) tc_fence_after();
         const uint32_t a_lo = a_lo0 + as * a_step, b_lo = b_lo0 + as * b_step;
         ap.advance(AS);
         if (i + 1 < nkb) { a_ok = mbar_test_wait(&a_ready[ap.stage], ap.phase); b_ok = mbar_test_wait(&b_full[ap.stage], ap.phase); }
 #pragma unroll
         for (int t = 0; t < NT; ++t) {
-          if (t < nt_live) {
+          if (t >= t_lo && t < t_hi) {
 #pragma unroll
             for (int ks = 0; ks < QL_KB / 16; ++ks) {
               // advancing K by 16 bf16 = 32 bytes inside the swizzle row: +2 in the address field
@@ -607,7 +640,15 @@ static cudaError_t launch_umma(const QLinearLaunch& l, QlKernelParams& p, cudaSt
     configured = true;
   }
   dim3 grid((w.n_tiles + NT - 1) / NT, w.splits);
-  return launch_k(qlinear_umma_kernel<BITS, GPK, NT>, grid, dim3(QL_THREADS), smem, s, l.x->map16, l.x->map64, p);
+  const CUtensorMap* first = &l.x->map16;
+  p.b_single = 0;
+  static const bool single_ok = !(getenv("KC_QL_NO_SINGLE"));
+  if (single_ok && p.m_pad <= 256) {
+    first = act_operand_rows_map(l.x, p.m_pad);
+    if (!first) return cudaErrorInvalidValue;
+    p.b_single = 1;
+  }
+  return launch_k(qlinear_umma_kernel<BITS, GPK, NT>, grid, dim3(QL_THREADS), smem, s, *first, l.x->map64, p);
 }
 
 template <int BITS, int GPK>
@@ -636,7 +677,7 @@ cudaError_t qlinear_umma(const QLinearLaunch& l, cudaStream_t s) {
   p.M = l.M; p.m_pad = (l.M + 15) & ~15; p.row0 = l.row0;
   if (l.row0 % 16 || l.row0 + p.m_pad > l.x->rows) return cudaErrorInvalidValue;
   p.splits = w.splits; p.kb_per_split = w.kblocks / w.splits;
-  p.raw_stride = (w.record_bytes + 127) & ~127u;
+  p.raw_stride = w.record_bytes;
   p.y = l.y; p.ldy = l.ldy; p.partial = l.partial; p.status = l.status;
   static const int env_nt = getenv("KC_QL_NT") ? atoi(getenv("KC_QL_NT")) : 0;
   int nt = plan_tiles_per_cta(w, p.m_pad, w.sm_count);

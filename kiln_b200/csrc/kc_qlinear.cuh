@@ -9,7 +9,7 @@
 // needs for one k-block is ONE contiguous, 16-byte aligned run that a single
 // bulk copy brings into shared memory:
 //
-//   record(tile t, kblock kb) = packed[128 rows][64*bits/8 bytes]
+//   record(tile t, kblock kb) = packed[128 rows][64*bits/8 bytes]   (stored in the order [t / 4][kb][t % 4])
 //                             ++ sb[128 rows][gpk] as bf162 (scale, bias)
 //
 // with 128 output rows per tile, 64 input features per k-block and gpk =
@@ -29,6 +29,7 @@ namespace kc {
 constexpr int QL_TILE_N = 128;  // output features per tile = UMMA M
 constexpr int QL_KB = 64;       // input features per k-block = one 128-byte swizzle row of bf16
 constexpr int QL_MAX_M = 512;   // activation rows per launch (TMEM columns)
+constexpr int QL_TILE_GROUP = 4;  // tiles whose records are interleaved per k-block (the most one CTA owns)
 
 struct QWeight {
   uint8_t* records = nullptr;  // [n_tiles][kblocks][record_bytes]
@@ -38,7 +39,7 @@ struct QWeight {
   uint32_t record_bytes = 0;
   int splits = 1;              // fixed function of (N, K): never of M
   int sm_count = 148;
-  size_t bytes() const { return (size_t)n_tiles * kblocks * record_bytes; }
+  size_t bytes() const { return (size_t)((n_tiles + QL_TILE_GROUP - 1) / QL_TILE_GROUP) * QL_TILE_GROUP * kblocks * record_bytes; }
   // Algorithmic bytes of the mlx tensors this weight was built from.
   size_t mlx_bytes() const { return (size_t)N * K * bits / 8 + (size_t)2 * N * (K / group) * 2; }
 };
@@ -52,6 +53,8 @@ struct ActOperand {
   int K = 0;
   CUtensorMap map16;
   CUtensorMap map64;
+  mutable CUtensorMap rows_map;   // box of rows_map_n rows: one TMA operation per k-block while the row count is stable
+  mutable int rows_map_n = 0;
 };
 
 struct QLinearLaunch {
