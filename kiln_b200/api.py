@@ -12,6 +12,7 @@ libkiln_cuda.so. Nothing in this module has a CPU code path.
 from __future__ import annotations
 
 import ctypes as C
+import weakref
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
 
@@ -197,7 +198,13 @@ class Context:
     def __init__(self, device: int = 0):
         self.device = device
         self._h = C.c_void_p()
+        # handles created on this context: closed before the context itself, whatever order the interpreter
+        # drops the Python objects in (a library handle must not outlive its context)
+        self._children = weakref.WeakSet()
         check(L.lib().kc_ctx_create(device, C.byref(self._h)))
+
+    def _adopt(self, child) -> None:
+        self._children.add(child)
 
     def sync(self) -> None:
         check(L.lib().kc_sync(self._h))
@@ -232,6 +239,8 @@ class Context:
 
     def close(self) -> None:
         if self._h:
+            for child in list(self._children):
+                child.close()
             L.lib().kc_ctx_destroy(self._h)
             self._h = C.c_void_p()
 
@@ -267,6 +276,7 @@ class PagedKv:
         self._h = C.c_void_p()
         check(L.lib().kc_kv_create(ctx._h, spec.layers, spec.kv_heads, spec.head_dim, spec.num_blocks,
                                    spec.block_size, L.KC_BF16, C.byref(self._h)))
+        ctx._adopt(self)
 
     def copy_block(self, src: int, dst: int) -> None:
         check(L.lib().kc_kv_copy_block(self._h, src, dst))
@@ -337,6 +347,7 @@ class CudaModel:
         arr, keep = tensor_views(tensors)
         check(L.lib().kc_model_load(ctx._h, C.byref(desc), arr, len(tensors), C.byref(self._h)))
         del keep
+        ctx._adopt(self)
 
     # --- StepModel -----------------------------------------------------------------
     def forward_step(self, batch: StepBatch, kv: PagedKv) -> Optional[torch.Tensor]:
@@ -443,6 +454,7 @@ class QuantizedWeight:
             torch.cuda.synchronize()
         check(L.lib().kc_qweight_create(ctx._h, w.data_ptr(), scales.data_ptr(), biases.data_ptr(), self.out_features,
                                         self.in_features, bits, group_size, on_dev, C.byref(self._h)))
+        ctx._adopt(self)
 
     def matmul(self, x: torch.Tensor) -> torch.Tensor:
         """y = x · dequant(W)ᵀ; x bf16 [m, in] on the device."""

@@ -320,26 +320,20 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// TEMPORARY instrumentation (KC_QL_DEBUG & 256): per-CTA phase timestamps.
-__device__ unsigned long long g_ql_trace[1024 * 48];
-#ifndef KC_QL_LOOP_FENCE
-#define KC_QL_LOOP_FENCE 0
-#endif
-#ifndef KC_QL_TRACE
-#define KC_QL_TRACE 0
-#endif
-#define TR(k) do { if (KC_QL_TRACE) g_ql_trace[(blockIdx.y * gridDim.x + blockIdx.x) * 48 + (k)] = (k) == 0 || (k) == 9 ? globaltimer_ns() : (unsigned long long)clock64(); } while (0)
-
 // BITS: 4 or 8. GPK: scale/bias pairs per row per k-block (1 or 2). NT: 128-row weight tiles per CTA, all
 // multiplied against the same activation k-block (NT * m_pad TMEM columns), which divides the activation
 // traffic from L2 by NT. NT is free to depend on the row count: it changes which CTA computes an output
 // element, never the order in which that element's k-blocks are accumulated.
 //
+// KC: 64-feature k-blocks per pipeline stage (1 or 2). The per-stage cost of the MMA issuer and of the barrier
+// hand-offs does not depend on how much a stage holds, so a CTA with a single tile (NT == 1) takes two k-blocks per
+// stage; they are multiplied in ascending k order into the same accumulator, so no bit changes.
+//
 // Warp roles: 0 = weight-record producer (bulk copies), 1 = activation producer (TMA), 2 = MMA issuer and
 // TMEM owner, 3 = second MMA issuer when the CTA owns several tiles, 4..19 = two dequantiser groups of eight warps that take alternate k-blocks (the waits,
 // the proxy fence and the barrier round trip of one group hide behind the other group's arithmetic), then
 // all sixteen drain TMEM.
-template <int BITS, int GPK, int NT>
+template <int BITS, int GPK, int NT, int KC>
 __global__ void __launch_bounds__(QL_THREADS, 1)
 qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_constant__ CUtensorMap map64,
                     const QlKernelParams p) {
@@ -349,11 +343,14 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int AS = p.a_stages, RS = p.r_stages;
   const uint32_t b_bytes = (uint32_t)p.m_pad * 128u;
-  const uint32_t a_stage = NT * QL_A_BYTES;
-  const uint32_t r_stage = NT * p.raw_stride;
+  constexpr int UNITS = NT * KC;                      // (k-block, tile) units of one stage, k-block major
+  const uint32_t a_stage = UNITS * QL_A_BYTES;
+  const uint32_t bk_bytes = b_bytes;                   // one activation k-block
+  const uint32_t b_stage = KC * bk_bytes;
+  const uint32_t r_stage = UNITS * p.raw_stride;
   uint8_t* sA = smem;
   uint8_t* sB = sA + (size_t)AS * a_stage;
-  uint8_t* sR = sB + (size_t)AS * b_bytes;
+  uint8_t* sR = sB + (size_t)AS * b_stage;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sR + (size_t)RS * r_stage);
   uint64_t* raw_full = bars;
   uint64_t* raw_empty = raw_full + RS;
@@ -367,14 +364,13 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
   const int tile0 = blockIdx.x * NT, split = blockIdx.y;
   const int nt_live = min(NT, p.n_tiles - tile0);   // tiles this CTA really owns
   const int kb0 = split * p.kb_per_split;
-  const int nkb = p.kb_per_split;
+  const int nkb = p.kb_per_split / KC;                 // pipeline iterations (stages) of this CTA
   // MMA issue is split by tile between warps 2 and 3 (independent accumulators, so no ordering between them):
   // one thread's issue rate, sharing its scheduler with dequantiser warps, does not keep the tensor pipe fed.
   constexpr int T_SPLIT = (NT + 1) / 2;
   const int n_issuers = nt_live > T_SPLIT ? 2 : 1;
 
   pdl_launch_dependents();
-  if (threadIdx.x == 0) { TR(0); TR(1); }
   if (threadIdx.x == 0) {
     for (int i = 0; i < RS; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], QL_DQ_GROUP_WARPS); }
     for (int i = 0; i < AS; ++i) { mbar_init(&b_full[i], 1); mbar_init(&a_ready[i], QL_DQ_GROUP_WARPS); mbar_init(&ab_empty[i], n_issuers); }
@@ -392,7 +388,6 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  if (threadIdx.x == 0) TR(2);
 
   if (warp == 0) {
     // ---- weight record producer: one bulk copy per owned tile per k-block ----
@@ -401,12 +396,13 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
       for (int i = 0; i < nkb; ++i, rp.advance(RS)) {
         const int rs = rp.stage; const uint32_t ph = rp.phase;
         if (!mbar_wait(&raw_empty[rs], ph ^ 1, p.status, KC_DEV_QLINEAR | 1)) break;
-        if (i == 8) TR(16);
-        // the records of this CTA's tiles for one k-block are neighbours in memory: one copy
-        mbar_arrive_expect_tx(&raw_full[rs], p.record_bytes * nt_live);
-        bulk_g2s(sR + (size_t)rs * r_stage,
-                 p.records + (((size_t)(tile0 / QL_TILE_GROUP) * p.kblocks + kb0 + i) * QL_TILE_GROUP + tile0 % QL_TILE_GROUP) * p.record_bytes,
-                 p.record_bytes * nt_live, &raw_full[rs]);
+        // the records of this CTA's tiles for one k-block are neighbours in memory: one copy per k-block
+        mbar_arrive_expect_tx(&raw_full[rs], p.record_bytes * nt_live * KC);
+#pragma unroll
+        for (int kc = 0; kc < KC; ++kc)
+          bulk_g2s(sR + (size_t)rs * r_stage + (size_t)kc * NT * p.raw_stride,
+                   p.records + (((size_t)(tile0 / QL_TILE_GROUP) * p.kblocks + kb0 + i * KC + kc) * QL_TILE_GROUP + tile0 % QL_TILE_GROUP) * p.record_bytes,
+                   p.record_bytes * nt_live, &raw_full[rs]);
       }
     }
   } else if (warp == 1) {
@@ -418,16 +414,18 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
       for (int i = 0; i < nkb; ++i, ap.advance(AS)) {
         const int as = ap.stage; const uint32_t ph = ap.phase;
         if (!mbar_wait(&ab_empty[as], ph ^ 1, p.status, KC_DEV_QLINEAR | 2)) break;
-        if (i == 8) TR(20);
-        mbar_arrive_expect_tx(&b_full[as], b_bytes);
-        uint8_t* dst = sB + (size_t)as * b_bytes;
-        const int x = (kb0 + i) * QL_KB;
-        if (p.b_single) {
-          tma_load_2d(dst, &map16, x, p.row0, &b_full[as]);   // map16 then is the map whose box spans all m_pad rows
-        } else {
-          int row = 0;
-          for (int j = 0; j < n64; ++j, row += 64) tma_load_2d(dst + row * 128, &map64, x, p.row0 + row, &b_full[as]);
-          for (int j = 0; j < n16; ++j, row += 16) tma_load_2d(dst + row * 128, &map16, x, p.row0 + row, &b_full[as]);
+        mbar_arrive_expect_tx(&b_full[as], b_stage);
+#pragma unroll
+        for (int kc = 0; kc < KC; ++kc) {
+          uint8_t* dst = sB + (size_t)as * b_stage + (size_t)kc * bk_bytes;
+          const int x = (kb0 + i * KC + kc) * QL_KB;
+          if (p.b_single) {
+            tma_load_2d(dst, &map16, x, p.row0, &b_full[as]);   // map16 then is the map whose box spans all m_pad rows
+          } else {
+            int row = 0;
+            for (int j = 0; j < n64; ++j, row += 64) tma_load_2d(dst + row * 128, &map64, x, p.row0 + row, &b_full[as]);
+            for (int j = 0; j < n16; ++j, row += 16) tma_load_2d(dst + row * 128, &map16, x, p.row0 + row, &b_full[as]);
+          }
         }
       }
     }
@@ -444,7 +442,7 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
       const uint64_t proto = umma_smem_desc_sw128(0);
       const uint32_t d_hi = (uint32_t)(proto >> 32), d_lo = (uint32_t)proto;
       const uint32_t a_lo0 = d_lo | ((smem_u32(sA) >> 4) & 0x3FFF), b_lo0 = d_lo | ((smem_u32(sB) >> 4) & 0x3FFF);
-      const uint32_t a_step = a_stage >> 4, b_step = b_bytes >> 4;
+      const uint32_t a_step = a_stage >> 4, b_step = b_stage >> 4;
       uint32_t acc = 0;
       RingPos ap;
       // The barrier tests for k-block i + 1 are issued before the MMAs of k-block i and read after them, so
@@ -453,38 +451,34 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
       for (int i = 0; i < nkb; ++i) {
         const int as = ap.stage; const uint32_t ph = ap.phase;
         if (!a_ok && !mbar_wait(&a_ready[as], ph, p.status, KC_DEV_QLINEAR | 3)) break;
-        if (i == 8) TR(18);
         if (!b_ok && !mbar_wait(&b_full[as], ph, p.status, KC_DEV_QLINEAR | 4)) break;
-        if (i == 8) TR(21);
-        if (i == 0) TR(4);
         // No tcgen05 fence here: the operands are ordinary shared memory made visible to the async proxy by the
         // writers' proxy fence and the mbarrier hand-off; a tcgen05.fence would only order this batch of MMAs
         // behind the completion of the previous one.
-        if (KC_QL_LOOP_FENCE) tc_fence_after();
         const uint32_t a_lo = a_lo0 + as * a_step, b_lo = b_lo0 + as * b_step;
         ap.advance(AS);
         if (i + 1 < nkb) { a_ok = mbar_test_wait(&a_ready[ap.stage], ap.phase); b_ok = mbar_test_wait(&b_full[ap.stage], ap.phase); }
 #pragma unroll
-        for (int t = 0; t < NT; ++t) {
-          if (t >= t_lo && t < t_hi) {
+        for (int kc = 0; kc < KC; ++kc) {
+          const uint32_t b_kc = b_lo + kc * (bk_bytes >> 4);
 #pragma unroll
-            for (int ks = 0; ks < QL_KB / 16; ++ks) {
-              // advancing K by 16 bf16 = 32 bytes inside the swizzle row: +2 in the address field
-              umma_bf16_ss2(tmem_base + t * col_stride, a_lo + t * (QL_A_BYTES >> 4) + 2 * ks, b_lo + 2 * ks, d_hi, idesc0,
-                            ks == 0 ? acc : 1u);
-              if (NT == 1 && n1)
-                umma_bf16_ss2(tmem_base + 256, a_lo + 2 * ks, b_lo + (256 * 128 >> 4) + 2 * ks, d_hi, idesc1, ks == 0 ? acc : 1u);
-              if (i == 8 && t < 2) TR(26 + t * 4 + ks);
+          for (int t = 0; t < NT; ++t) {
+            if (t >= t_lo && t < t_hi) {
+              const uint32_t a_u = a_lo + (kc * NT + t) * (QL_A_BYTES >> 4);
+#pragma unroll
+              for (int ks = 0; ks < QL_KB / 16; ++ks) {
+                // advancing K by 16 bf16 = 32 bytes inside the swizzle row: +2 in the address field
+                umma_bf16_ss2(tmem_base + t * col_stride, a_u + 2 * ks, b_kc + 2 * ks, d_hi, idesc0, ks == 0 ? acc : 1u);
+                if (NT == 1 && n1)
+                  umma_bf16_ss2(tmem_base + 256, a_u + 2 * ks, b_kc + (256 * 128 >> 4) + 2 * ks, d_hi, idesc1, ks == 0 ? acc : 1u);
+              }
             }
           }
+          acc = 1u;
         }
-        acc = 1u;
         umma_commit(&ab_empty[as]);
-        if (i == 8) TR(19);
-        if (i >= 4 && i <= 7) TR(18 + i);   // 22..25: commits of k-blocks 4..7
       }
       umma_commit(acc_full);
-      TR(5);
     }
   } else if (warp >= QL_DQ_WARP0) {
     // ---- dequantisers: thread = (row pair r0 / r0 + 64, chunk pair 2c', 2c' + 1) of every owned tile ----
@@ -509,19 +503,15 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
     for (int i = grp; i < nkb && ok; i += QL_DQ_GROUPS) {
       const int rs = rp.stage; const uint32_t rph = rp.phase;
       const int as = ap.stage; const uint32_t aph = ap.phase;
-      if (i == 8 && td == 0) TR(11);
       ok = __all_sync(0xffffffffu, mbar_wait(&raw_full[rs], rph, p.status, KC_DEV_QLINEAR | 5));
       if (!ok) break;
-      if (i == 8 && td == 0) TR(17);
       ok = __all_sync(0xffffffffu, mbar_wait(&ab_empty[as], aph ^ 1, p.status, KC_DEV_QLINEAR | 6));
       if (!ok) break;
-      if (i == 8 && td == 0) TR(12);
-      if (i == grp && tg == 0 && grp == 0) TR(3);
 #pragma unroll
-      for (int t = 0; t < NT; ++t) {
-        if (t < nt_live) {
-          const uint8_t* rec = sR + (size_t)rs * r_stage + (size_t)t * p.raw_stride;
-          uint8_t* a = sA + (size_t)as * a_stage + (size_t)t * QL_A_BYTES;
+      for (int u = 0; u < UNITS; ++u) {
+        if ((u % NT) < nt_live) {
+          const uint8_t* rec = sR + (size_t)rs * r_stage + (size_t)u * p.raw_stride;
+          uint8_t* a = sA + (size_t)as * a_stage + (size_t)u * QL_A_BYTES;
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
             const bf162 sb = *reinterpret_cast<const bf162*>(rec + sb_off[h]);
@@ -538,20 +528,15 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
           }
         }
       }
-      if (i == 8 && td == 0) TR(13);
       fence_proxy_async_smem();
-      if (i == 8 && td == 0) TR(14);
       __syncwarp();
       if (lane == 0) { mbar_arrive(&raw_empty[rs]); mbar_arrive(&a_ready[as]); }
-      if (i == 8 && td == 0) TR(15);
 #pragma unroll
       for (int g = 0; g < QL_DQ_GROUPS; ++g) { rp.advance(RS); ap.advance(AS); }
     }
     // ---- epilogue: TMEM -> per-warp transpose in shared memory -> row-contiguous vector stores ----
-    if (td == 0) TR(10);
     pdl_wait();   // the stores below may overwrite what an earlier kernel still reads
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(acc_full, 0, p.status, KC_DEV_QLINEAR | 7));
-    if (td == 0) TR(6);
     if (ok) {
       tc_fence_after();
       // every MMA has completed and every copy into the rings has been consumed: the ring memory is free
@@ -600,11 +585,9 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
       }
     }
   }
-  if (threadIdx.x == QL_DQ_WARP0 * 32) TR(7);
   __syncwarp();
   tc_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0) { TR(8); TR(9); }
   if (warp == 2) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(p.tmem_cols)
@@ -612,7 +595,7 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
   }
 }
 
-template <int BITS, int GPK, int NT>
+template <int BITS, int GPK, int NT, int KC>
 static cudaError_t launch_umma(const QLinearLaunch& l, QlKernelParams& p, cudaStream_t s) {
   const QWeight& w = *l.w;
   uint32_t cols = 32;
@@ -621,12 +604,12 @@ static cudaError_t launch_umma(const QLinearLaunch& l, QlKernelParams& p, cudaSt
   // Shared memory plan: the A+B ring first (2..4 stages), what is left goes to the raw-record ring.
   static const int env_kb = getenv("KC_QL_SMEM_KB") ? atoi(getenv("KC_QL_SMEM_KB")) : 212;
   const size_t budget = (size_t)env_kb * 1024;
-  const size_t ab = (size_t)NT * QL_A_BYTES + (size_t)p.m_pad * 128;
-  const size_t rstage = (size_t)NT * p.raw_stride;
+  const size_t ab = (size_t)KC * ((size_t)NT * QL_A_BYTES + (size_t)p.m_pad * 128);
+  const size_t rstage = (size_t)KC * NT * p.raw_stride;
   static const int env_as = getenv("KC_QL_AS") ? atoi(getenv("KC_QL_AS")) : 4;
   int as = (int)std::min<size_t>(env_as, (budget - 3 * rstage) / ab);
   if (as < 2) as = 2;
-  as = std::min(as, std::max(2, p.kb_per_split));
+  as = std::min(as, std::max(2, p.kb_per_split / KC));
   const size_t left = budget > (size_t)as * ab ? budget - (size_t)as * ab : 0;
   int rs = (int)std::min<size_t>(24, left / rstage);
   if (rs < 2) rs = 2;
@@ -635,7 +618,7 @@ static cudaError_t launch_umma(const QLinearLaunch& l, QlKernelParams& p, cudaSt
   if (smem > 227 * 1024) return cudaErrorInvalidValue;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(qlinear_umma_kernel<BITS, GPK, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(qlinear_umma_kernel<BITS, GPK, NT, KC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return e;
     configured = true;
   }
@@ -648,16 +631,22 @@ static cudaError_t launch_umma(const QLinearLaunch& l, QlKernelParams& p, cudaSt
     if (!first) return cudaErrorInvalidValue;
     p.b_single = 1;
   }
-  return launch_k(qlinear_umma_kernel<BITS, GPK, NT>, grid, dim3(QL_THREADS), smem, s, *first, l.x->map64, p);
+  return launch_k(qlinear_umma_kernel<BITS, GPK, NT, KC>, grid, dim3(QL_THREADS), smem, s, *first, l.x->map64, p);
 }
 
 template <int BITS, int GPK>
 static cudaError_t launch_umma_nt(const QLinearLaunch& l, QlKernelParams& p, int nt, cudaStream_t s) {
   switch (nt) {
-    case 4: return launch_umma<BITS, GPK, 4>(l, p, s);
-    case 2: return launch_umma<BITS, GPK, 2>(l, p, s);
-    default: return launch_umma<BITS, GPK, 1>(l, p, s);
+    case 4: return launch_umma<BITS, GPK, 4, 1>(l, p, s);
+    case 2: return launch_umma<BITS, GPK, 2, 1>(l, p, s);
+    default: break;
   }
+  // one tile per CTA: two k-blocks per stage when the split holds an even number of them and two such stages fit
+  static const bool kc2_ok = !getenv("KC_QL_NO_KC2");
+  const size_t ab2 = 2 * ((size_t)QL_A_BYTES + (size_t)p.m_pad * 128);
+  if (kc2_ok && p.kb_per_split % 2 == 0 && p.kb_per_split >= 4 && 2 * ab2 + 3 * 2 * p.raw_stride <= 212 * 1024)
+    return launch_umma<BITS, GPK, 1, 2>(l, p, s);
+  return launch_umma<BITS, GPK, 1, 1>(l, p, s);
 }
 
 // Weight tiles per CTA: as many as TMEM holds for this row count, but never so many that the grid drops
@@ -718,7 +707,3 @@ cudaError_t qlinear_reduce_splits(const float* partial, int splits, int M, int N
 
 }  // namespace kc
 
-// TEMPORARY: copies the per-CTA phase trace to the host.
-extern "C" __attribute__((visibility("default"))) int kc_debug_ql_trace(unsigned long long* out, int n) {
-  return (int)cudaMemcpyFromSymbol(out, kc::g_ql_trace, sizeof(unsigned long long) * n);
-}

@@ -6,6 +6,11 @@ namespace kc {
 namespace {
 
 struct ArgMax { float v; int i; };
+__device__ __forceinline__ void load8_bf16(const bf16* p, float (&v)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const float2 a = unpack_bf162(u.x), b = unpack_bf162(u.y), c = unpack_bf162(u.z), d = unpack_bf162(u.w);
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
+}
 __device__ __forceinline__ ArgMax better(ArgMax a, ArgMax b) {
   // larger value wins; on equal values the lower index wins (MLX argmax tie-break as
   // observed in docs/decisions/0004-golden-parity-device-scope-and-dtype-aware-delta.md:53-56)
@@ -28,12 +33,27 @@ greedy_rows_kernel(const bf16* __restrict__ logits, int vocab, int normalize, ui
   __shared__ float s_lse;
   const bf16* row = logits + (size_t)blockIdx.x * vocab;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  const bool vec = (vocab & 7) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0;   // rows start on 16-byte boundaries
   if (normalize) {
     float m = -INFINITY, s = 0.f;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-      const float x = __bfloat162float(row[i]);
-      if (x > m) { s = s * __expf(m - x) + 1.f; m = x; }
-      else s += __expf(x - m);
+    if (vec) {
+      // 8 logits per 16-byte load; the running (max, sum) is rescaled once per vector
+      for (int i = threadIdx.x * 8; i < vocab; i += blockDim.x * 8) {
+        float x[8];
+        load8_bf16(row + i, x);
+        float vm = x[0];
+#pragma unroll
+        for (int k = 1; k < 8; ++k) vm = fmaxf(vm, x[k]);
+        if (vm > m) { s *= __expf(m - vm); m = vm; }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) s += __expf(x[k] - m);
+      }
+    } else {
+      for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float x = __bfloat162float(row[i]);
+        if (x > m) { s = s * __expf(m - x) + 1.f; m = x; }
+        else s += __expf(x - m);
+      }
     }
     // merge (m, s) pairs
 #pragma unroll
@@ -61,10 +81,22 @@ greedy_rows_kernel(const bf16* __restrict__ logits, int vocab, int normalize, ui
   }
   const float lse = normalize ? s_lse : 0.f;
   ArgMax best{-INFINITY, 0x7fffffff};
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-    float x = __bfloat162float(row[i]);
-    if (normalize) x = bf16_round(x - lse);
-    best = better(best, ArgMax{x, i});
+  if (vec) {
+    for (int i = threadIdx.x * 8; i < vocab; i += blockDim.x * 8) {
+      float x[8];
+      load8_bf16(row + i, x);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float v = normalize ? bf16_round(x[k] - lse) : x[k];
+        if (v > best.v) best = ArgMax{v, i + k};   // indices rise within a thread: strict > keeps the lowest
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+      float x = __bfloat162float(row[i]);
+      if (normalize) x = bf16_round(x - lse);
+      best = better(best, ArgMax{x, i});
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
