@@ -150,6 +150,7 @@ struct kc_model {
   kc_model_desc d{};
   int Hq = 0, Hkv = 0;                 // local (tensor-parallel) head counts
   int F = 0;                           // local intermediate size
+  bool glu_interleaved = false;        // gate_up rows alternate gate / up in blocks of 128 (so the GEMM can fuse the activation)
   int n_qkv = 0;
   std::vector<Layer> layers;
   // embedding table in mlx layout (gather) and the head as GEMM records
@@ -399,6 +400,27 @@ static int run_qlinear(kc_ctx* c, const QWeight& w, const ActOperand& x, int M, 
       LAUNCH(c, KC_PROF_GEMM_REDUCE, 1, qlinear_reduce_splits(partial, w.splits, l.M, w.N, y + (size_t)row0 * ldy, ldy, c->stream));
   }
   if (fused) *fused = defer ? SublayerOut::partials(partial, w.splits, (size_t)M, w.N) : SublayerOut::dense(y, ldy);
+  return KC_OK;
+}
+
+// act[M, F] = activation(x . Wgate^T) * (x . Wup^T) for a gate_up weight whose tiles alternate gate / up. Row slabs
+// whose GEMM launch owns whole tile pairs get the activation in the GEMM's epilogue; the others write the
+// interleaved [M, 2F] product and run the element-wise kernel on it. Both ways round at the same points.
+static int run_gated(kc_ctx* c, const QWeight& w, const ActOperand& x, int M, bf16* gu, int F, int gelu, bool interleaved,
+                     bf16* act, float* partial) {
+  for (int row0 = 0; row0 < M; row0 += QL_MAX_M) {
+    const int rows = std::min(QL_MAX_M, M - row0);
+    int done = 0;
+    QLinearLaunch l;
+    l.w = &w; l.x = &x; l.row0 = row0; l.M = rows;
+    l.y = gu; l.ldy = 2 * F; l.partial = partial; l.status = c->status;
+    if (interleaved) { l.glu = gelu ? 2 : 1; l.act = act; l.ld_act = F; l.glu_done = &done; }
+    LAUNCH(c, KC_PROF_GEMM, 1, qlinear_umma(l, c->stream));
+    if (done) continue;
+    if (w.splits > 1)
+      LAUNCH(c, KC_PROF_GEMM_REDUCE, 1, qlinear_reduce_splits(partial, w.splits, rows, w.N, gu + (size_t)row0 * 2 * F, 2 * F, c->stream));
+    LAUNCH(c, KC_PROF_ROWWISE, 1, launch_glu(gu + (size_t)row0 * 2 * F, rows, F, gelu, interleaved ? 1 : 0, act + (size_t)row0 * F, c->stream));
+  }
   return KC_OK;
 }
 
@@ -717,7 +739,21 @@ extern "C" int kc_model_load(kc_ctx_t c, const kc_model_desc* desc, const kc_ten
                            H, 0, H, &L.qkv, &L.qkv_bias));
     LOAD_FAIL(build_linear(m, idx, {{p + ".self_attn.o_proj", 0, H}}, d.num_heads * D, (int)q0, (int)q1, &L.o, nullptr));
     const int64_t f0 = (int64_t)d.tp_rank * m->F, f1 = f0 + m->F;
-    LOAD_FAIL(build_linear(m, idx, {{p + ".mlp.gate_proj", f0, f1}, {p + ".mlp.up_proj", f0, f1}}, H, 0, H, &L.gate_up, nullptr));
+    {
+      // gate and up rows alternate in blocks of one GEMM tile (128 rows) when the width allows it, so a CTA that owns
+      // two neighbouring tiles holds gate and up of the same features
+      std::vector<Part> gu_parts;
+      m->glu_interleaved = m->F % 128 == 0;
+      if (m->glu_interleaved) {
+        for (int64_t r = f0; r < f1; r += 128) {
+          gu_parts.push_back({p + ".mlp.gate_proj", r, r + 128});
+          gu_parts.push_back({p + ".mlp.up_proj", r, r + 128});
+        }
+      } else {
+        gu_parts = {{p + ".mlp.gate_proj", f0, f1}, {p + ".mlp.up_proj", f0, f1}};
+      }
+      LOAD_FAIL(build_linear(m, idx, gu_parts, H, 0, H, &L.gate_up, nullptr));
+    }
     LOAD_FAIL(build_linear(m, idx, {{p + ".mlp.down_proj", 0, H}}, d.intermediate_size, (int)f0, (int)f1, &L.down, nullptr));
     LOAD_FAIL(load_norm(m, idx, p + ".input_layernorm.weight", gemma, &L.input_ln));
     LOAD_FAIL(load_norm(m, idx, p + ".post_attention_layernorm.weight", gemma, &L.post_attn_ln));
@@ -1005,8 +1041,7 @@ int run_forward(kc_model* m, kc_kv* kv, const uint32_t* tokens_dev, const StepPl
     if (d.tp_world > 1 && (rc = tp_allreduce(m, m->proj, n))) return rc;
     if (gemma) LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, so, L.post_attn_ln, L.pre_ffw_ln, nullptr, n, H, d.rms_norm_eps, m->h, m->normed, c->stream));
     else LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, so, nullptr, L.post_attn_ln, nullptr, n, H, d.rms_norm_eps, m->h, m->normed, c->stream));
-    RC(run_qlinear(c, L.gate_up, m->op_normed, n, m->gu, 2 * m->F, m->partial));
-    LAUNCH(c, KC_PROF_ROWWISE, 1, launch_glu(m->gu, n, m->F, gemma ? 1 : 0, m->act, c->stream));
+    RC(run_gated(c, L.gate_up, m->op_normed, n, m->gu, m->F, gemma ? 1 : 0, m->glu_interleaved, m->act, m->partial));
     RC(run_qlinear(c, L.down, m->op_act, n, m->proj, H, m->partial, d.tp_world > 1 ? nullptr : &so));
     if (d.tp_world > 1) so = SublayerOut::dense(m->proj, H);
     if (d.tp_world > 1 && (rc = tp_allreduce(m, m->proj, n))) return rc;

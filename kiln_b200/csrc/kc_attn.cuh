@@ -7,7 +7,10 @@ namespace kc {
 
 // Keys per chunk. Chunks are cut at absolute key positions, so the partition a
 // query row sees depends only on its own position.
-constexpr int ATT_CHUNK = 512;
+#ifndef ATT_CHUNK_KEYS
+#define ATT_CHUNK_KEYS 512
+#endif
+constexpr int ATT_CHUNK = ATT_CHUNK_KEYS;
 
 struct AttnParams {
   const bf16* q;               // [n_tokens, Hq, D] post-RoPE

@@ -199,6 +199,22 @@ inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
+// Mlp::forward activation (nn.rs:284-294): silu(gate) * up with the three bf16 roundings of the composed ops, or
+// gelu_approx(gate) * up op for op (nn.rs:221-235). g and u are bf16 values held in fp32; so is the result.
+__device__ __forceinline__ float act_silu_mul(float g, float u) {
+  const float s = bf16_round(1.f / (1.f + __expf(-g)));
+  const float t = bf16_round(g * s);
+  return bf16_round(t * u);
+}
+__device__ __forceinline__ float act_gelu_mul(float g, float u) {
+  const float cube = bf16_round(g * g * g);  // power(x, 3) in fp32, rounded once
+  const float inner = bf16_round(g + bf16_round(bf16_round(0.044715f) * cube));
+  const float scaled = bf16_round(bf16_round(0.7978845608028654f) * inner);
+  const float gate = bf16_round(1.f + bf16_round(tanhf(scaled)));
+  const float act = bf16_round(bf16_round(0.5f * g) * gate);
+  return bf16_round(act * u);
+}
+
 // A ring position: stage index and phase bit, advanced without division.
 struct RingPos {
   int stage = 0;

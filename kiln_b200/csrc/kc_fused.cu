@@ -316,30 +316,20 @@ rope_kv_write_kernel(RowSource qkv, const bf16* __restrict__ bias, const float* 
 // roundings of the composed ops, or gelu_approx(gate) * up op for op (nn.rs:221-235).
 // gu: [n, 2F] (gate | up)
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ float act_silu_mul(float g, float u) {
-  const float s = bf16_round(1.f / (1.f + __expf(-g)));
-  const float t = bf16_round(g * s);
-  return bf16_round(t * u);
-}
-__device__ __forceinline__ float act_gelu_mul(float g, float u) {
-  const float cube = bf16_round(g * g * g);  // power(x, 3) in fp32, rounded once
-  const float inner = bf16_round(g + bf16_round(bf16_round(0.044715f) * cube));
-  const float scaled = bf16_round(bf16_round(0.7978845608028654f) * inner);
-  const float gate = bf16_round(1.f + bf16_round(tanhf(scaled)));
-  const float act = bf16_round(bf16_round(0.5f * g) * gate);
-  return bf16_round(act * u);
-}
-
-__global__ void __launch_bounds__(256) glu_kernel(const bf16* __restrict__ gu, int n, int F, int gelu, bf16* __restrict__ out) {
+// interleaved: gate and up features alternate in blocks of 128 columns (gate block j at columns 256 j, up block j at
+// 256 j + 128) instead of all gate columns followed by all up columns.
+__global__ void __launch_bounds__(256) glu_kernel(const bf16* __restrict__ gu, int n, int F, int gelu, int interleaved, bf16* __restrict__ out) {
   pdl_launch_dependents();
   pdl_wait();
   const int per_row = F / 8;
   const int total = n * per_row;
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
     const int row = i / per_row, col = (i - row * per_row) * 8;
+    const int gcol = interleaved ? (col >> 7) * 256 + (col & 127) : col;
+    const int ucol = interleaved ? gcol + 128 : F + col;
     float g[8], u[8];
-    load8_bf16(gu + (size_t)row * 2 * F + col, g);
-    load8_bf16(gu + (size_t)row * 2 * F + F + col, u);
+    load8_bf16(gu + (size_t)row * 2 * F + gcol, g);
+    load8_bf16(gu + (size_t)row * 2 * F + ucol, u);
 #pragma unroll
     for (int k = 0; k < 8; ++k) g[k] = gelu ? act_gelu_mul(g[k], u[k]) : act_silu_mul(g[k], u[k]);
     store8_bf16(out + (size_t)row * F + col, g);
@@ -411,11 +401,11 @@ cudaError_t launch_rope_kv_write(const SublayerOut& qkv, const bf16* bias, const
                   traditional, layer, NB, BS, pool, q_out);
 }
 
-cudaError_t launch_glu(const bf16* gu, int n, int F, int gelu, bf16* out, cudaStream_t s) {
-  if (F % 8) return cudaErrorInvalidValue;
+cudaError_t launch_glu(const bf16* gu, int n, int F, int gelu, int interleaved, bf16* out, cudaStream_t s) {
+  if (F % 8 || (interleaved && F % 128)) return cudaErrorInvalidValue;
   const long long total = (long long)n * (F / 8);
   const int blocks = (int)std::min<long long>((total + 255) / 256, 148LL * 8);
-  return launch_k(glu_kernel, dim3(blocks), dim3(256), 0, s, gu, n, F, gelu, out);
+  return launch_k(glu_kernel, dim3(blocks), dim3(256), 0, s, gu, n, F, gelu, interleaved, out);
 }
 
 cudaError_t launch_softcap(bf16* x, long long total, float cap, cudaStream_t s) {

@@ -301,6 +301,8 @@ struct QlKernelParams {
   int a_stages, r_stages;
   uint32_t raw_stride;   // distance between the records of neighbouring tiles in a raw stage (= record_bytes)
   int b_single;          // 1: the first tensor map's box spans all m_pad rows (one TMA operation per k-block)
+  int glu;               // 0, or 1 (silu) / 2 (gelu_approx): the epilogue writes act = activation(gate tile) * up tile
+  bf16* act; int ld_act;
   uint32_t tmem_cols;    // power of two >= max(32, NT * m_pad)
   bf16* y; int ldy;
   float* partial;
@@ -548,6 +550,34 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
       const bool vec_ok = p.splits == 1 ? ((p.ldy & 3) == 0 && (reinterpret_cast<uintptr_t>(p.y) & 7) == 0)
                                         : ((p.N & 3) == 0 && (reinterpret_cast<uintptr_t>(p.partial) & 15) == 0);
       const int nl = 4 * (lane & 7), mr0 = lane >> 3;
+      if (NT >= 2 && p.glu) {
+        // tiles (2 pr, 2 pr + 1) of this CTA are the gate and up halves of features 128 * (tile0 / 2 + pr) ..:
+        // both accumulators' values of a (feature, row) sit in the same thread, 16 rows at a time
+        const int chunks16 = p.m_pad >> 4;
+        for (int item = eg; item < (nt_live >> 1) * chunks16; item += QL_DQ_WARPS / 4) {
+          const int pr = item / chunks16, ch = item - pr * chunks16;
+          uint32_t g[16], u[16];
+          tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (2 * pr) * col_stride + ch * 16, g);
+          tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (2 * pr + 1) * col_stride + ch * 16, u);
+          __syncwarp();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float gv = bf16_round(__uint_as_float(g[j])), uv = bf16_round(__uint_as_float(u[j]));
+            stage[j * 32 + lane] = p.glu == 2 ? act_gelu_mul(gv, uv) : act_silu_mul(gv, uv);
+          }
+          __syncwarp();
+          const int f = ((tile0 >> 1) + pr) * QL_TILE_N + q * 32 + nl;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int mr = 4 * k + mr0;
+            const int m = ch * 16 + mr;
+            if (m >= p.M) continue;
+            const float4 v4 = *reinterpret_cast<const float4*>(stage + mr * 32 + nl);
+            *reinterpret_cast<uint2*>(p.act + (size_t)(p.row0 + m) * p.ld_act + f) =
+                make_uint2(pack_bf162(v4.x, v4.y), pack_bf162(v4.z, v4.w));
+          }
+        }
+      } else
       for (int item = eg; item < nt_live * chunks; item += QL_DQ_WARPS / 4) {
         const int t = item / chunks, ch = item - t * chunks;
         const int col = (NT == 1 ? 0 : t * col_stride) + ch * 32;   // NT == 1: columns are m directly (incl. the 256+ accumulator)
@@ -671,6 +701,11 @@ cudaError_t qlinear_umma(const QLinearLaunch& l, cudaStream_t s) {
   static const int env_nt = getenv("KC_QL_NT") ? atoi(getenv("KC_QL_NT")) : 0;
   int nt = plan_tiles_per_cta(w, p.m_pad, w.sm_count);
   if (env_nt) nt = std::min(env_nt, p.m_pad <= 128 ? 4 : (p.m_pad <= 256 ? 2 : 1));
+  // the gated activation is fused when a CTA owns whole (gate, up) tile pairs and writes final values
+  const bool glu = l.glu && nt >= 2 && w.splits == 1 && (w.n_tiles & 1) == 0 && (w.N % (2 * QL_TILE_N)) == 0 && l.act &&
+                   (l.ld_act & 3) == 0 && (reinterpret_cast<uintptr_t>(l.act) & 7) == 0;
+  p.glu = glu ? l.glu : 0; p.act = l.act; p.ld_act = l.ld_act;
+  if (l.glu_done) *l.glu_done = glu ? 1 : 0;
   if (w.bits == 4) return w.gpk == 2 ? launch_umma_nt<4, 2>(l, p, nt, s) : launch_umma_nt<4, 1>(l, p, nt, s);
   return w.gpk == 2 ? launch_umma_nt<8, 2>(l, p, nt, s) : launch_umma_nt<8, 1>(l, p, nt, s);
 }

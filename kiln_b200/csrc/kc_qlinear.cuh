@@ -66,6 +66,14 @@ struct QLinearLaunch {
   int ldy;
   float* partial;   // [splits][M][N] fp32 workspace when splits > 1 (rows relative to row0)
   uint32_t* status; // device status word
+  // Optional fused gated activation for a weight whose 128-row tiles alternate gate / up (tile 2j = gate features
+  // 128 j.., tile 2j + 1 = the matching up features): glu = 1 (silu) or 2 (gelu_approx) asks the epilogue to write
+  // act[M, N / 2] = activation(gate) * up instead of y. Honoured only when one CTA owns whole gate/up tile pairs and
+  // K is not split; *glu_done then is set to 1, otherwise y is written as usual and *glu_done is 0.
+  int glu = 0;
+  bf16* act = nullptr;
+  int ld_act = 0;
+  int* glu_done = nullptr;
 };
 
 // Fixed split-K plan: a function of the weight's shape only, so a row's

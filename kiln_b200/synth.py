@@ -141,6 +141,8 @@ PRESETS: Dict[str, ModelConfig] = {
     "tiny-llama-d128": ModelConfig("llama", 512, 2, 4, 1, 128, 1024, 2048, 4, 64, 1e-5, 10000.0, False, None, False),
     # hidden 2048: the row-wise kernels' register-resident path and split-K partials at a real row width
     "tiny-llama-h2048": ModelConfig("llama", 2048, 1, 16, 4, 128, 2048, 1024, 4, 64, 1e-5, 500000.0, False, None, False),
+    # a wide MLP (208 gate_up tiles): the GEMM keeps two tiles per CTA and fuses the gated activation into its epilogue
+    "tiny-llama-wide": ModelConfig("llama", 128, 1, 2, 1, 64, 13312, 512, 4, 64, 1e-5, 10000.0, False, None, False),
     "tiny-qwen2": ModelConfig("qwen2", 448, 2, 7, 1, 64, 1024, 1536, 8, 32, 1e-6, 1000000.0, False, None, False,
                               qkv_bias=True),
     "tiny-gemma2": ModelConfig("gemma2", 512, 2, 4, 2, 256, 1024, 2048, 4, 128, 1e-6, 10000.0, False, None, True,

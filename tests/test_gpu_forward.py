@@ -22,7 +22,7 @@ from tests.conftest import cosine
 
 pytestmark = pytest.mark.gpu
 
-MODELS = ["tiny-llama", "tiny-llama-d128", "tiny-qwen2", "tiny-gemma2", "tiny-llama-h2048"]
+MODELS = ["tiny-llama", "tiny-llama-d128", "tiny-qwen2", "tiny-gemma2", "tiny-llama-h2048", "tiny-llama-wide"]
 BS = 16
 
 
