@@ -282,6 +282,9 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 // The kernel
 // ---------------------------------------------------------------------------
 
+#ifndef KC_QL_SLEEP
+#define KC_QL_SLEEP 0
+#endif
 constexpr int QL_DQ_WARP0 = 4;         // first dequant/epilogue warp
 constexpr int QL_DQ_GROUPS = 2;        // dequant groups; group g converts k-blocks g, g + G, g + 2G, ...
 constexpr int QL_DQ_GROUP_WARPS = 8;
@@ -505,9 +508,9 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
     for (int i = grp; i < nkb && ok; i += QL_DQ_GROUPS) {
       const int rs = rp.stage; const uint32_t rph = rp.phase;
       const int as = ap.stage; const uint32_t aph = ap.phase;
-      ok = __all_sync(0xffffffffu, mbar_wait(&raw_full[rs], rph, p.status, KC_DEV_QLINEAR | 5));
+      ok = __all_sync(0xffffffffu, KC_QL_SLEEP ? mbar_wait_relaxed(&raw_full[rs], rph, p.status, KC_DEV_QLINEAR | 5, KC_QL_SLEEP) : mbar_wait(&raw_full[rs], rph, p.status, KC_DEV_QLINEAR | 5));
       if (!ok) break;
-      ok = __all_sync(0xffffffffu, mbar_wait(&ab_empty[as], aph ^ 1, p.status, KC_DEV_QLINEAR | 6));
+      ok = __all_sync(0xffffffffu, KC_QL_SLEEP ? mbar_wait_relaxed(&ab_empty[as], aph ^ 1, p.status, KC_DEV_QLINEAR | 6, KC_QL_SLEEP) : mbar_wait(&ab_empty[as], aph ^ 1, p.status, KC_DEV_QLINEAR | 6));
       if (!ok) break;
 #pragma unroll
       for (int u = 0; u < UNITS; ++u) {
