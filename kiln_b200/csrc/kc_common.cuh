@@ -113,23 +113,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32
   return true;
 }
 
-// Bounded wait for waiters with slack (a stage hand-off that is normally hundreds of cycles away): between polls the
-// warp sleeps, so that its polling does not take issue slots from the warps doing arithmetic on the same scheduler.
-__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, uint32_t* status, uint32_t code,
-                                                  unsigned sleep_ns) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = globaltimer_ns();
-  uint32_t spins = 0;
-  for (;;) {
-    __nanosleep(sleep_ns);
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 0x3f) == 0 && globaltimer_ns() - t0 > KC_SPIN_LIMIT_NS) {
-      if (status) atomicOr(status, code);
-      return false;
-    }
-  }
-}
-
 // ---- async-proxy fences, bulk copies (TMA) --------------------------------
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

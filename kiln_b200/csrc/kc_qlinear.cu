@@ -282,9 +282,6 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 // The kernel
 // ---------------------------------------------------------------------------
 
-#ifndef KC_QL_SLEEP
-#define KC_QL_SLEEP 0
-#endif
 constexpr int QL_DQ_WARP0 = 4;         // first dequant/epilogue warp
 constexpr int QL_DQ_GROUPS = 2;        // dequant groups; group g converts k-blocks g, g + G, g + 2G, ...
 constexpr int QL_DQ_GROUP_WARPS = 8;
@@ -508,9 +505,9 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
     for (int i = grp; i < nkb && ok; i += QL_DQ_GROUPS) {
       const int rs = rp.stage; const uint32_t rph = rp.phase;
       const int as = ap.stage; const uint32_t aph = ap.phase;
-      ok = __all_sync(0xffffffffu, KC_QL_SLEEP ? mbar_wait_relaxed(&raw_full[rs], rph, p.status, KC_DEV_QLINEAR | 5, KC_QL_SLEEP) : mbar_wait(&raw_full[rs], rph, p.status, KC_DEV_QLINEAR | 5));
+      ok = __all_sync(0xffffffffu, mbar_wait(&raw_full[rs], rph, p.status, KC_DEV_QLINEAR | 5));
       if (!ok) break;
-      ok = __all_sync(0xffffffffu, KC_QL_SLEEP ? mbar_wait_relaxed(&ab_empty[as], aph ^ 1, p.status, KC_DEV_QLINEAR | 6, KC_QL_SLEEP) : mbar_wait(&ab_empty[as], aph ^ 1, p.status, KC_DEV_QLINEAR | 6));
+      ok = __all_sync(0xffffffffu, mbar_wait(&ab_empty[as], aph ^ 1, p.status, KC_DEV_QLINEAR | 6));
       if (!ok) break;
 #pragma unroll
       for (int u = 0; u < UNITS; ++u) {
@@ -635,12 +632,10 @@ static cudaError_t launch_umma(const QLinearLaunch& l, QlKernelParams& p, cudaSt
   while ((int)cols < (NT == 1 ? p.m_pad : NT * ((p.m_pad + 31) & ~31))) cols <<= 1;
   p.tmem_cols = cols;
   // Shared memory plan: the A+B ring first (2..4 stages), what is left goes to the raw-record ring.
-  static const int env_kb = getenv("KC_QL_SMEM_KB") ? atoi(getenv("KC_QL_SMEM_KB")) : 212;
-  const size_t budget = (size_t)env_kb * 1024;
+  const size_t budget = (size_t)212 * 1024;
   const size_t ab = (size_t)KC * ((size_t)NT * QL_A_BYTES + (size_t)p.m_pad * 128);
   const size_t rstage = (size_t)KC * NT * p.raw_stride;
-  static const int env_as = getenv("KC_QL_AS") ? atoi(getenv("KC_QL_AS")) : 4;
-  int as = (int)std::min<size_t>(env_as, (budget - 3 * rstage) / ab);
+  int as = (int)std::min<size_t>(4, (budget - 3 * rstage) / ab);
   if (as < 2) as = 2;
   as = std::min(as, std::max(2, p.kb_per_split / KC));
   const size_t left = budget > (size_t)as * ab ? budget - (size_t)as * ab : 0;
@@ -658,8 +653,7 @@ static cudaError_t launch_umma(const QLinearLaunch& l, QlKernelParams& p, cudaSt
   dim3 grid((w.n_tiles + NT - 1) / NT, w.splits);
   const CUtensorMap* first = &l.x->map16;
   p.b_single = 0;
-  static const bool single_ok = !(getenv("KC_QL_NO_SINGLE"));
-  if (single_ok && p.m_pad <= 256) {
+  if (p.m_pad <= 256) {
     first = act_operand_rows_map(l.x, p.m_pad);
     if (!first) return cudaErrorInvalidValue;
     p.b_single = 1;
@@ -675,9 +669,8 @@ static cudaError_t launch_umma_nt(const QLinearLaunch& l, QlKernelParams& p, int
     default: break;
   }
   // one tile per CTA: two k-blocks per stage when the split holds an even number of them and two such stages fit
-  static const bool kc2_ok = !getenv("KC_QL_NO_KC2");
   const size_t ab2 = 2 * ((size_t)QL_A_BYTES + (size_t)p.m_pad * 128);
-  if (kc2_ok && p.kb_per_split % 2 == 0 && p.kb_per_split >= 4 && 2 * ab2 + 3 * 2 * p.raw_stride <= 212 * 1024)
+  if (p.kb_per_split % 2 == 0 && p.kb_per_split >= 4 && 2 * ab2 + 3 * 2 * p.raw_stride <= 212 * 1024)
     return launch_umma<BITS, GPK, 1, 2>(l, p, s);
   return launch_umma<BITS, GPK, 1, 1>(l, p, s);
 }
@@ -701,9 +694,7 @@ cudaError_t qlinear_umma(const QLinearLaunch& l, cudaStream_t s) {
   p.splits = w.splits; p.kb_per_split = w.kblocks / w.splits;
   p.raw_stride = w.record_bytes;
   p.y = l.y; p.ldy = l.ldy; p.partial = l.partial; p.status = l.status;
-  static const int env_nt = getenv("KC_QL_NT") ? atoi(getenv("KC_QL_NT")) : 0;
   int nt = plan_tiles_per_cta(w, p.m_pad, w.sm_count);
-  if (env_nt) nt = std::min(env_nt, p.m_pad <= 128 ? 4 : (p.m_pad <= 256 ? 2 : 1));
   // the gated activation is fused when a CTA owns whole (gate, up) tile pairs and writes final values
   const bool glu = l.glu && nt >= 2 && w.splits == 1 && (w.n_tiles & 1) == 0 && (w.N % (2 * QL_TILE_N)) == 0 && l.act &&
                    (l.ld_act & 3) == 0 && (reinterpret_cast<uintptr_t>(l.act) & 7) == 0;
