@@ -122,6 +122,13 @@ def algorithmic(cfg, batch, k, mean_ctx):
             "attn_flops": attn_flops, "M": M}
 
 
+# DRAM traffic of the dominant kernel (the quantised GEMM) relative to its algorithmic weight bytes, from one ncu
+# capture of a single launch larger than L2 (out 128256 x in 4096, 192 rows; summary committed under profiles/):
+# dram__bytes_read.sum + dram__bytes_write.sum = 300.3 MB + 33.6 MB for 295.5 MB of weight records. The traffic of a
+# launch grows in proportion to its weight bytes, so the per-launch figure reported is this ratio times the mean
+# algorithmic weight bytes per GEMM launch of the step.
+GEMM_DRAM_TRAFFIC_PER_WEIGHT_BYTE = (300.3 + 33.6) / 295.5
+
 # --------------------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------------------
@@ -422,7 +429,10 @@ def main():
         "gpu_launches": int(launches_per_step * steps),
         "roofline": {"kernel": "qlinear_umma_kernel (affine-dequant GEMM, tcgen05)", "bound": "tensor",
                      "achieved": gemm_tflops, "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
-                     "frac": (gemm_tflops / pk["bf16_tflops_sustained"]) if gemm_tflops else None, "traffic": None,
+                     "frac": (gemm_tflops / pk["bf16_tflops_sustained"]) if gemm_tflops else None,
+                     "traffic": (GEMM_DRAM_TRAFFIC_PER_WEIGHT_BYTE * alg["weight_bytes"] / gemm_n) if gemm_n else None,
+                     "traffic_unit": "bytes per launch (ncu dram read+write of one launch, scaled by weight bytes)",
+                     "algorithmic_bytes_per_launch": (alg["weight_bytes"] / gemm_n) if gemm_n else None,
                      "peak_source": pk["source"] + " (sustained: the kernel runs inside a long step)",
                      "launches_per_step": gemm_n, "ms_per_step": gemm_ms,
                      "algorithmic_flops_per_launch": alg["gemm_flops"] / gemm_n if gemm_n else None},
