@@ -41,6 +41,11 @@ WORKLOADS = {
     # name: (preset, batch, k, prompt_lo, prompt_hi, generated)
     "llama-3.1-8b-w4g64-verify-k5-bs32": ("llama-3.1-8b", 32, 5, 512, 2048, 256),
     "llama-3.2-1b-w4g64-verify-k4-bs1": ("llama-3.2-1b", 1, 4, 128, 128, 64),
+    # parity-sized cases (speculation on == off at full size), not headline numbers: 64 requests that share a
+    # 1024-token prefix (radix cache + copy-on-write) with 256-token unique suffixes; Gemma-2 with 6144-token prompts
+    # (sliding window 4096 on even layers, attention and final-logit softcaps)
+    "qwen2.5-7b-w8g32-sharedprefix-k4-bs64": ("qwen2.5-7b", 64, 4, 1280, 1280, 128, {"shared_prefix": 1024}),
+    "gemma-2-9b-w4g128-verify-k3-bs16": ("gemma-2-9b", 16, 3, 6144, 6144, 128),
     "tiny-llama-verify-k4-bs4": ("tiny-llama", 4, 4, 40, 90, 48),
 }
 METRIC = "verified tok/s/GPU, Llama-3-8B w4g64 k=5 bs32; p50 verify-step ms"
@@ -142,7 +147,8 @@ class Workload:
         from kiln_b200 import api, host
         from kiln_b200.replicas import rank_seed
         from kiln_b200.synth import PRESETS, synth_checkpoint
-        preset, self.batch, self.k, lo, hi, self.gen = WORKLOADS[name]
+        preset, self.batch, self.k, lo, hi, self.gen = WORKLOADS[name][:6]
+        extras = WORKLOADS[name][6] if len(WORKLOADS[name]) > 6 else {}
         self.name, self.cfg = name, PRESETS[preset]
         cfg = self.cfg
         torch.cuda.set_device(local_rank)
@@ -162,6 +168,9 @@ class Workload:
         rng = np.random.default_rng(rank_seed(1000, rank))
         lens = rng.integers(lo, hi + 1, size=self.batch)
         self.prompts = [rng.integers(0, cfg.vocab_size, size=int(n), dtype=np.int64).tolist() for n in lens]
+        if extras.get("shared_prefix"):
+            common = rng.integers(0, cfg.vocab_size, size=int(extras["shared_prefix"]), dtype=np.int64).tolist()
+            self.prompts = [common + p[len(common):] for p in self.prompts]
         bs = 16
         per_seq = [-(-(len(p) + self.gen + self.k + 1) // bs) for p in self.prompts]
         self.num_blocks = sum(per_seq) + self.batch * ((self.gen + self.k + 1) // bs + 3) + 64
@@ -284,7 +293,7 @@ def cpu_reference(name: str, tensors, ctxs, steps: int, warmup: int, budget_s: f
     from kiln_b200 import api
     from kiln_b200.synth import PRESETS, synth_checkpoint, truncated
     from oracle import oracle as O
-    preset, batch, k, lo, hi, gen = WORKLOADS[name]
+    preset, batch, k, lo, hi, gen = WORKLOADS[name][:6]
     cfg = PRESETS[preset]
     cfg1 = truncated(cfg, 1)
     if tensors is None:
@@ -331,6 +340,9 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--check-only", action="store_true",
+                    help="run the workload once with speculation off and once with it on, to completion, and print only "
+                         "whether the two outputs are identical (full-size parity property; no benchmark line)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="llama-3.1-8b-w4g64-verify-k5-bs32", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -339,7 +351,7 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 0)
-    preset, batch, k, lo, hi, gen = WORKLOADS[args.workload]
+    preset, batch, k, lo, hi, gen = WORKLOADS[args.workload][:6]
     config = {"workload": args.workload, "batch": batch, "k": k, "prompt_tokens": [lo, hi], "generated_tokens": gen,
               "kv_block": 16, "draft": "scripted, greedy token with p=0.7 else uniform-random id (seeded)",
               "parallelism": f"replicas x{world}" if world > 1 else "single GPU",
@@ -368,8 +380,27 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
-    want_cpu = rank == 0 and world == 1 and not args.no_cpu_baseline
+    want_cpu = rank == 0 and world == 1 and not args.no_cpu_baseline and not args.check_only
     w = Workload(args.workload, rank, local_rank, keep_cpu_sample=want_cpu)
+    if args.check_only:
+        t0 = time.time()
+        base = w.run_off()
+        off_s = time.time() - t0
+        t0 = time.time()
+        arrivals = w.submit_on(base)
+        fin = w.engine.run_to_completion(arrivals)
+        on_s = time.time() - t0
+        same = [fin[a][0] == cont for a, cont in zip(arrivals, base)]
+        st = w.engine.spec_stats()
+        print(json.dumps({"check_only": True, "workload": args.workload, "rank": rank,
+                          "spec_on_equals_off": {"sequences_checked": len(same), "identical": all(same)},
+                          "generated_tokens": sum(len(c) for c in base), "speculation_off_s": round(off_s, 2),
+                          "speculation_on_s": round(on_s, 2), "proposed": st["proposed_total"], "accepted": st["accepted_total"],
+                          "rollback_rounds": st["rollback_rounds_total"], "cache": w.engine.cache_stats(),
+                          "device_status": w.ctx.device_status()}))
+        if dist:
+            dist.destroy_process_group()
+        return
     t0 = time.time()
     base = w.run_off()
     off_s = time.time() - t0

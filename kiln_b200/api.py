@@ -209,6 +209,19 @@ class Context:
     def sync(self) -> None:
         check(L.lib().kc_sync(self._h))
 
+    @staticmethod
+    def tp_unique_id() -> bytes:
+        """The 128 bytes of an NCCL unique id, to be created on rank 0 and handed to every rank's tp_init."""
+        buf = (C.c_uint8 * 128)()
+        check(L.lib().kc_tp_unique_id(buf))
+        return bytes(buf)
+
+    def tp_init(self, unique_id: bytes, rank: int, world: int) -> None:
+        """Joins the tensor-parallel communicator (before any model of that world is loaded on this context)."""
+        assert len(unique_id) == 128
+        buf = (C.c_uint8 * 128).from_buffer_copy(unique_id)
+        check(L.lib().kc_tp_init(self._h, buf, rank, world))
+
     @property
     def stream(self) -> int:
         return int(L.lib().kc_ctx_stream(self._h) or 0)

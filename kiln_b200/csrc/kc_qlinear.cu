@@ -661,16 +661,22 @@ static cudaError_t launch_umma(const QLinearLaunch& l, QlKernelParams& p, cudaSt
   return launch_k(qlinear_umma_kernel<BITS, GPK, NT, KC>, grid, dim3(QL_THREADS), smem, s, *first, l.x->map64, p);
 }
 
+// Two A/B stages and three raw stages of the given geometry within the shared-memory budget?
+static bool ql_fits(int nt, int kc, int m_pad, uint32_t raw_stride) {
+  const size_t ab = (size_t)kc * ((size_t)nt * QL_A_BYTES + (size_t)m_pad * 128);
+  const size_t rstage = (size_t)kc * nt * raw_stride;
+  return 2 * ab + 3 * rstage <= (size_t)212 * 1024;
+}
+
 template <int BITS, int GPK>
 static cudaError_t launch_umma_nt(const QLinearLaunch& l, QlKernelParams& p, int nt, cudaStream_t s) {
-  switch (nt) {
+  switch (nt) {   // the caller has lowered nt until its stages fit shared memory (wide 8-bit records, many rows)
     case 4: return launch_umma<BITS, GPK, 4, 1>(l, p, s);
     case 2: return launch_umma<BITS, GPK, 2, 1>(l, p, s);
     default: break;
   }
   // one tile per CTA: two k-blocks per stage when the split holds an even number of them and two such stages fit
-  const size_t ab2 = 2 * ((size_t)QL_A_BYTES + (size_t)p.m_pad * 128);
-  if (p.kb_per_split % 2 == 0 && p.kb_per_split >= 4 && 2 * ab2 + 3 * 2 * p.raw_stride <= 212 * 1024)
+  if (p.kb_per_split % 2 == 0 && p.kb_per_split >= 4 && ql_fits(1, 2, p.m_pad, p.raw_stride))
     return launch_umma<BITS, GPK, 1, 2>(l, p, s);
   return launch_umma<BITS, GPK, 1, 1>(l, p, s);
 }
@@ -695,6 +701,7 @@ cudaError_t qlinear_umma(const QLinearLaunch& l, cudaStream_t s) {
   p.raw_stride = w.record_bytes;
   p.y = l.y; p.ldy = l.ldy; p.partial = l.partial; p.status = l.status;
   int nt = plan_tiles_per_cta(w, p.m_pad, w.sm_count);
+  while (nt > 1 && !ql_fits(nt, 1, p.m_pad, p.raw_stride)) nt >>= 1;
   // the gated activation is fused when a CTA owns whole (gate, up) tile pairs and writes final values
   const bool glu = l.glu && nt >= 2 && w.splits == 1 && (w.n_tiles & 1) == 0 && (w.N % (2 * QL_TILE_N)) == 0 && l.act &&
                    (l.ld_act & 3) == 0 && (reinterpret_cast<uintptr_t>(l.act) & 7) == 0;

@@ -575,7 +575,15 @@ class Engine:
     def step(self) -> None:
         rc = lib().kh_engine_step(self._h)
         if rc != 0:
-            raise HostError(rc, lib().kh_engine_last_error(self._h).decode())
+            msg = lib().kh_engine_last_error(self._h).decode()
+            try:   # the step ran on this thread: the device library's own message names the failing call
+                from . import _lib as _cuda
+                detail = _cuda.lib().kc_last_error().decode("utf-8", "replace")
+                if detail:
+                    msg += f" ({detail})"
+            except Exception:
+                pass
+            raise HostError(rc, msg)
 
     num_running = property(lambda self: int(lib().kh_engine_num_running(self._h)))
     num_waiting = property(lambda self: int(lib().kh_engine_num_waiting(self._h)))

@@ -43,6 +43,7 @@ CASES = [
     (1024, 4096, 4, 64, 192),      # the 8B attention-output shape at verify width: split-K engaged
     (2048, 2048, 4, 64, 320),      # two accumulator tiles (M > 256)
     (512, 2048, 4, 64, 1),         # decode row
+    (53248, 256, 8, 32, 100),      # 416 tiles of 8-bit records at 100 rows: four tiles per CTA do not fit shared memory
 ]
 
 
