@@ -46,6 +46,10 @@ WORKLOADS = {
     # (sliding window 4096 on even layers, attention and final-logit softcaps)
     "qwen2.5-7b-w8g32-sharedprefix-k4-bs64": ("qwen2.5-7b", 64, 4, 1280, 1280, 128, {"shared_prefix": 1024}),
     "gemma-2-9b-w4g128-verify-k3-bs16": ("gemma-2-9b", 16, 3, 6144, 6144, 128),
+    # the tensor-parallel configuration: under torchrun every rank holds a slice of every layer and all ranks run the
+    # SAME requests (strong scaling); on one GPU it runs unsharded
+    "llama-3-70b-w4g64-verify-k4-bs64-tp": ("llama-3-70b", 64, 4, 1024, 4096, 256, {"tp": True}),
+    "llama-3.1-8b-w4g64-verify-k5-bs32-tp": ("llama-3.1-8b", 32, 5, 512, 2048, 256, {"tp": True}),
     "tiny-llama-verify-k4-bs4": ("tiny-llama", 4, 4, 40, 90, 48),
 }
 METRIC = "verified tok/s/GPU, Llama-3-8B w4g64 k=5 bs32; p50 verify-step ms"
@@ -141,7 +145,7 @@ GEMM_DRAM_TRAFFIC_PER_WEIGHT_BYTE = (300.3 + 33.6) / 295.5
 class Workload:
     """Model + pools + engine for one rank."""
 
-    def __init__(self, name: str, rank: int, local_rank: int, keep_cpu_sample: bool):
+    def __init__(self, name: str, rank: int, local_rank: int, keep_cpu_sample: bool, world: int = 1, dist=None):
         import numpy as np
         import torch
         from kiln_b200 import api, host
@@ -153,11 +157,19 @@ class Workload:
         cfg = self.cfg
         torch.cuda.set_device(local_rank)
         self.ctx = api.Context(local_rank)
+        self.tp = world if (extras.get("tp") and world > 1) else 1
+        if self.tp > 1:   # rank 0 creates the NCCL id; the bytes travel through the benchmark's own process group
+            ident = torch.zeros(128, dtype=torch.uint8, device=f"cuda:{local_rank}")
+            if rank == 0:
+                ident.copy_(torch.frombuffer(bytearray(api.Context.tp_unique_id()), dtype=torch.uint8))
+            dist.broadcast(ident, src=0)
+            self.ctx.tp_init(bytes(ident.cpu().numpy().tobytes()), rank, world)
         t0 = time.time()
         ck = synth_checkpoint(cfg, seed=0, device=f"cuda:{local_rank}")
         self.prefill_chunk = 2048 if cfg.hidden_size >= 2048 else 256
         max_step = self.prefill_chunk + self.batch * (self.k + 1)
-        self.model = api.CudaModel(self.ctx, cfg, ck, max_step_tokens=max_step, max_step_seqs=self.batch + 1)
+        self.model = api.CudaModel(self.ctx, cfg, ck, max_step_tokens=max_step, max_step_seqs=self.batch + 1,
+                                   tp_rank=rank if self.tp > 1 else 0, tp_world=self.tp)
         self.cpu_sample = None
         if keep_cpu_sample:   # layer 0 + embedding + final norm + head on the host, for the CPU baseline
             keep = {n: t.cpu() for n, t in ck.items() if not n.startswith("model.layers.") or n.startswith("model.layers.0.")}
@@ -165,7 +177,7 @@ class Workload:
         del ck
         torch.cuda.empty_cache()
         self.build_s = time.time() - t0
-        rng = np.random.default_rng(rank_seed(1000, rank))
+        rng = np.random.default_rng(rank_seed(1000, 0 if self.tp > 1 else rank))   # tensor-parallel ranks serve the same requests
         lens = rng.integers(lo, hi + 1, size=self.batch)
         self.prompts = [rng.integers(0, cfg.vocab_size, size=int(n), dtype=np.int64).tolist() for n in lens]
         if extras.get("shared_prefix"):
@@ -174,15 +186,23 @@ class Workload:
         bs = 16
         per_seq = [-(-(len(p) + self.gen + self.k + 1) // bs) for p in self.prompts]
         self.num_blocks = sum(per_seq) + self.batch * ((self.gen + self.k + 1) // bs + 3) + 64
-        self.kv = api.PagedKv(self.ctx, self.model.kv_spec(self.num_blocks, bs))
+        self.kv = api.PagedKv(self.ctx, self.model.kv_spec(self.num_blocks, bs, tp_world=self.tp))
         ec = host.EngineConfig(block_size=bs, num_blocks=self.num_blocks, max_batch_tokens=max_step,
                                prefill_chunk=self.prefill_chunk, prefill_fine_chunk=128, prefix_cache=True,
-                               deterministic_decode_width=32, gamma=self.k,
+                               deterministic_decode_width=max(32, self.batch), gamma=self.k,
                                spec_max_batch=1 << 20,   # keeps the width ramp (drafter.rs:62-70) at gamma = k for the whole batch
                                spec_min_acceptance=0.0, max_key_len=0, batch_verify=True)
         self.engine = host.Engine(ec, host.StepModel.from_cuda(self.model, self.kv))
         self.host = host
         self.mean_prompt = float(sum(len(p) for p in self.prompts)) / self.batch
+
+    def close(self):
+        """Releases the device objects in dependency order (before the process group and the interpreter go away)."""
+        self.ctx.sync()
+        self.engine = None
+        self.model.close()
+        self.kv.close()
+        self.ctx.close()
 
     def run_off(self):
         """Phase 1: speculation off, to completion. Returns the greedy continuation of every prompt."""
@@ -352,10 +372,11 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 0)
     preset, batch, k, lo, hi, gen = WORKLOADS[args.workload][:6]
+    metric = METRIC if args.workload == "llama-3.1-8b-w4g64-verify-k5-bs32" else f"verified tok/s, {args.workload}"
     config = {"workload": args.workload, "batch": batch, "k": k, "prompt_tokens": [lo, hi], "generated_tokens": gen,
               "kv_block": 16, "draft": "scripted, greedy token with p=0.7 else uniform-random id (seeded)",
               "parallelism": f"replicas x{world}" if world > 1 else "single GPU",
-              "l2": "inputs larger than L2 (4.2 GB weights + ~5.9 GB KV per step vs 126 MB)"}
+              "l2": ("inputs larger than L2 (4.2 GB weights + ~5.9 GB KV per step vs 126 MB)" if args.workload == "llama-3.1-8b-w4g64-verify-k5-bs32" else "inputs larger than L2 (the weights and the KV of a step are far above 126 MB)")}
 
     if args.impl == "reference":
         if rank != 0:
@@ -363,7 +384,7 @@ def main():
         r = cpu_reference(args.workload, None, None, args.steps, warmup)
         commit = 1 + sum(0.7 ** i for i in range(1, k + 1))
         val = batch * commit / r["step_s"]
-        line = {"impl": "reference", "metric": METRIC, "value": val, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
+        line = {"impl": "reference", "metric": metric, "value": val, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
                 "warmup": warmup, "ms_per_step": r["step_s"] * 1e3, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config,
                 "cpu_baseline": {"value": val, "unit": "tok/s", "cores": r["cores"], "kind": "port", "sample": r["sample"]},
@@ -381,7 +402,9 @@ def main():
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
     want_cpu = rank == 0 and world == 1 and not args.no_cpu_baseline and not args.check_only
-    w = Workload(args.workload, rank, local_rank, keep_cpu_sample=want_cpu)
+    w = Workload(args.workload, rank, local_rank, keep_cpu_sample=want_cpu, world=world, dist=dist)
+    if w.tp > 1:
+        config["parallelism"] = f"tp{world}"
     if args.check_only:
         t0 = time.time()
         base = w.run_off()
@@ -391,13 +414,25 @@ def main():
         fin = w.engine.run_to_completion(arrivals)
         on_s = time.time() - t0
         same = [fin[a][0] == cont for a, cont in zip(arrivals, base)]
+        first_bad = [(i, next((j for j, (x, y) in enumerate(zip(fin[a][0], cont)) if x != y), min(len(fin[a][0]), len(cont))),
+                      len(fin[a][0]), len(cont), fin[a][1])
+                     for i, (a, cont) in enumerate(zip(arrivals, base)) if fin[a][0] != cont][:4]
+        # a second speculation-on pass over the same requests: equal to the first unless something is not deterministic
+        arrivals2 = w.submit_on(base)
+        fin2 = w.engine.run_to_completion(arrivals2)
+        on_twice_equal = all(fin2[b][0] == fin[a][0] for a, b in zip(arrivals, arrivals2))
         st = w.engine.spec_stats()
         print(json.dumps({"check_only": True, "workload": args.workload, "rank": rank,
-                          "spec_on_equals_off": {"sequences_checked": len(same), "identical": all(same)},
+                          "spec_on_equals_off": {"sequences_checked": len(same), "identical": all(same),
+                                                 "mismatching": len(same) - sum(same),
+                                                 "first_mismatches(seq, position, len_on, len_off, finish)": first_bad},
+                          "speculation_on_twice_equal": on_twice_equal, "launches": w.ctx.launch_count(),
+                          "iterations": w.engine.iterations,
                           "generated_tokens": sum(len(c) for c in base), "speculation_off_s": round(off_s, 2),
                           "speculation_on_s": round(on_s, 2), "proposed": st["proposed_total"], "accepted": st["accepted_total"],
                           "rollback_rounds": st["rollback_rounds_total"], "cache": w.engine.cache_stats(),
                           "device_status": w.ctx.device_status()}))
+        w.close()
         if dist:
             dist.destroy_process_group()
         return
@@ -435,9 +470,12 @@ def main():
             identical &= (outs.get(a, []) + fin[a][0]) == cont
 
     from kiln_b200.replicas import combine_over_ranks
+    if w.tp > 1 and rank != 0:
+        tokens = 0   # every tensor-parallel rank verified the same tokens: count them once
     tot = combine_over_ranks(dist, f"cuda:{local_rank}", dev_ms, wall_ms, tokens, identical, world)
     dev_ms, wall_ms, tokens, identical = tot.device_ms, tot.wall_ms, tot.tokens, tot.all_identical
     if rank != 0:
+        w.close()
         if dist:
             dist.destroy_process_group()
         return
@@ -451,8 +489,9 @@ def main():
     gemm_tflops = alg["gemm_flops"] / (gemm_ms * 1e-3) / 1e12 if gemm_ms else None
     p50 = step_ms[len(step_ms) // 2]
     line = {
-        "metric": METRIC, "value": tokens / (dev_ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warmup,
-        "ms_per_step": dev_ms / steps, "p50_step_ms": p50, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "metric": metric, "value": tokens / (dev_ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+        "ms_per_step": dev_ms / steps, "p50_step_ms": p50, "higher_is_better": True,
+        "scaling": "strong" if w.tp > 1 else "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic", "config": config, "clocks": clocks,
         "e2e": {"value": tokens / (wall_ms * 1e-3), "unit": "tok/s", "ms_per_step": wall_ms / steps,
                 "h2d_bytes_per_step": int(batch * (k + 1) * 4 * 4 + batch * (mean_ctx / 16 + 2) * 4 + batch * 16 + batch * 12 + batch * (k + 1) * 8),
@@ -473,7 +512,7 @@ def main():
         "kernel_classes_ms_per_step": {k2: round(v[0], 4) for k2, v in prof.items()},
         "kernel_classes_launches_per_step": {k2: v[1] for k2, v in prof.items()},
         "acceptance": {"proposed": sum(r["proposed"] for r in records), "accepted": sum(r["accepted"] for r in records),
-                       "tokens_per_step": tokens / steps / world},
+                       "tokens_per_step": tokens / steps / (1 if w.tp > 1 else world)},
         "spec_on_equals_off": {"sequences_checked": checked, "identical": bool(identical)},
         "setup_s": {"build_model": round(w.build_s, 1), "speculation_off_run": round(off_s, 1)},
     }
@@ -483,6 +522,7 @@ def main():
         line["cpu_baseline"] = {"value": (tokens / steps) / r["step_s"], "unit": "tok/s", "cores": r["cores"], "kind": "port",
                                 "sample": r["sample"], "ms_per_step": r["step_s"] * 1e3}
     print(json.dumps(line))
+    w.close()
     if dist:
         dist.destroy_process_group()
 

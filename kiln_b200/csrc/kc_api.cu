@@ -163,7 +163,7 @@ struct kc_model {
   int64_t weight_bytes = 0;
   // activations
   int max_rows = 0, max_seqs = 0, logit_rows = 0;
-  bf16 *h = nullptr, *normed = nullptr, *qkv = nullptr, *q_rot = nullptr, *attn = nullptr, *proj = nullptr,
+  bf16 *h = nullptr, *normed = nullptr, *qkv = nullptr, *q_rot = nullptr, *attn = nullptr, *proj = nullptr, *proj_ranks = nullptr,
        *gu = nullptr, *act = nullptr, *hs = nullptr, *logits = nullptr;
   ActOperand op_normed, op_attn, op_act, op_hs;
   float* partial = nullptr; size_t partial_bytes = 0;
@@ -657,7 +657,7 @@ void free_model(kc_model* m) {
   }
   qweight_free(&m->head);
   cudaFree(m->emb_w); cudaFree(m->emb_s); cudaFree(m->emb_b); cudaFree(m->final_norm); cudaFree(m->inv_freq);
-  cudaFree(m->h); cudaFree(m->normed); cudaFree(m->qkv); cudaFree(m->q_rot); cudaFree(m->attn); cudaFree(m->proj);
+  cudaFree(m->h); cudaFree(m->normed); cudaFree(m->qkv); cudaFree(m->q_rot); cudaFree(m->attn); cudaFree(m->proj); cudaFree(m->proj_ranks);
   cudaFree(m->gu); cudaFree(m->act); cudaFree(m->hs); cudaFree(m->logits); cudaFree(m->partial); cudaFree(m->attn_ws);
   cudaFree(m->tp_buf);
   cudaFree(m->meta_dev);
@@ -797,6 +797,7 @@ extern "C" int kc_model_load(kc_ctx_t c, const kc_model_desc* desc, const kc_ten
   };
   LOAD_FAIL(dalloc(&m->h, R * H)); LOAD_FAIL(dalloc(&m->normed, R * H)); LOAD_FAIL(dalloc(&m->qkv, R * m->n_qkv));
   LOAD_FAIL(dalloc(&m->q_rot, R * m->Hq * D)); LOAD_FAIL(dalloc(&m->attn, R * m->Hq * D)); LOAD_FAIL(dalloc(&m->proj, R * H));
+  if (d.tp_world > 1) LOAD_FAIL(dalloc(&m->proj_ranks, (size_t)d.tp_world * R * H));
   LOAD_FAIL(dalloc(&m->gu, R * 2 * m->F)); LOAD_FAIL(dalloc(&m->act, R * m->F)); LOAD_FAIL(dalloc(&m->hs, (size_t)m->logit_rows * H));
   LOAD_FAIL(dalloc(&m->logits, (size_t)m->logit_rows * V));
   const char* terr = "";
@@ -1006,12 +1007,14 @@ AttnParams attn_params(kc_model* m, kc_kv* kv, const StepPlan& p, int layer, con
   return a;
 }
 
-// All-reduce of a bf16 [n, H] sublayer output across the tensor-parallel ranks, summed in fp32.
-int tp_allreduce(kc_model* m, bf16* buf, int n) {
-  // bf16 partial sums are exchanged as-is: NCCL reduces bf16 in a fixed ring/tree order per
-  // communicator, so a row's bits do not depend on how many rows are in flight.
-  ncclResult_t r = ncclAllReduce(buf, buf, (size_t)n * m->d.hidden_size, ncclBfloat16, ncclSum, m->ctx->comm, m->ctx->stream);
-  if (r != ncclSuccess) return fail(KC_ERR_CUDA, "ncclAllReduce: %s", ncclGetErrorString(r));
+// Brings every tensor-parallel rank's bf16 [n, H] sublayer output to every rank: out[r] = rank r's rows. The SUM is
+// left to the consumer kernel, which adds the ranks in rank order in fp32 and rounds once. An all-gather only moves
+// bytes, so a row's bits cannot depend on which algorithm the library picks for a message size — a reduction inside
+// the collective did depend on it (speculation on and off disagreed on 6 of 64 sequences of the 70B configuration
+// when the all-reduce's choice differed between 64-row and 320-row messages).
+int tp_allgather(kc_model* m, const bf16* local, bf16* out, int n) {
+  ncclResult_t r = ncclAllGather(local, out, (size_t)n * m->d.hidden_size, ncclBfloat16, m->ctx->comm, m->ctx->stream);
+  if (r != ncclSuccess) return fail(KC_ERR_CUDA, "ncclAllGather: %s", ncclGetErrorString(r));
   return KC_OK;
 }
 
@@ -1037,14 +1040,18 @@ int run_forward(kc_model* m, kc_kv* kv, const uint32_t* tokens_dev, const StepPl
     AttnParams a = attn_params(m, kv, p, l, m->q_rot, m->attn, m->attn_scale, gemma ? d.attn_logit_softcapping : 0.f, window, m->Hq);
     LAUNCH(c, KC_PROF_ATTN, 2, paged_attention(kv->map, a, D, p.tokens_per_item, p.n_work, p.max_chunks, n, c->stream));
     RC(run_qlinear(c, L.o, m->op_attn, n, m->proj, H, m->partial, d.tp_world > 1 ? nullptr : &so));
-    if (d.tp_world > 1) so = SublayerOut::dense(m->proj, H);
-    if (d.tp_world > 1 && (rc = tp_allreduce(m, m->proj, n))) return rc;
+    if (d.tp_world > 1) {
+      if ((rc = tp_allgather(m, m->proj, m->proj_ranks, n))) return rc;
+      so = SublayerOut::of_ranks(m->proj_ranks, d.tp_world, (size_t)n, H);
+    }
     if (gemma) LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, so, L.post_attn_ln, L.pre_ffw_ln, nullptr, n, H, d.rms_norm_eps, m->h, m->normed, c->stream));
     else LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, so, nullptr, L.post_attn_ln, nullptr, n, H, d.rms_norm_eps, m->h, m->normed, c->stream));
     RC(run_gated(c, L.gate_up, m->op_normed, n, m->gu, m->F, gemma ? 1 : 0, m->glu_interleaved, m->act, m->partial));
     RC(run_qlinear(c, L.down, m->op_act, n, m->proj, H, m->partial, d.tp_world > 1 ? nullptr : &so));
-    if (d.tp_world > 1) so = SublayerOut::dense(m->proj, H);
-    if (d.tp_world > 1 && (rc = tp_allreduce(m, m->proj, n))) return rc;
+    if (d.tp_world > 1) {
+      if ((rc = tp_allgather(m, m->proj, m->proj_ranks, n))) return rc;
+      so = SublayerOut::of_ranks(m->proj_ranks, d.tp_world, (size_t)n, H);
+    }
     const bf16* next_ln = l + 1 < d.num_layers ? m->layers[l + 1].input_ln : nullptr;
     LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, so, gemma ? L.post_ffw_ln : nullptr, next_ln, nullptr, n, H, d.rms_norm_eps, m->h, m->normed, c->stream));
   }

@@ -31,7 +31,10 @@ namespace {
 
 // A multiple of every key-split count, so one ring slot is always drained by the same
 // consumer warps and each warp meets a slot's barrier phases strictly in order.
-constexpr int ATT_STAGES = 8;
+#ifndef ATT_RING_STAGES
+#define ATT_RING_STAGES 8
+#endif
+constexpr int ATT_STAGES = ATT_RING_STAGES;
 #ifndef ATT_Q_REGS
 #define ATT_Q_REGS 0
 #endif

@@ -11,6 +11,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdlib.h>
+#include <utility>
 
 #ifndef __CUDA_ARCH_FEAT_SM100_ALL
 #if defined(__CUDA_ARCH__)
@@ -186,17 +187,24 @@ inline bool pdl_enabled() {
 }
 #endif
 
+// allow_early = false launches with plain stream order: used for the first kernel after a collective, whose duration
+// depends on the OTHER ranks — nothing of this library may be resident and counting down a bounded wait meanwhile.
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
+inline cudaError_t launch_k_opt(bool allow_early, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                                Args&&... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = s;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
 #ifndef __CUDA_ARCH__
-  if (pdl_enabled()) { cfg.attrs = attr; cfg.numAttrs = 1; }
+  if (allow_early && pdl_enabled()) { cfg.attrs = attr; cfg.numAttrs = 1; }
 #endif
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
+  return launch_k_opt(true, kernel, grid, block, smem, s, std::forward<Args>(args)...);
 }
 
 // Mlp::forward activation (nn.rs:284-294): silu(gate) * up with the three bf16 roundings of the composed ops, or

@@ -61,6 +61,9 @@ struct RowSource {
   int splits;
   size_t split_stride;  // rows * N
   int ld;               // row pitch in elements (N)
+  const bf16* rank_y;   // per-rank bf16 form [ranks][rows][ld], or null
+  int ranks;
+  size_t rank_stride;
 };
 __device__ __forceinline__ void load8(const RowSource& s, size_t row, int col, float (&v)[8]) {
   if (s.part) {
@@ -73,6 +76,16 @@ __device__ __forceinline__ void load8(const RowSource& s, size_t row, int col, f
     }
     v[0] = bf16_round(a.x); v[1] = bf16_round(a.y); v[2] = bf16_round(a.z); v[3] = bf16_round(a.w);
     v[4] = bf16_round(b.x); v[5] = bf16_round(b.y); v[6] = bf16_round(b.z); v[7] = bf16_round(b.w);
+  } else if (s.rank_y) {
+    // rank order, fp32, one rounding: the same bits whatever collective moved the per-rank outputs here
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < s.ranks; ++r) {
+      const uint4 u = *reinterpret_cast<const uint4*>(s.rank_y + r * s.rank_stride + row * s.ld + col);
+      const float2 a = unpack_bf162(u.x), b = unpack_bf162(u.y), c = unpack_bf162(u.z), d = unpack_bf162(u.w);
+      acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y; acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v[k] = bf16_round(acc[k]);
   } else {
     const uint4 u = *reinterpret_cast<const uint4*>(s.y + row * s.ld + col);
     const float2 a = unpack_bf162(u.x), b = unpack_bf162(u.y), c = unpack_bf162(u.z), d = unpack_bf162(u.w);
@@ -108,7 +121,7 @@ add_rmsnorm_kernel(const bf16* __restrict__ x, RowSource y, const bf16* __restri
   const int row = blockIdx.x;
   const size_t src = row_map ? row_map[row] : row;
   const bf16* xr = x + src * H;
-  const bool has_y = y.y || y.part;
+  const bool has_y = y.y || y.part || y.rank_y;
   float ss = 0.f;
   if (has_y && w_pre) {
     for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
@@ -178,7 +191,7 @@ add_rmsnorm_reg_kernel(const bf16* __restrict__ x, RowSource y, const bf16* __re
   const int row = blockIdx.x;
   const size_t src = row_map ? row_map[row] : row;
   const bf16* xr = x + src * H;
-  const bool has_y = y.y || y.part;
+  const bool has_y = y.y || y.part || y.rank_y;
   float v[CPT][8];
   uint4 xraw[CPT];
 #pragma unroll
@@ -209,7 +222,7 @@ add_rmsnorm_reg_kernel(const bf16* __restrict__ x, RowSource y, const bf16* __re
       }
     } else {
 #pragma unroll
-      for (int c = 0; c < CPT; ++c) load8_bf16(y.y + src * y.ld + (c * 256 + threadIdx.x) * 8, v[c]);
+      for (int c = 0; c < CPT; ++c) load8(y, src, (c * 256 + threadIdx.x) * 8, v[c]);
     }
   }
   float ss = 0.f;
@@ -376,6 +389,7 @@ cudaError_t launch_embed(const uint32_t* w, const bf16* scales, const bf16* bias
 static RowSource row_source(const SublayerOut& y) {
   RowSource r;
   r.y = y.y; r.part = y.part; r.splits = y.splits; r.split_stride = y.split_stride; r.ld = y.ld;
+  r.rank_y = y.rank_y; r.ranks = y.ranks; r.rank_stride = y.rank_stride;
   return r;
 }
 
@@ -385,12 +399,13 @@ cudaError_t launch_add_rmsnorm(const bf16* x, const SublayerOut& y, const bf16* 
   if (rows <= 0) return cudaSuccess;
   if (H % 8) return cudaErrorInvalidValue;
   const bool aligned = !y.part || ((reinterpret_cast<uintptr_t>(y.part) & 15) == 0 && (y.ld & 3) == 0 && (y.split_stride & 3) == 0);
+  const bool early = y.rank_y == nullptr;   // per-rank inputs arrive from a collective: see launch_k_opt
   if (!w_pre && aligned) {
-    if (H == 2048) return launch_k(add_rmsnorm_reg_kernel<1>, dim3(rows), dim3(256), 0, s, x, row_source(y), w_out, row_map, eps, h_out, normed);
-    if (H == 4096) return launch_k(add_rmsnorm_reg_kernel<2>, dim3(rows), dim3(256), 0, s, x, row_source(y), w_out, row_map, eps, h_out, normed);
-    if (H == 8192) return launch_k(add_rmsnorm_reg_kernel<4>, dim3(rows), dim3(256), 0, s, x, row_source(y), w_out, row_map, eps, h_out, normed);
+    if (H == 2048) return launch_k_opt(early, add_rmsnorm_reg_kernel<1>, dim3(rows), dim3(256), 0, s, x, row_source(y), w_out, row_map, eps, h_out, normed);
+    if (H == 4096) return launch_k_opt(early, add_rmsnorm_reg_kernel<2>, dim3(rows), dim3(256), 0, s, x, row_source(y), w_out, row_map, eps, h_out, normed);
+    if (H == 8192) return launch_k_opt(early, add_rmsnorm_reg_kernel<4>, dim3(rows), dim3(256), 0, s, x, row_source(y), w_out, row_map, eps, h_out, normed);
   }
-  return launch_k(add_rmsnorm_kernel, dim3(rows), dim3(256), H * sizeof(float), s, x, row_source(y), w_pre, w_out, row_map, H, eps, h_out, normed);
+  return launch_k_opt(early, add_rmsnorm_kernel, dim3(rows), dim3(256), H * sizeof(float), s, x, row_source(y), w_pre, w_out, row_map, H, eps, h_out, normed);
 }
 
 cudaError_t launch_rope_kv_write(const SublayerOut& qkv, const bf16* bias, const float* inv_freq, const int32_t* token_pos,

@@ -9,13 +9,20 @@ cudaError_t launch_embed(const uint32_t* w, const bf16* scales, const bf16* bias
                          int bits, int group, float embed_scale, int vocab, bf16* out, cudaStream_t s);
 
 // A GEMM output as its consumer reads it: bf16 [rows, ld], or the GEMM's fp32 split-K partials
-// [splits][rows][ld] (summed in split order and rounded to bf16 by the consumer), or nothing.
+// [splits][rows][ld] (summed in split order and rounded to bf16 by the consumer), or the bf16 outputs of the
+// tensor-parallel ranks [ranks][rows][ld] (summed in rank order in fp32 and rounded once by the consumer), or nothing.
 struct SublayerOut {
   const bf16* y = nullptr;
   const float* part = nullptr;
   int splits = 0;
   size_t split_stride = 0;
   int ld = 0;
+  const bf16* rank_y = nullptr;
+  int ranks = 0;
+  size_t rank_stride = 0;
+  static SublayerOut of_ranks(const bf16* rank_y, int ranks, size_t rows, int ld) {
+    SublayerOut s; s.rank_y = rank_y; s.ranks = ranks; s.rank_stride = rows * (size_t)ld; s.ld = ld; return s;
+  }
   static SublayerOut none() { return SublayerOut{}; }
   static SublayerOut dense(const bf16* y, int ld) { SublayerOut s; s.y = y; s.ld = ld; return s; }
   static SublayerOut partials(const float* part, int splits, size_t rows, int ld) {

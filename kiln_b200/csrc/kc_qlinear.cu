@@ -483,22 +483,19 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
       umma_commit(acc_full);
     }
   } else if (warp >= QL_DQ_WARP0) {
-    // ---- dequantisers: thread = (row pair r0 / r0 + 64, chunk pair 2c', 2c' + 1) of every owned tile ----
+    // ---- dequantisers: thread = (row r, half hf of the k-block's 64 features) of every owned tile: one 16- or
+    //      32-byte load of packed weights, one (scale, bias) pair, four 16-byte stores of bf16 ----
     const int td = threadIdx.x - QL_DQ_WARP0 * 32;  // 0..511
     const int grp = td / QL_DQ_GROUP_THREADS;
     const int tg = td - grp * QL_DQ_GROUP_THREADS;  // 0..255 inside the group
-    const int cp = tg & 3, r0 = tg >> 2;            // chunk pair 0..3, row 0..63
-    const int gi = (GPK == 2) ? (cp >> 1) : 0;
+    const int hf = tg & 1, r = tg >> 1;             // half 0..1, row 0..127
+    const int gi = (GPK == 2) ? hf : 0;
     // shared-memory offsets that do not change with the k-block
-    uint32_t a_off[2][2], raw_off[2], sb_off[2];
+    const uint32_t raw_off = r * (QL_KB * BITS / 8) + hf * (QL_KB * BITS / 16);   // 16 (w4) or 32 (w8) bytes per half row
+    const uint32_t sb_off = PACKED + (r * GPK + gi) * 4;
+    uint32_t a_off[4];
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const int r = r0 + 64 * h;
-      raw_off[h] = r * (QL_KB * BITS / 8) + cp * (2 * BITS);          // 8 (w4) or 16 (w8) bytes per chunk pair
-      sb_off[h] = PACKED + (r * GPK + gi) * 4;
-      a_off[h][0] = r * 128 + (((2 * cp) ^ (r & 7)) << 4);
-      a_off[h][1] = r * 128 + (((2 * cp + 1) ^ (r & 7)) << 4);
-    }
+    for (int j = 0; j < 4; ++j) a_off[j] = r * 128 + (((4 * hf + j) ^ (r & 7)) << 4);
     bool ok = true;
     RingPos rp, ap;
     for (int g = 0; g < grp; ++g) { rp.advance(RS); ap.advance(AS); }
@@ -514,20 +511,19 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
         if ((u % NT) < nt_live) {
           const uint8_t* rec = sR + (size_t)rs * r_stage + (size_t)u * p.raw_stride;
           uint8_t* a = sA + (size_t)as * a_stage + (size_t)u * QL_A_BYTES;
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const bf162 sb = *reinterpret_cast<const bf162*>(rec + sb_off[h]);
-            uint4 v0, v1;
-            if (BITS == 4) {
-              const uint2 u = *reinterpret_cast<const uint2*>(rec + raw_off[h]);
-              v0 = dequant8_w4(u.x, sb); v1 = dequant8_w4(u.y, sb);
-            } else {
-              const uint4 u = *reinterpret_cast<const uint4*>(rec + raw_off[h]);
-              v0 = dequant8_w8(u.x, u.y, sb); v1 = dequant8_w8(u.z, u.w, sb);
-            }
-            *reinterpret_cast<uint4*>(a + a_off[h][0]) = v0;
-            *reinterpret_cast<uint4*>(a + a_off[h][1]) = v1;
+          const bf162 sb = *reinterpret_cast<const bf162*>(rec + sb_off);
+          uint4 v[4];
+          if (BITS == 4) {
+            const uint4 q = *reinterpret_cast<const uint4*>(rec + raw_off);
+            v[0] = dequant8_w4(q.x, sb); v[1] = dequant8_w4(q.y, sb); v[2] = dequant8_w4(q.z, sb); v[3] = dequant8_w4(q.w, sb);
+          } else {
+            const uint4 q0 = *reinterpret_cast<const uint4*>(rec + raw_off);
+            const uint4 q1 = *reinterpret_cast<const uint4*>(rec + raw_off + 16);
+            v[0] = dequant8_w8(q0.x, q0.y, sb); v[1] = dequant8_w8(q0.z, q0.w, sb);
+            v[2] = dequant8_w8(q1.x, q1.y, sb); v[3] = dequant8_w8(q1.z, q1.w, sb);
           }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(a + a_off[j]) = v[j];
         }
       }
       fence_proxy_async_smem();
