@@ -486,7 +486,8 @@ def main():
     mean_ctx = w.mean_prompt + gen / 2.0
     alg = algorithmic(w.cfg, batch, k, mean_ctx)
     gemm_ms, gemm_n = prof.get("gemm", (0.0, 0))
-    gemm_tflops = alg["gemm_flops"] / (gemm_ms * 1e-3) / 1e12 if gemm_ms else None
+    # per-GPU rate: under tensor parallelism every rank multiplies 1 / tp of the weights
+    gemm_tflops = alg["gemm_flops"] / w.tp / (gemm_ms * 1e-3) / 1e12 if gemm_ms else None
     p50 = step_ms[len(step_ms) // 2]
     line = {
         "metric": metric, "value": tokens / (dev_ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warmup,
@@ -500,14 +501,14 @@ def main():
         "roofline": {"kernel": "qlinear_umma_kernel (affine-dequant GEMM, tcgen05)", "bound": "tensor",
                      "achieved": gemm_tflops, "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
                      "frac": (gemm_tflops / pk["bf16_tflops_sustained"]) if gemm_tflops else None,
-                     "traffic": (GEMM_DRAM_TRAFFIC_PER_WEIGHT_BYTE * alg["weight_bytes"] / gemm_n) if gemm_n else None,
+                     "traffic": (GEMM_DRAM_TRAFFIC_PER_WEIGHT_BYTE * alg["weight_bytes"] / w.tp / gemm_n) if gemm_n else None,
                      "traffic_unit": "bytes per launch (ncu dram read+write of one launch, scaled by weight bytes)",
-                     "algorithmic_bytes_per_launch": (alg["weight_bytes"] / gemm_n) if gemm_n else None,
+                     "algorithmic_bytes_per_launch": (alg["weight_bytes"] / w.tp / gemm_n) if gemm_n else None,
                      "peak_source": pk["source"] + " (sustained: the kernel runs inside a long step)",
                      "launches_per_step": gemm_n, "ms_per_step": gemm_ms,
-                     "algorithmic_flops_per_launch": alg["gemm_flops"] / gemm_n if gemm_n else None},
+                     "algorithmic_flops_per_launch": alg["gemm_flops"] / w.tp / gemm_n if gemm_n else None},
         "step_roofline": {"bound": "hbm", "algorithmic_bytes_per_step": alg["bytes"], "achieved": alg["bytes"] / (p50 * 1e-3) / 1e9,
-                          "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": alg["bytes"] / (p50 * 1e-3) / 1e9 / pk["hbm_gbs"],
+                          "peak": pk["hbm_gbs"] * w.tp, "unit": "GB/s", "frac": alg["bytes"] / (p50 * 1e-3) / 1e9 / (pk["hbm_gbs"] * w.tp),
                           "frac_of_nominal_8tbs": alg["bytes"] / (p50 * 1e-3) / 8e12, "mean_context": mean_ctx},
         "kernel_classes_ms_per_step": {k2: round(v[0], 4) for k2, v in prof.items()},
         "kernel_classes_launches_per_step": {k2: v[1] for k2, v in prof.items()},

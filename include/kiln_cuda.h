@@ -330,8 +330,10 @@ KC_API int kc_rope_kv_write(kc_ctx_t ctx, kc_kv_t kv, int32_t layer, const void*
 /* ---- tensor parallel (no counterpart in the reference, which has no
  *      collective of any kind: docs/SPEC.md:70-75) ------------------------ */
 
-/* Joins an NCCL communicator of `world` ranks for the all-reduce after o_proj
- * and down_proj. unique_id: the 128 bytes of an ncclUniqueId from rank 0. */
+/* Joins an NCCL communicator of `world` ranks. After o_proj and down_proj the
+ * ranks' bf16 outputs are all-gathered and summed in rank order (fp32, one
+ * rounding) by the next kernel. unique_id: the 128 bytes of an ncclUniqueId
+ * from rank 0. */
 KC_API int kc_tp_init(kc_ctx_t ctx, const void* unique_id, int32_t rank, int32_t world);
 KC_API int kc_tp_unique_id(void* unique_id_out_128);
 
