@@ -298,7 +298,7 @@ struct QlKernelParams {
   int M, m_pad;          // live rows, rows rounded up to 16
   int row0;              // first activation row
   int splits, kb_per_split;
-  int a_stages, r_stages;
+  int a_stages, r_stages, b_stages;   // b_stages: activation ring of the kernel that keeps its A ring in TMEM
   uint32_t raw_stride;   // distance between the records of neighbouring tiles in a raw stage (= record_bytes)
   int b_single;          // 1: the first tensor map's box spans all m_pad rows (one TMA operation per k-block)
   int glu;               // 0, or 1 (silu) / 2 (gelu_approx): the epilogue writes act = activation(gate tile) * up tile
@@ -320,6 +320,87 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr));
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// The epilogue shared by the GEMM kernels: every epilogue warp drains its TMEM lane quarter, 32 columns (rows of the
+// step) at a time, transposes through a private 4 KB shared buffer and stores row-contiguous vectors: bf16 y, fp32
+// split-K partials, or — when the CTA owns (gate, up) tile pairs — the gated activation.
+template <int NT>
+__device__ __forceinline__ void ql_epilogue(const QlKernelParams& p, uint8_t* smem, int warp, int lane, uint32_t tmem_base,
+                                            int tile0, int nt_live, int split) {
+  tc_fence_after();
+  // every MMA has completed and every copy into the rings has been consumed: the ring memory is free
+  float* stage = reinterpret_cast<float*>(smem + (size_t)(warp - QL_DQ_WARP0) * QL_EPI_STAGE_BYTES);
+  const int q = warp & 3;                        // TMEM lane quarter this warp may read
+  const int eg = (warp - QL_DQ_WARP0) >> 2;      // warps of one quarter split the 32-column chunks
+  const int chunks = (p.m_pad + 31) >> 5;
+  const int col_stride = (p.m_pad + 31) & ~31;
+  const bool vec_ok = p.splits == 1 ? ((p.ldy & 3) == 0 && (reinterpret_cast<uintptr_t>(p.y) & 7) == 0)
+                                    : ((p.N & 3) == 0 && (reinterpret_cast<uintptr_t>(p.partial) & 15) == 0);
+  const int nl = 4 * (lane & 7), mr0 = lane >> 3;
+  if (NT >= 2 && p.glu) {
+    // tiles (2 pr, 2 pr + 1) of this CTA are the gate and up halves of features 128 * (tile0 / 2 + pr) ..:
+    // both accumulators' values of a (feature, row) sit in the same thread, 16 rows at a time
+    const int chunks16 = p.m_pad >> 4;
+    for (int item = eg; item < (nt_live >> 1) * chunks16; item += QL_DQ_WARPS / 4) {
+      const int pr = item / chunks16, ch = item - pr * chunks16;
+      uint32_t g[16], u[16];
+      tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (2 * pr) * col_stride + ch * 16, g);
+      tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (2 * pr + 1) * col_stride + ch * 16, u);
+      __syncwarp();
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        const float gv = bf16_round(__uint_as_float(g[j])), uv = bf16_round(__uint_as_float(u[j]));
+        stage[j * 32 + lane] = p.glu == 2 ? act_gelu_mul(gv, uv) : act_silu_mul(gv, uv);
+      }
+      __syncwarp();
+      const int f = ((tile0 >> 1) + pr) * QL_TILE_N + q * 32 + nl;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int mr = 4 * k + mr0;
+        const int m = ch * 16 + mr;
+        if (m >= p.M) continue;
+        const float4 v4 = *reinterpret_cast<const float4*>(stage + mr * 32 + nl);
+        *reinterpret_cast<uint2*>(p.act + (size_t)(p.row0 + m) * p.ld_act + f) =
+            make_uint2(pack_bf162(v4.x, v4.y), pack_bf162(v4.z, v4.w));
+      }
+    }
+  } else
+  for (int item = eg; item < nt_live * chunks; item += QL_DQ_WARPS / 4) {
+    const int t = item / chunks, ch = item - t * chunks;
+    const int col = (NT == 1 ? 0 : t * col_stride) + ch * 32;   // NT == 1: columns are m directly (incl. the 256+ accumulator)
+    uint32_t v[32];
+    tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + col, v);
+    __syncwarp();                                // the previous item's reads of the buffer are done
+#pragma unroll
+    for (int j = 0; j < 32; ++j) stage[j * 32 + lane] = __uint_as_float(v[j]);   // stage[m][n]
+    __syncwarp();
+    const int n = (tile0 + t) * QL_TILE_N + q * 32 + nl;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int mr = 4 * k + mr0;
+      const int m = ch * 32 + mr;
+      if (m >= p.M || n >= p.N) continue;
+      const float4 f = *reinterpret_cast<const float4*>(stage + mr * 32 + nl);
+      if (p.splits == 1) {
+        bf16* dst = p.y + (size_t)(p.row0 + m) * p.ldy + n;
+        if (vec_ok && n + 3 < p.N) {
+          *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf162(f.x, f.y), pack_bf162(f.z, f.w));
+        } else {
+          const float e[4] = {f.x, f.y, f.z, f.w};
+          for (int c = 0; c < 4 && n + c < p.N; ++c) dst[c] = __float2bfloat16_rn(e[c]);
+        }
+      } else {
+        float* dst = p.partial + ((size_t)split * p.M + m) * p.N + n;
+        if (vec_ok && n + 3 < p.N) {
+          *reinterpret_cast<float4*>(dst) = f;
+        } else {
+          const float e[4] = {f.x, f.y, f.z, f.w};
+          for (int c = 0; c < 4 && n + c < p.N; ++c) dst[c] = e[c];
+        }
+      }
+    }
+  }
 }
 
 // BITS: 4 or 8. GPK: scale/bias pairs per row per k-block (1 or 2). NT: 128-row weight tiles per CTA, all
@@ -535,81 +616,237 @@ qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_cons
     // ---- epilogue: TMEM -> per-warp transpose in shared memory -> row-contiguous vector stores ----
     pdl_wait();   // the stores below may overwrite what an earlier kernel still reads
     if (ok) ok = __all_sync(0xffffffffu, mbar_wait(acc_full, 0, p.status, KC_DEV_QLINEAR | 7));
-    if (ok) {
-      tc_fence_after();
-      // every MMA has completed and every copy into the rings has been consumed: the ring memory is free
-      float* stage = reinterpret_cast<float*>(smem + (size_t)(warp - QL_DQ_WARP0) * QL_EPI_STAGE_BYTES);
-      const int q = warp & 3;                        // TMEM lane quarter this warp may read
-      const int eg = (warp - QL_DQ_WARP0) >> 2;      // warps of one quarter split the 32-column chunks
-      const int chunks = (p.m_pad + 31) >> 5;
-      const int col_stride = (p.m_pad + 31) & ~31;
-      const bool vec_ok = p.splits == 1 ? ((p.ldy & 3) == 0 && (reinterpret_cast<uintptr_t>(p.y) & 7) == 0)
-                                        : ((p.N & 3) == 0 && (reinterpret_cast<uintptr_t>(p.partial) & 15) == 0);
-      const int nl = 4 * (lane & 7), mr0 = lane >> 3;
-      if (NT >= 2 && p.glu) {
-        // tiles (2 pr, 2 pr + 1) of this CTA are the gate and up halves of features 128 * (tile0 / 2 + pr) ..:
-        // both accumulators' values of a (feature, row) sit in the same thread, 16 rows at a time
-        const int chunks16 = p.m_pad >> 4;
-        for (int item = eg; item < (nt_live >> 1) * chunks16; item += QL_DQ_WARPS / 4) {
-          const int pr = item / chunks16, ch = item - pr * chunks16;
-          uint32_t g[16], u[16];
-          tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (2 * pr) * col_stride + ch * 16, g);
-          tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (2 * pr + 1) * col_stride + ch * 16, u);
-          __syncwarp();
+    if (ok) ql_epilogue<NT>(p, smem, warp, lane, tmem_base, tile0, nt_live, split);
+  }
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(p.tmem_cols)
+                 : "memory");
+  }
+}
+
+
+// ---------------------------------------------------------------------------
+// The same GEMM with the dequantised weights handed to the tensor core through TENSOR MEMORY instead of shared
+// memory (tcgen05.mma with the A operand in TMEM). Measured reason: an M = 128, N = 192 MMA needs 97 cycles when run
+// alone, but the k-block of the kernel above took ≈ 1140 cycles for eight of them — its 154 KB of shared-memory
+// traffic per k-block (32 KB of bf16 weights written, 32 KB read back by the MMAs, the activation k-block read once
+// per tile, the copies) is what the 128 B/clk shared memory can move in that time. Here a dequantiser thread owns one
+// weight row (= one TMEM lane) of one unit, expands its 64 weights in registers and writes them with one tcgen05.st
+// (column c = weights 2c and 2c + 1), so the MMAs read only the activation k-block from shared memory and the A ring
+// costs no shared memory at all. Units per stage are fixed at two: two tiles of one k-block (NT == 2), or two
+// k-blocks of one tile (NT == 1). Accumulation order per output element is unchanged.
+//
+// TMEM columns: [NT accumulators of round32(m_pad)] [a_stages x 2 units x 32 columns of bf16 pairs].
+// Warp roles as above; warp 3 issues the second tile's MMAs when NT == 2.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo, uint32_t d_hi, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "r"(b_lo), "r"(d_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]),
+        "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]),
+        "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+template <int BITS, int GPK, int NT>
+__global__ void __launch_bounds__(QL_THREADS, 1)
+qlinear_umma_ta_kernel(const __grid_constant__ CUtensorMap map_rows, const QlKernelParams p) {
+  constexpr int KC = NT == 1 ? 2 : 1;
+  constexpr int UNITS = 2;
+  static_assert(NT * KC == UNITS, "two units per stage");
+  constexpr uint32_t PACKED = QL_TILE_N * (QL_KB * BITS / 8);
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int SA = p.a_stages, SB = p.b_stages, RS = p.r_stages;
+  const uint32_t bk_bytes = (uint32_t)p.m_pad * 128u;   // one activation k-block
+  const uint32_t b_stage = KC * bk_bytes;
+  const uint32_t r_stage = UNITS * p.raw_stride;
+  uint8_t* sB = smem;
+  uint8_t* sR = sB + (size_t)SB * b_stage;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sR + (size_t)RS * r_stage);
+  uint64_t* raw_full = bars;
+  uint64_t* raw_empty = raw_full + RS;
+  uint64_t* b_full = raw_empty + RS;
+  uint64_t* b_empty = b_full + SB;
+  uint64_t* a_ready = b_empty + SB;
+  uint64_t* a_empty = a_ready + SA;
+  uint64_t* acc_full = a_empty + SA;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile0 = blockIdx.x * NT, split = blockIdx.y;
+  const int nt_live = min(NT, p.n_tiles - tile0);
+  const int kb0 = split * p.kb_per_split;
+  const int nst = p.kb_per_split / KC;                  // pipeline stages of this CTA
+  const int n_issuers = (NT == 2 && nt_live == 2) ? 2 : 1;
+  const uint32_t col_stride = (uint32_t)(p.m_pad + 31) & ~31u;
+  const uint32_t a_col0 = NT * col_stride;              // first column of the A ring
+
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < RS; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], QL_DQ_GROUP_WARPS); }
+    for (int i = 0; i < SB; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], n_issuers); }
+    for (int i = 0; i < SA; ++i) { mbar_init(&a_ready[i], QL_DQ_GROUP_WARPS); mbar_init(&a_empty[i], n_issuers); }
+    mbar_init(acc_full, n_issuers);
+    mbar_fence_init();
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(p.tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  if (warp == 1 && lane == 0) tma_prefetch_desc(&map_rows);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  bool ok = true;
+
+  if (warp == 0) {
+    // ---- weight record producer ----
+    if (lane == 0) {
+      RingPos rp;
+      for (int i = 0; i < nst; ++i, rp.advance(RS)) {
+        if (!mbar_wait(&raw_empty[rp.stage], rp.phase ^ 1, p.status, KC_DEV_QLINEAR | 1)) { ok = false; break; }
+        mbar_arrive_expect_tx(&raw_full[rp.stage], p.record_bytes * nt_live * KC);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const float gv = bf16_round(__uint_as_float(g[j])), uv = bf16_round(__uint_as_float(u[j]));
-            stage[j * 32 + lane] = p.glu == 2 ? act_gelu_mul(gv, uv) : act_silu_mul(gv, uv);
-          }
-          __syncwarp();
-          const int f = ((tile0 >> 1) + pr) * QL_TILE_N + q * 32 + nl;
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const int mr = 4 * k + mr0;
-            const int m = ch * 16 + mr;
-            if (m >= p.M) continue;
-            const float4 v4 = *reinterpret_cast<const float4*>(stage + mr * 32 + nl);
-            *reinterpret_cast<uint2*>(p.act + (size_t)(p.row0 + m) * p.ld_act + f) =
-                make_uint2(pack_bf162(v4.x, v4.y), pack_bf162(v4.z, v4.w));
-          }
-        }
-      } else
-      for (int item = eg; item < nt_live * chunks; item += QL_DQ_WARPS / 4) {
-        const int t = item / chunks, ch = item - t * chunks;
-        const int col = (NT == 1 ? 0 : t * col_stride) + ch * 32;   // NT == 1: columns are m directly (incl. the 256+ accumulator)
-        uint32_t v[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + col, v);
-        __syncwarp();                                // the previous item's reads of the buffer are done
-#pragma unroll
-        for (int j = 0; j < 32; ++j) stage[j * 32 + lane] = __uint_as_float(v[j]);   // stage[m][n]
-        __syncwarp();
-        const int n = (tile0 + t) * QL_TILE_N + q * 32 + nl;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const int mr = 4 * k + mr0;
-          const int m = ch * 32 + mr;
-          if (m >= p.M || n >= p.N) continue;
-          const float4 f = *reinterpret_cast<const float4*>(stage + mr * 32 + nl);
-          if (p.splits == 1) {
-            bf16* dst = p.y + (size_t)(p.row0 + m) * p.ldy + n;
-            if (vec_ok && n + 3 < p.N) {
-              *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf162(f.x, f.y), pack_bf162(f.z, f.w));
-            } else {
-              const float e[4] = {f.x, f.y, f.z, f.w};
-              for (int c = 0; c < 4 && n + c < p.N; ++c) dst[c] = __float2bfloat16_rn(e[c]);
-            }
-          } else {
-            float* dst = p.partial + ((size_t)split * p.M + m) * p.N + n;
-            if (vec_ok && n + 3 < p.N) {
-              *reinterpret_cast<float4*>(dst) = f;
-            } else {
-              const float e[4] = {f.x, f.y, f.z, f.w};
-              for (int c = 0; c < 4 && n + c < p.N; ++c) dst[c] = e[c];
-            }
-          }
-        }
+        for (int kc = 0; kc < KC; ++kc)
+          bulk_g2s(sR + (size_t)rp.stage * r_stage + (size_t)kc * NT * p.raw_stride,
+                   p.records + (((size_t)(tile0 / QL_TILE_GROUP) * p.kblocks + kb0 + i * KC + kc) * QL_TILE_GROUP + tile0 % QL_TILE_GROUP) * p.record_bytes,
+                   p.record_bytes * nt_live, &raw_full[rp.stage]);
       }
     }
+  } else if (warp == 1) {
+    // ---- activation producer: the first access of this kernel to memory written by earlier kernels ----
+    if (lane == 0) {
+      pdl_wait();
+      RingPos bp;
+      for (int i = 0; i < nst; ++i, bp.advance(SB)) {
+        if (!mbar_wait(&b_empty[bp.stage], bp.phase ^ 1, p.status, KC_DEV_QLINEAR | 2)) { ok = false; break; }
+        mbar_arrive_expect_tx(&b_full[bp.stage], b_stage);
+#pragma unroll
+        for (int kc = 0; kc < KC; ++kc)
+          tma_load_2d(sB + (size_t)bp.stage * b_stage + (size_t)kc * bk_bytes, &map_rows, (kb0 + i * KC + kc) * QL_KB, p.row0,
+                      &b_full[bp.stage]);
+      }
+    }
+  } else if (warp == 2 || warp == 3) {
+    // ---- MMA issuers: warp 2 takes unit 0 (and unit 1 when both units feed one accumulator), warp 3 the second tile ----
+    const bool mine0 = warp == 2;
+    const bool mine1 = NT == 1 ? warp == 2 : (warp == 3 && nt_live == 2);
+    if (lane == 0 && (mine0 || mine1)) {
+      const uint32_t idesc = umma_idesc_bf16(QL_TILE_N, p.m_pad);
+      const uint64_t proto = umma_smem_desc_sw128(0);
+      const uint32_t d_hi = (uint32_t)(proto >> 32), d_lo = (uint32_t)proto;
+      const uint32_t b_lo0 = d_lo | ((smem_u32(sB) >> 4) & 0x3FFF);
+      const uint32_t b_step = b_stage >> 4;
+      uint32_t acc = 0;
+      RingPos ap, bp;
+      for (int i = 0; i < nst; ++i, ap.advance(SA), bp.advance(SB)) {
+        if (!mbar_wait(&a_ready[ap.stage], ap.phase, p.status, KC_DEV_QLINEAR | 3)) { ok = false; break; }
+        if (!mbar_wait(&b_full[bp.stage], bp.phase, p.status, KC_DEV_QLINEAR | 4)) { ok = false; break; }
+        tc_fence_after();   // the A operand was written with tcgen05.st by other threads
+        const uint32_t b_lo = b_lo0 + bp.stage * b_step;
+        const uint32_t a_t = tmem_base + a_col0 + ap.stage * (UNITS * 32);
+#pragma unroll
+        for (int u = 0; u < UNITS; ++u) {
+          if (u == 0 ? mine0 : mine1) {
+            const int t = NT == 2 ? u : 0, kc = NT == 2 ? 0 : u;
+            const uint32_t b_u = b_lo + kc * (bk_bytes >> 4);
+#pragma unroll
+            for (int ks = 0; ks < QL_KB / 16; ++ks)
+              umma_bf16_ts(tmem_base + t * col_stride, a_t + u * 32 + 8 * ks, b_u + 2 * ks, d_hi, idesc,
+                           (NT == 1 && u == 1) ? 1u : (ks == 0 ? acc : 1u));
+          }
+        }
+        acc = 1u;
+        umma_commit(&a_empty[ap.stage]);
+        umma_commit(&b_empty[bp.stage]);
+      }
+      umma_commit(acc_full);
+    }
+  } else {
+    // ---- dequantisers: thread = one weight row (TMEM lane 32 * (warp % 4) + lane) of one unit ----
+    const int td = threadIdx.x - QL_DQ_WARP0 * 32;  // 0..511
+    const int grp = td / QL_DQ_GROUP_THREADS;
+    const int wj = (warp - QL_DQ_WARP0) & 7;        // warp inside the group; (wj & 3) == (warp & 3): the lane quarter
+    const int unit = wj >> 2;
+    const int row = (wj & 3) * 32 + lane;
+    const bool live = NT == 1 || unit < nt_live;
+    const uint32_t raw_off = (uint32_t)unit * p.raw_stride + row * (QL_KB * BITS / 8);
+    const uint32_t sb_off = (uint32_t)unit * p.raw_stride + PACKED + row * GPK * 4;
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    RingPos rp, ap;
+    for (int g = 0; g < grp; ++g) { rp.advance(RS); ap.advance(SA); }
+    for (int i = grp; i < nst && ok; i += QL_DQ_GROUPS) {
+      ok = __all_sync(0xffffffffu, mbar_wait(&raw_full[rp.stage], rp.phase, p.status, KC_DEV_QLINEAR | 5));
+      if (!ok) break;
+      uint32_t v[32];
+      if (live) {
+        const uint8_t* rec = sR + (size_t)rp.stage * r_stage;
+        bf162 sb[GPK];
+#pragma unroll
+        for (int g = 0; g < GPK; ++g) sb[g] = *reinterpret_cast<const bf162*>(rec + sb_off + g * 4);
+        if (BITS == 4) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const uint4 q = *reinterpret_cast<const uint4*>(rec + raw_off + h * 16);
+            const uint32_t w4[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              const uint4 o = dequant8_w4(w4[c], sb[GPK == 2 ? h : 0]);
+              v[(h * 4 + c) * 4 + 0] = o.x; v[(h * 4 + c) * 4 + 1] = o.y; v[(h * 4 + c) * 4 + 2] = o.z; v[(h * 4 + c) * 4 + 3] = o.w;
+            }
+          }
+        } else {
+#pragma unroll
+          for (int h = 0; h < 4; ++h) {
+            const uint4 q = *reinterpret_cast<const uint4*>(rec + raw_off + h * 16);
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+              const uint4 o = dequant8_w8(c ? q.z : q.x, c ? q.w : q.y, sb[GPK == 2 ? (h >> 1) : 0]);
+              v[(h * 2 + c) * 4 + 0] = o.x; v[(h * 2 + c) * 4 + 1] = o.y; v[(h * 2 + c) * 4 + 2] = o.z; v[(h * 2 + c) * 4 + 3] = o.w;
+            }
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = 0u;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&raw_empty[rp.stage]);   // the record is in registers: its slot can refill
+      ok = __all_sync(0xffffffffu, mbar_wait(&a_empty[ap.stage], ap.phase ^ 1, p.status, KC_DEV_QLINEAR | 6));
+      if (!ok) break;
+      tc_fence_after();
+      tmem_st32(tmem_base + lane_addr + a_col0 + ap.stage * (UNITS * 32) + unit * 32, v);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&a_ready[ap.stage]);
+#pragma unroll
+      for (int g = 0; g < QL_DQ_GROUPS; ++g) { rp.advance(RS); ap.advance(SA); }
+    }
+    // ---- epilogue ----
+    pdl_wait();   // the stores below may overwrite what an earlier kernel still reads
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(acc_full, 0, p.status, KC_DEV_QLINEAR | 7));
+    if (ok) ql_epilogue<NT>(p, smem, warp, lane, tmem_base, tile0, nt_live, split);
   }
   __syncwarp();
   tc_fence_before();
@@ -657,6 +894,45 @@ static cudaError_t launch_umma(const QLinearLaunch& l, QlKernelParams& p, cudaSt
   return launch_k(qlinear_umma_kernel<BITS, GPK, NT, KC>, grid, dim3(QL_THREADS), smem, s, *first, l.x->map64, p);
 }
 
+// Launch of the kernel that keeps its A ring in tensor memory. Returns cudaErrorNotSupported when the geometry does not
+// fit (the caller then uses the shared-memory kernel).
+template <int BITS, int GPK, int NT>
+static cudaError_t launch_umma_ta(const QLinearLaunch& l, QlKernelParams& p, cudaStream_t s) {
+  constexpr int KC = NT == 1 ? 2 : 1;
+  const QWeight& w = *l.w;
+  const int col_stride = (p.m_pad + 31) & ~31;
+  const int acc_cols = NT * col_stride;
+  int sa = (512 - acc_cols) / 64;            // two units of 32 columns per stage
+  if (sa > 4) sa = 4;
+  if (sa < 2 || p.m_pad > 256 || p.kb_per_split % KC) return cudaErrorNotSupported;
+  uint32_t cols = 32;
+  while ((int)cols < acc_cols + sa * 64) cols <<= 1;
+  p.tmem_cols = cols;
+  const size_t budget = (size_t)212 * 1024;
+  const size_t b_stage = (size_t)KC * p.m_pad * 128;
+  const size_t rstage = (size_t)2 * p.raw_stride;
+  int sb = (int)std::min<size_t>(4, (budget - 6 * rstage) / b_stage);
+  if (sb < 2) return cudaErrorNotSupported;
+  int rs = (int)std::min<size_t>(24, (budget - (size_t)sb * b_stage) / rstage);
+  if (rs < 3) return cudaErrorNotSupported;
+  // the epilogue's per-warp transpose buffers reuse the ring memory from its start
+  while ((size_t)sb * b_stage + (size_t)rs * rstage < (size_t)QL_DQ_WARPS * QL_EPI_STAGE_BYTES) ++rs;
+  p.a_stages = sa; p.b_stages = sb; p.r_stages = rs;
+  const size_t smem = 1024 + (size_t)sb * b_stage + (size_t)rs * rstage + (2 * rs + 2 * sb + 2 * sa + 1) * 8 + 16;
+  if (smem > 227 * 1024) return cudaErrorNotSupported;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(qlinear_umma_ta_kernel<BITS, GPK, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  const CUtensorMap* rows = act_operand_rows_map(l.x, p.m_pad);
+  if (!rows) return cudaErrorInvalidValue;
+  p.b_single = 1;
+  dim3 grid((w.n_tiles + NT - 1) / NT, w.splits);
+  return launch_k(qlinear_umma_ta_kernel<BITS, GPK, NT>, grid, dim3(QL_THREADS), smem, s, *rows, p);
+}
+
 // Two A/B stages and three raw stages of the given geometry within the shared-memory budget?
 static bool ql_fits(int nt, int kc, int m_pad, uint32_t raw_stride) {
   const size_t ab = (size_t)kc * ((size_t)nt * QL_A_BYTES + (size_t)m_pad * 128);
@@ -666,6 +942,15 @@ static bool ql_fits(int nt, int kc, int m_pad, uint32_t raw_stride) {
 
 template <int BITS, int GPK>
 static cudaError_t launch_umma_nt(const QLinearLaunch& l, QlKernelParams& p, int nt, cudaStream_t s) {
+  // first choice: the kernel with its A ring in tensor memory (two tiles per CTA up to 192 rows, else one tile with two
+  // k-blocks per stage up to 256 rows); its launcher declines geometries that do not fit
+  if (nt >= 2 && p.m_pad <= 192) {
+    const cudaError_t e = launch_umma_ta<BITS, GPK, 2>(l, p, s);
+    if (e != cudaErrorNotSupported) return e;
+  } else if (nt == 1 && p.m_pad <= 256) {
+    const cudaError_t e = launch_umma_ta<BITS, GPK, 1>(l, p, s);
+    if (e != cudaErrorNotSupported) return e;
+  }
   switch (nt) {   // the caller has lowered nt until its stages fit shared memory (wide 8-bit records, many rows)
     case 4: return launch_umma<BITS, GPK, 4, 1>(l, p, s);
     case 2: return launch_umma<BITS, GPK, 2, 1>(l, p, s);
