@@ -133,10 +133,10 @@ def algorithmic(cfg, batch, k, mean_ctx):
 
 # DRAM traffic of the dominant kernel (the quantised GEMM) relative to its algorithmic weight bytes, from one ncu
 # capture of a single launch larger than L2 (out 128256 x in 4096, 192 rows; summary committed under profiles/):
-# dram__bytes_read.sum + dram__bytes_write.sum = 300.3 MB + 33.6 MB for 295.5 MB of weight records. The traffic of a
+# dram__bytes_read.sum + dram__bytes_write.sum = 299.9 MB + 33.6 MB for 295.5 MB of weight records. The traffic of a
 # launch grows in proportion to its weight bytes, so the per-launch figure reported is this ratio times the mean
 # algorithmic weight bytes per GEMM launch of the step.
-GEMM_DRAM_TRAFFIC_PER_WEIGHT_BYTE = (300.3 + 33.6) / 295.5
+GEMM_DRAM_TRAFFIC_PER_WEIGHT_BYTE = (299.9 + 33.6) / 295.5
 
 # --------------------------------------------------------------------------------------
 # GPU arm
@@ -498,7 +498,7 @@ def main():
                 "h2d_bytes_per_step": int(batch * (k + 1) * 4 * 4 + batch * (mean_ctx / 16 + 2) * 4 + batch * 16 + batch * 12 + batch * (k + 1) * 8),
                 "d2h_bytes_per_step": int(batch * (k + 1) * 4 + batch * 8)},
         "gpu_launches": int(launches_per_step * steps),
-        "roofline": {"kernel": "qlinear_umma_kernel (affine-dequant GEMM, tcgen05)", "bound": "tensor",
+        "roofline": {"kernel": "qlinear_umma_ta_kernel (affine-dequant GEMM, tcgen05, A operand in TMEM)", "bound": "tensor",
                      "achieved": gemm_tflops, "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
                      "frac": (gemm_tflops / pk["bf16_tflops_sustained"]) if gemm_tflops else None,
                      "traffic": (GEMM_DRAM_TRAFFIC_PER_WEIGHT_BYTE * alg["weight_bytes"] / w.tp / gemm_n) if gemm_n else None,

@@ -4,8 +4,10 @@
     python -m kiln_b200.opbench attention --seqs 32 --context 1400 --rows 6 [--heads 32 --kv-heads 8 --head-dim 128]
 
 Each call warms up, then times `iters` back-to-back launches and prints one line with the mean duration and
-the algorithmic throughput (weights read once / K+V read once per sequence). Inputs are synthetic and larger
-than L2 for the default sizes. `--iters 1 --warmup 1` gives a short run suitable for a profiler.
+the algorithmic throughput (weights read once / K+V read once per sequence). Inputs are synthetic. The qlinear
+bench rotates over `--copies` separate copies of the weight (default: enough that they total more than twice the
+126 MB L2), so that every launch streams its weights from HBM as it does inside a decode step; `--copies 1` times
+the L2-resident case. `--iters 1 --warmup 1 --copies 1` gives a short run suitable for a profiler.
 """
 from __future__ import annotations
 
@@ -32,27 +34,29 @@ def bench_qlinear(args) -> dict:
     p, s, b = quantize_affine(w, args.bits, args.group)
     reps = -(-n // base_rows)
     p, s, b = (t.repeat(reps, 1)[:n].contiguous() for t in (p, s, b))
-    qw = api.QuantizedWeight(ctx, p, s, b, args.bits, args.group)
+    wbytes = n * k * args.bits / 8 + n * (k // args.group) * 4
+    copies = args.copies if args.copies > 0 else max(1, int(2 * 126e6 // wbytes) + 1)
+    qws = [api.QuantizedWeight(ctx, p, s, b, args.bits, args.group) for _ in range(copies)]
     m = args.rows
     x = torch.randn((m + 15) // 16 * 16, k, device="cuda").to(torch.bfloat16)
     y = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
     torch.cuda.synchronize()
     lib = L.lib()
-    for _ in range(args.warmup):
-        api.check(lib.kc_quantized_matmul(ctx._h, qw._h, x.data_ptr(), m, y.data_ptr()))
+    for i in range(max(args.warmup, copies)):
+        api.check(lib.kc_quantized_matmul(ctx._h, qws[i % copies]._h, x.data_ptr(), m, y.data_ptr()))
     ctx.sync()
     stream, e0, e1 = _events(ctx)
     e0.record(stream)
-    for _ in range(args.iters):
-        api.check(lib.kc_quantized_matmul(ctx._h, qw._h, x.data_ptr(), m, y.data_ptr()))
+    for i in range(args.iters):
+        api.check(lib.kc_quantized_matmul(ctx._h, qws[i % copies]._h, x.data_ptr(), m, y.data_ptr()))
     e1.record(stream)
     ctx.sync()
     us = e0.elapsed_time(e1) * 1e3 / args.iters
     flops = 2.0 * m * n * k
-    wbytes = n * k * args.bits / 8 + n * (k // args.group) * 4
-    out = {"op": "qlinear", "N": n, "K": k, "rows": m, "bits": args.bits, "group": args.group, "us": us,
+    out = {"op": "qlinear", "N": n, "K": k, "rows": m, "bits": args.bits, "group": args.group, "copies": copies, "us": us,
            "tflops": flops / us / 1e6, "weight_gbs": wbytes / us / 1e3}
-    qw.close()
+    for qw in qws:
+        qw.close()
     return out
 
 
@@ -110,6 +114,7 @@ def main(argv=None):
     a.add_argument("--rows", type=int, default=192)
     a.add_argument("--bits", type=int, default=4)
     a.add_argument("--group", type=int, default=64)
+    a.add_argument("--copies", type=int, default=0, help="separate weight copies to rotate over (0: more than 2 x L2 in total)")
     b = sub.add_parser("attention")
     b.add_argument("--seqs", type=int, default=32)
     b.add_argument("--context", type=int, default=1400)
@@ -119,7 +124,7 @@ def main(argv=None):
     b.add_argument("--head-dim", type=int, default=128)
     b.add_argument("--ragged", action="store_true", help="contexts uniform in [context/2, 3*context/2]")
     for s in (a, b):
-        s.add_argument("--iters", type=int, default=20)
+        s.add_argument("--iters", type=int, default=40)
         s.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args(argv)
     r = bench_qlinear(args) if args.op == "qlinear" else bench_attention(args)
