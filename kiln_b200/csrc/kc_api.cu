@@ -30,6 +30,8 @@ using namespace kc;
 namespace kc {
 bool make_tmap_bf16_2d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint32_t box_inner,
                        uint32_t box_outer, const char** err);
+bool make_tmap_kv_4d(CUtensorMap* map, const void* pool, uint32_t head_dim, uint64_t plane_rows, uint64_t planes,
+                     const char** err);
 }
 
 // ---------------------------------------------------------------------------
@@ -115,7 +117,8 @@ struct kc_kv {
   bf16* pool = nullptr;        // [layers][2][num_blocks][kv_heads][block_size][head_dim]
   size_t block_elems = 0;      // kv_heads * block_size * head_dim
   size_t bytes = 0;
-  CUtensorMap map;             // all pool rows x head_dim, box {64, 16}, 128-byte swizzle
+  CUtensorMap map;             // all pool rows x head_dim, box {64, 16}, 128-byte swizzle; or, with map4d, the 4-D
+  bool map4d = false;          // map whose box is the K and the V tile of a layer (make_tmap_kv_4d)
 };
 
 struct kc_qweight {
@@ -319,7 +322,11 @@ extern "C" int kc_kv_create(kc_ctx_t c, int32_t layers, int32_t kv_heads, int32_
   if (e != cudaSuccess) { delete kv; return fail(KC_ERR_OOM, "kc_kv_create: %zu bytes: %s", kv->bytes, cudaGetErrorString(e)); }
   e = cudaMemsetAsync(kv->pool, 0, kv->bytes, c->stream);
   const char* terr = "";
-  if (e != cudaSuccess || !make_tmap_bf16_2d(&kv->map, kv->pool, head_dim, rows, 64, 16, &terr)) {
+  if (e == cudaSuccess && !getenv("KILN_KV_MAP_2D")) {   // KILN_KV_MAP_2D=1 keeps the 2-D map (4 operations per tile pair)
+    const char* e4 = "";
+    kv->map4d = make_tmap_kv_4d(&kv->map, kv->pool, head_dim, (uint64_t)num_blocks * kv_heads * block_size, (uint64_t)layers * 2, &e4);
+  }
+  if (e != cudaSuccess || (!kv->map4d && !make_tmap_bf16_2d(&kv->map, kv->pool, head_dim, rows, 64, 16, &terr))) {
     cudaFree(kv->pool); delete kv;
     return fail(KC_ERR_CUDA, "kc_kv_create: %s", e != cudaSuccess ? cudaGetErrorString(e) : terr);
   }
@@ -1004,6 +1011,7 @@ AttnParams attn_params(kc_model* m, kc_kv* kv, const StepPlan& p, int layer, con
   a.max_chunks = p.max_chunks; a.chunk_lo_grid = 0;
   a.scale = scale; a.softcap = softcap; a.window = window;
   a.pool = kv->pool;
+  a.kv4d = kv->map4d ? 1 : 0;
   return a;
 }
 

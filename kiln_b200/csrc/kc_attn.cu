@@ -140,7 +140,7 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap kvmap, const AttnParams 
   __syncthreads();
 
   if (warp == CW) {
-    // ---- producer: one TMA per 64-feature slab of a K or V tile. The chunk's block-table entries (at most
+    // ---- producer: one TMA per K+V tile pair (4-D map), or one per 64-feature slab of a K or V tile (2-D map). The chunk's block-table entries (at most
     //      ATT_CHUNK / 16 = 32) are fetched once, one per lane, so the per-tile loop has no global load in it ----
     if (lane == 0) tma_prefetch_desc(&kvmap);
     const int32_t* tbl = p.block_tables + (size_t)seq * p.max_blocks;
@@ -160,10 +160,15 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap kvmap, const AttnParams 
         const long long rowV = ((((long long)p.layer * 2 + 1) * p.NB + blk) * p.Hkv + kvh) * p.BS + in_blk;
         mbar_arrive_expect_tx(&full[st], S::STAGE_BYTES);
         uint8_t* dst = ring + (size_t)st * S::STAGE_BYTES;
+        if (p.kv4d) {
+          // one operation: K slabs then V slabs, the layout of the loads below
+          tma_load_4d(dst, &kvmap, 0, (blk * p.Hkv + kvh) * p.BS + in_blk, 0, p.layer * 2, &full[st]);
+        } else {
 #pragma unroll
-        for (int h = 0; h < D / 64; ++h) {
-          tma_load_2d(dst + h * 2048, &kvmap, h * 64, (int)rowK, &full[st]);
-          tma_load_2d(dst + S::TILE_BYTES + h * 2048, &kvmap, h * 64, (int)rowV, &full[st]);
+          for (int h = 0; h < D / 64; ++h) {
+            tma_load_2d(dst + h * 2048, &kvmap, h * 64, (int)rowK, &full[st]);
+            tma_load_2d(dst + S::TILE_BYTES + h * 2048, &kvmap, h * 64, (int)rowV, &full[st]);
+          }
         }
       }
     }

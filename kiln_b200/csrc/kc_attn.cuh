@@ -30,13 +30,14 @@ struct AttnParams {
   float softcap;               // 0 = off
   int window;                  // 0 = global
   const bf16* pool;            // K/V pools: [layers][2][NB][Hkv][BS][head_dim]
+  int kv4d;                    // kvmap is the 4-D map (one operation per K+V tile pair) instead of the 2-D one
 };
 
 // Tokens of one sequence that share a CTA (their rows x gqa must fit 64 rows).
 int attn_tokens_per_item(int gqa, int max_len);
 
-// kvmap: 2-D tensor map over all pool rows ([layers*2*NB*Hkv*BS, D] bf16, box {64, 16},
-// 128-byte swizzle). n_work CTAs in z, grid_chunks in x.
+// kvmap: 2-D tensor map over all pool rows ([layers*2*NB*Hkv*BS, D] bf16, box {64, 16}, 128-byte swizzle), or, with
+// p.kv4d, the 4-D map of make_tmap_kv_4d. n_work CTAs in z, grid_chunks in x.
 cudaError_t paged_attention(const CUtensorMap& kvmap, const AttnParams& p, int head_dim, int tokens_per_item,
                             int n_work, int grid_chunks, int n_tokens, cudaStream_t s);
 

@@ -140,6 +140,15 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* t
       "l"(tmap), "r"(smem_u32(bar)), "r"(x), "r"(y)
       : "memory");
 }
+// 4-D tiled TMA load (no multicast): coordinates {x = innermost, y, z, w}; x * element size a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* tmap, int32_t x, int32_t y, int32_t z,
+                                            int32_t w, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];" ::
+          "r"(smem_u32(smem_dst)),
+      "l"(tmap), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
+      : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }

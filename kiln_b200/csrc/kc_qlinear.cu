@@ -154,6 +154,26 @@ bool make_tmap_bf16_2d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64
   return true;
 }
 
+// K/V pools [planes = layers * 2][plane_rows = NB * Hkv * BS][head_dim] bf16 as a 4-D tensor
+// {64 features, plane_rows, head_dim / 64 slabs, planes} with box {64, 16, head_dim / 64, 2}: ONE operation brings the
+// 16-key K tile and the V tile of a layer (plane 2 * layer and the next), each as head_dim / 64 slabs of [16][128 B]
+// with the 128-byte swizzle — the shared-memory image of 2 * head_dim / 64 separate 2-D loads. The slab stride
+// (128 B) is smaller than the row stride, which the encoder may refuse: the caller then keeps the 2-D map.
+bool make_tmap_kv_4d(CUtensorMap* map, const void* pool, uint32_t head_dim, uint64_t plane_rows, uint64_t planes,
+                     const char** err) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) { *err = "cuTensorMapEncodeTiled entry point unavailable"; return false; }
+  cuuint64_t dims[4] = {64, plane_rows, head_dim / 64, planes};
+  cuuint64_t strides[3] = {head_dim * sizeof(bf16), 128, plane_rows * head_dim * sizeof(bf16)};
+  cuuint32_t box[4] = {64, 16, head_dim / 64, 2};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(pool), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);   // head_dim >= 128: a key's row is 256 B or more, both slabs of it in one L2 fill
+  if (r != CUDA_SUCCESS) { *err = "cuTensorMapEncodeTiled rejected the 4-D K/V geometry"; return false; }
+  return true;
+}
+
 // The map whose box covers `m_pad` rows (<= 256), so that one TMA operation brings a whole activation k-block.
 // Re-encoded only when the row count changes (a host-side encode, no device work).
 static const CUtensorMap* act_operand_rows_map(const ActOperand* op, int m_pad) {
