@@ -50,6 +50,9 @@ WORKLOADS = {
     # SAME requests (strong scaling); on one GPU it runs unsharded
     "llama-3-70b-w4g64-verify-k4-bs64-tp": ("llama-3-70b", 64, 4, 1024, 4096, 256, {"tp": True}),
     "llama-3.1-8b-w4g64-verify-k5-bs32-tp": ("llama-3.1-8b", 32, 5, 512, 2048, 256, {"tp": True}),
+    # the 70B configuration's batch, k and prompt lengths (320 rows per step: two row chunks per GEMM) on the 8B model
+    "llama-3.1-8b-w4g64-verify-k4-bs64-tp": ("llama-3.1-8b", 64, 4, 1024, 4096, 256, {"tp": True}),
+    "llama-3-70b-8l-w4g64-verify-k4-bs64-tp": ("llama-3-70b-8l", 64, 4, 1024, 4096, 256, {"tp": True}),
     "tiny-llama-verify-k4-bs4": ("tiny-llama", 4, 4, 40, 90, 48),
 }
 METRIC = "verified tok/s/GPU, Llama-3-8B w4g64 k=5 bs32; p50 verify-step ms"

@@ -136,6 +136,8 @@ PRESETS: Dict[str, ModelConfig] = {
     "gemma-2-9b": ModelConfig("gemma2", 3584, 42, 16, 8, 256, 14336, 256000, 4, 128, 1e-6, 10000.0, False, None, True,
                               50.0, 30.0, 256.0, 4096),
     "llama-3-70b": ModelConfig("llama", 8192, 80, 64, 8, 128, 28672, 128256, 4, 64, 1e-5, 500000.0, False, None, False),
+    # the 70B layer shapes with 8 of the 80 layers: a tensor-parallel parity case that loads in seconds
+    "llama-3-70b-8l": ModelConfig("llama", 8192, 8, 64, 8, 128, 28672, 128256, 4, 64, 1e-5, 500000.0, False, None, False),
     # small shapes for parity tests (every code path of the big ones, seconds on one CPU core)
     "tiny-llama": ModelConfig("llama", 256, 2, 8, 2, 64, 512, 1024, 4, 64, 1e-5, 500000.0, False, _LLAMA3_SCALING, True),
     "tiny-llama-d128": ModelConfig("llama", 512, 2, 4, 1, 128, 1024, 2048, 4, 64, 1e-5, 10000.0, False, None, False),
