@@ -103,3 +103,24 @@ def test_verify_rows_carry_decode_bits(ctx, hd, heads, kvh, bs):
             assert torch.equal(one.view(torch.int16), batched[row:row + 1].view(torch.int16)), \
                 f"offset {s.offset} row {j}: verify row differs from decode row"
             row += 1
+
+
+@pytest.mark.parametrize("hd,heads,kvh,bs,layers", [(128, 8, 2, 16, 3), (64, 8, 2, 32, 2), (256, 4, 2, 16, 2)])
+def test_one_operation_per_tile_pair_matches_the_slab_loads(ctx, monkeypatch, hd, heads, kvh, bs, layers):
+    """A pool created with KILN_KV_MAP_2D=1 is read with one TMA operation per 64-feature slab of a K or V tile, the
+    default with one 4-D operation per K+V tile pair: the same shared-memory image, so the same bits, in every layer."""
+    segs = [(6, 40), (1, 511), (6, 1020), (5, 7)]
+    nb = sum((off + ln + bs - 1) // bs for ln, off in segs) + 2
+    spec = api.KvSpec(layers, kvh, hd, nb, bs)
+    kv4, _ = fill_pools(ctx, spec, 31)
+    monkeypatch.setenv("KILN_KV_MAP_2D", "1")
+    kv2, _ = fill_pools(ctx, spec, 31)
+    monkeypatch.delenv("KILN_KV_MAP_2D")
+    seqs = build_seqs(segs, bs, nb, 6)
+    n = sum(s.len for s in seqs)
+    q = outlier_values((n, heads, hd), 12).cuda()
+    for layer in range(layers):
+        a = api.paged_attention(ctx, kv4, layer, q, seqs, hd ** -0.5).cpu()
+        b = api.paged_attention(ctx, kv2, layer, q, seqs, hd ** -0.5).cpu()
+        assert torch.equal(a.view(torch.int16), b.view(torch.int16)), f"layer {layer}"
+    assert ctx.device_status() == 0
