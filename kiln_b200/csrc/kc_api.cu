@@ -74,6 +74,7 @@ struct kc_ctx {
   int sm_count = 148;
   cudaStream_t stream = nullptr;
   uint32_t* status = nullptr;  // device status word
+  uint32_t* status_host = nullptr;  // pinned copy, filled by the copy that precedes a synchronisation
   ncclComm_t comm = nullptr;
   int tp_rank = 0, tp_world = 1;
   // launch accounting and optional per-class timing (kc_profile_*)
@@ -133,6 +134,7 @@ struct kc_qweight {
 namespace kc {
 CtxView ctx_view(kc_ctx* c) { return CtxView{c->device, c->stream, c->status}; }
 const QWeight* qweight_view(kc_qweight* q) { return &q->w; }
+kc_ctx* qweight_owner(kc_qweight* q) { return q->ctx; }
 void ctx_count_launches(kc_ctx* c, int cls, int n) { c->launches += n; c->class_launches[cls] += n; }
 int api_fail(int code, const char* msg) { return fail(code, "%s", msg); }
 }  // namespace kc
@@ -207,7 +209,11 @@ extern "C" int kc_ctx_create(int device, kc_ctx_t* out) {
   c->sm_count = prop.multiProcessorCount;
   if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess ||
       cudaMalloc(&c->status, sizeof(uint32_t)) != cudaSuccess ||
+      cudaMallocHost(&c->status_host, sizeof(uint32_t)) != cudaSuccess ||
       cudaMemsetAsync(c->status, 0, sizeof(uint32_t), c->stream) != cudaSuccess) {
+    if (c->stream) cudaStreamDestroy(c->stream);
+    cudaFree(c->status);
+    if (c->status_host) cudaFreeHost(c->status_host);
     delete c;
     return fail(KC_ERR_CUDA, "kc_ctx_create: stream/status allocation failed");
   }
@@ -228,29 +234,44 @@ extern "C" void kc_ctx_destroy(kc_ctx_t c) {
   cudaEventDestroy(c->step_b);
   if (c->comm) ncclCommDestroy(c->comm);
   cudaFree(c->status);
+  cudaFreeHost(c->status_host);
   cudaStreamDestroy(c->stream);
   delete c;
   g_live--;
 }
 
+// Queues the copy of the status word into the context's pinned word; the caller synchronises the stream and then
+// calls status_verdict. A bounded wait that gave up therefore never passes as success: every entry point that
+// synchronises returns KC_ERR_TIMEOUT when a kernel of the queue before it abandoned its work.
+static cudaError_t status_fetch(kc_ctx* c) {
+  return cudaMemcpyAsync(c->status_host, c->status, sizeof(uint32_t), cudaMemcpyDeviceToHost, c->stream);
+}
+static int status_verdict(kc_ctx* c, const char* where) {
+  const uint32_t st = *c->status_host;
+  if (!st) return KC_OK;
+  *c->status_host = 0;
+  cudaMemsetAsync(c->status, 0, sizeof(uint32_t), c->stream);
+  return fail(KC_ERR_TIMEOUT, "%s: device status 0x%x: a bounded wait gave up (kernel 0x%x, wait %u); the results of the "
+              "calls since the last synchronisation are not valid", where, st, st & 0xff00u, st & 0xffu);
+}
+
 extern "C" int kc_sync(kc_ctx_t c) {
   if (!c) return fail(KC_ERR_INVALID, "kc_sync: ctx is NULL");
+  CK(cudaSetDevice(c->device));
+  CK(status_fetch(c));
   CK(cudaStreamSynchronize(c->stream));
-  return KC_OK;
+  return status_verdict(c, "kc_sync");
 }
 
 extern "C" void* kc_ctx_stream(kc_ctx_t c) { return c ? (void*)c->stream : nullptr; }
 
 extern "C" int kc_device_status(kc_ctx_t c, uint32_t* status) {
   if (!c || !status) return fail(KC_ERR_INVALID, "kc_device_status: NULL argument");
-  CK(cudaMemcpyAsync(status, c->status, sizeof(uint32_t), cudaMemcpyDeviceToHost, c->stream));
+  CK(cudaSetDevice(c->device));
+  CK(status_fetch(c));
   CK(cudaStreamSynchronize(c->stream));
-  if (*status) {
-    CK(cudaMemsetAsync(c->status, 0, sizeof(uint32_t), c->stream));
-    return fail(KC_ERR_TIMEOUT, "device status 0x%x: a bounded wait gave up (kernel 0x%x, wait %u)", *status,
-                *status & 0xff00u, *status & 0xffu);
-  }
-  return KC_OK;
+  *status = *c->status_host;
+  return status_verdict(c, "kc_device_status");
 }
 
 extern "C" int64_t kc_launch_count(kc_ctx_t c) { return c ? c->launches : 0; }
@@ -493,6 +514,7 @@ extern "C" int kc_quantized_matmul(kc_ctx_t c, kc_qweight_t q, const void* x_dev
   if (!c || !q || !x_dev || !y_dev) return fail(KC_ERR_INVALID, "kc_quantized_matmul: NULL argument");
   if (m < 1) return fail(KC_ERR_INVALID, "kc_quantized_matmul: m = %d", m);
   if ((uintptr_t)x_dev % 16) return fail(KC_ERR_INVALID, "kc_quantized_matmul: x must be 16-byte aligned");
+  if (q->ctx != c) return fail(KC_ERR_INVALID, "kc_quantized_matmul: the weight was created on another context");
   CK(cudaSetDevice(c->device));
   // x must be readable for round_up(m, 16) rows; rows past m may hold anything.
   const int rows = (m + 15) & ~15;
@@ -1134,16 +1156,20 @@ extern "C" int kc_verify_step(kc_model_t m, kc_kv_t kv, const uint32_t* token_id
     CK(cudaMemcpyAsync(hb, m->row_tokens, (size_t)p.n_sampled * 4, cudaMemcpyDeviceToHost, c->stream));
     CK(cudaMemcpyAsync(hb + o1, m->n_committed, (size_t)n_seqs * 4, cudaMemcpyDeviceToHost, c->stream));
     CK(cudaMemcpyAsync(hb + o2, m->n_accepted, (size_t)n_seqs * 4, cudaMemcpyDeviceToHost, c->stream));
+    CK(status_fetch(c));
     CK(cudaEventRecord(c->step_b, c->stream));
     CK(cudaStreamSynchronize(c->stream));
     cudaEventElapsedTime(&c->last_step_ms, c->step_a, c->step_b);
+    RC(status_verdict(c, "kc_verify_step"));
     if (row_tokens_out) memcpy(row_tokens_out, hb, (size_t)p.n_sampled * 4);
     if (n_committed_out) memcpy(n_committed_out, hb + o1, (size_t)n_seqs * 4);
     if (n_accepted_out) memcpy(n_accepted_out, hb + o2, (size_t)n_seqs * 4);
   } else {
+    CK(status_fetch(c));
     CK(cudaEventRecord(c->step_b, c->stream));
     CK(cudaStreamSynchronize(c->stream));
     cudaEventElapsedTime(&c->last_step_ms, c->step_a, c->step_b);
+    RC(status_verdict(c, "kc_verify_step"));
     if (n_committed_out) memset(n_committed_out, 0, (size_t)n_seqs * 4);
     if (n_accepted_out) memset(n_accepted_out, 0, (size_t)n_seqs * 4);
   }
@@ -1170,7 +1196,9 @@ extern "C" int kc_draft_chain(kc_model_t m, kc_kv_t kv, uint32_t first_token, in
     LAUNCH(c, KC_PROF_SAMPLE, 1, launch_greedy_rows(m->logits, 1, m->d.vocab_size, 0, m->row_tokens + j, c->stream));
   }
   CK(cudaMemcpyAsync(m->result_host, m->row_tokens, (size_t)gamma * 4, cudaMemcpyDeviceToHost, c->stream));
+  CK(status_fetch(c));
   CK(cudaStreamSynchronize(c->stream));
+  RC(status_verdict(c, "kc_draft_chain"));
   memcpy(proposal_out, m->result_host, (size_t)gamma * 4);
   return KC_OK;
 }

@@ -31,19 +31,8 @@ namespace {
 
 // A multiple of every key-split count, so one ring slot is always drained by the same
 // consumer warps and each warp meets a slot's barrier phases strictly in order.
-#ifndef ATT_RING_STAGES
-#define ATT_RING_STAGES 8
-#endif
-constexpr int ATT_STAGES = ATT_RING_STAGES;
-#ifndef ATT_Q_REGS
-#define ATT_Q_REGS 0
-#endif
-#ifndef ATT_COND_RESCALE
-#define ATT_COND_RESCALE 1
-#endif
-#ifndef ATT_MINB
-#define ATT_MINB 3
-#endif
+constexpr int ATT_STAGES = 8;
+constexpr int ATT_MINB = 3;   // CTAs per SM the compiler must leave room for (head_dim <= 128, at most 32 query rows)
 
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -190,13 +179,6 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap kvmap, const AttnParams 
     float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
 
     const uint32_t q_base = smem_u32(sQ) + (mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * S::Q_LD + (lane >> 4) * 16;
-    // The Q fragments do not change over the key loop: keep them in registers when head_dim leaves room.
-    constexpr bool Q_IN_REGS = ATT_Q_REGS && D <= 128;
-    uint32_t qf[Q_IN_REGS ? KSTEPS : 1][4];
-    if (Q_IN_REGS) {
-#pragma unroll
-      for (int kk = 0; kk < KSTEPS; ++kk) ldsm_x4(qf[kk], q_base + kk * 32);
-    }
     bool ok = true;
     for (int t = ks; t < ntiles; t += KS) {
       const int st = t & (ATT_STAGES - 1); const uint32_t ph = (t / ATT_STAGES) & 1;
@@ -210,8 +192,7 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap kvmap, const AttnParams 
 #pragma unroll
       for (int kk = 0; kk < KSTEPS; ++kk) {
         uint32_t a[4], b[4];
-        if (Q_IN_REGS) { a[0] = qf[kk][0]; a[1] = qf[kk][1]; a[2] = qf[kk][2]; a[3] = qf[kk][3]; }
-        else ldsm_x4(a, q_base + kk * 32);
+        ldsm_x4(a, q_base + kk * 32);
         {
           const int mi = lane >> 3;
           const int key = (mi >> 1) * 8 + (lane & 7);
@@ -272,7 +253,7 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap kvmap, const AttnParams 
 
       // O = O * alpha + P V. Multiplying by exactly 1 changes no bit, so the rescale is skipped when no row of
       // the warp moved its maximum (the common case once the running maximum has settled).
-      if (!ATT_COND_RESCALE || !__all_sync(0xffffffffu, al_lo == 1.f && al_hi == 1.f)) {
+      if (!__all_sync(0xffffffffu, al_lo == 1.f && al_hi == 1.f)) {
 #pragma unroll
         for (int dn = 0; dn < NT_D; ++dn) { o[dn][0] *= al_lo; o[dn][1] *= al_lo; o[dn][2] *= al_hi; o[dn][3] *= al_hi; }
       }
@@ -393,11 +374,10 @@ __global__ void attn_combine_kernel(const AttnParams p, int n_rows) {
 template <int D, int MT>
 cudaError_t launch_partial(const CUtensorMap& map, const AttnParams& p, int n_work, int grid_chunks, cudaStream_t s) {
   using S = AttnSmem<D, MT>;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce configured;   // the attribute belongs to the device's copy of the kernel
+  if (configured.first_on_current_device()) {
     cudaError_t e = cudaFuncSetAttribute(attn_partial_kernel<D, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
-    if (e != cudaSuccess) return e;
-    configured = true;
+    if (e != cudaSuccess) { configured.forget_current_device(); return e; }
   }
   dim3 grid(grid_chunks, p.Hkv, n_work);
   return launch_k(attn_partial_kernel<D, MT>, grid, dim3((S::CW + 1) * 32), S::TOTAL, s, map, p);

@@ -187,14 +187,23 @@ __device__ __forceinline__ float warp_max(float v) {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-#ifndef __CUDA_ARCH__
-// KILN_PDL=0 in the environment launches every kernel with plain stream ordering (the device-side calls above are
-// then no-ops).
-inline bool pdl_enabled() {
-  static const bool on = [] { const char* e = getenv("KILN_PDL"); return !(e && e[0] == '0'); }();
-  return on;
-}
-#endif
+// One-time set-up that has to happen once per DEVICE (kernel attributes live in the device's copy of the module, and
+// one process may hold contexts on several devices). Host threads of different contexts may race here: the worst
+// case is that the set-up runs twice, which is harmless.
+struct DeviceOnce {
+  unsigned long long done = 0;   // bit d: device d is configured (devices past 63 are configured on every call)
+  bool first_on_current_device() {
+    int d = 0;
+    if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d > 63) return true;
+    if (done >> d & 1ull) return false;
+    done |= 1ull << d;
+    return true;
+  }
+  void forget_current_device() {
+    int d = 0;
+    if (cudaGetDevice(&d) == cudaSuccess && d >= 0 && d <= 63) done &= ~(1ull << d);
+  }
+};
 
 // allow_early = false launches with plain stream order: used for the first kernel after a collective, whose duration
 // depends on the OTHER ranks — nothing of this library may be resident and counting down a bounded wait meanwhile.
@@ -206,9 +215,7 @@ inline cudaError_t launch_k_opt(bool allow_early, void (*kernel)(KArgs...), dim3
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
-#ifndef __CUDA_ARCH__
-  if (allow_early && pdl_enabled()) { cfg.attrs = attr; cfg.numAttrs = 1; }
-#endif
+  if (allow_early) { cfg.attrs = attr; cfg.numAttrs = 1; }
   return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 template <typename... KArgs, typename... Args>

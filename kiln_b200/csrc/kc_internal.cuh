@@ -17,6 +17,7 @@ struct CtxView {
 
 CtxView ctx_view(kc_ctx* c);
 const QWeight* qweight_view(kc_qweight* q);
+kc_ctx* qweight_owner(kc_qweight* q);   // the context the weight's device memory belongs to
 // Adds n launches of the GEMM (cls 0) / split-K reduction (cls 1) class to the context's launch counters.
 void ctx_count_launches(kc_ctx* c, int cls, int n);
 // Records `msg` as the calling thread's last error (what kc_last_error returns) and returns `code`.

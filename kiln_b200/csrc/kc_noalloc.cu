@@ -43,6 +43,8 @@ extern "C" int kc_quantized_matmul_static(kc_ctx_t c, kc_qweight_t q, const void
     return api_fail(KC_ERR_INVALID, msg);
   }
   if ((uintptr_t)x_dev % 16) return api_fail(KC_ERR_INVALID, "kc_quantized_matmul_static: x must be 16-byte aligned");
+  if (qweight_owner(q) != c)
+    return api_fail(KC_ERR_INVALID, "kc_quantized_matmul_static: the weight was created on another context");
   const CtxView cv = ctx_view(c);
   const QWeight& w = *qweight_view(q);
 
@@ -81,11 +83,12 @@ extern "C" int kc_quantized_matmul_static(kc_ctx_t c, kc_qweight_t q, const void
     QLinearLaunch l;
     l.w = &w; l.x = &op; l.row0 = row0; l.M = (m - row0) < QL_MAX_M ? (m - row0) : QL_MAX_M;
     l.y = y; l.ldy = w.N; l.partial = scratch; l.status = cv.status;
-    ctx_count_launches(c, 0, 1);
+    // launches are counted once they are queued; this entry point takes no part in kc_profile_* timing
     e = qlinear_umma(l, cv.stream);
+    if (e == cudaSuccess) ctx_count_launches(c, 0, 1);
     if (e == cudaSuccess && w.splits > 1) {
-      ctx_count_launches(c, 1, 1);
       e = qlinear_reduce_splits(scratch, w.splits, l.M, w.N, y + (size_t)row0 * w.N, w.N, cv.stream);
+      if (e == cudaSuccess) ctx_count_launches(c, 1, 1);
     }
     if (e != cudaSuccess) {
       snprintf(msg, sizeof msg, "kc_quantized_matmul_static: launch: %s", cudaGetErrorString(e));

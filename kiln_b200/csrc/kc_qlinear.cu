@@ -897,11 +897,10 @@ static cudaError_t launch_umma(const QLinearLaunch& l, QlKernelParams& p, cudaSt
   p.a_stages = as; p.r_stages = rs;
   const size_t smem = 1024 + (size_t)as * ab + (size_t)rs * rstage + (2 * rs + 3 * as + 1) * 8 + 16;
   if (smem > 227 * 1024) return cudaErrorInvalidValue;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce configured;   // the attribute belongs to the device's copy of the kernel
+  if (configured.first_on_current_device()) {
     cudaError_t e = cudaFuncSetAttribute(qlinear_umma_kernel<BITS, GPK, NT, KC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    if (e != cudaSuccess) return e;
-    configured = true;
+    if (e != cudaSuccess) { configured.forget_current_device(); return e; }
   }
   dim3 grid((w.n_tiles + NT - 1) / NT, w.splits);
   const CUtensorMap* first = &l.x->map16;
@@ -940,11 +939,10 @@ static cudaError_t launch_umma_ta(const QLinearLaunch& l, QlKernelParams& p, cud
   p.a_stages = sa; p.b_stages = sb; p.r_stages = rs;
   const size_t smem = 1024 + (size_t)sb * b_stage + (size_t)rs * rstage + (2 * rs + 2 * sb + 2 * sa + 1) * 8 + 16;
   if (smem > 227 * 1024) return cudaErrorNotSupported;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce configured;   // the attribute belongs to the device's copy of the kernel
+  if (configured.first_on_current_device()) {
     cudaError_t e = cudaFuncSetAttribute(qlinear_umma_ta_kernel<BITS, GPK, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    if (e != cudaSuccess) return e;
-    configured = true;
+    if (e != cudaSuccess) { configured.forget_current_device(); return e; }
   }
   const CUtensorMap* rows = act_operand_rows_map(l.x, p.m_pad);
   if (!rows) return cudaErrorInvalidValue;
@@ -1016,30 +1014,47 @@ cudaError_t qlinear_umma(const QLinearLaunch& l, cudaStream_t s) {
 // Split-K reduction
 // ---------------------------------------------------------------------------
 
+// Pairs of neighbouring features go through 8-byte loads when every row of the partials and of y starts on the
+// matching boundary (N, ldy even, bases aligned); otherwise one element per thread. The additions of an element are
+// the same on both paths.
 __global__ void qlinear_reduce_kernel(const float* __restrict__ partial, int splits, int M, int N,
-                                      bf16* __restrict__ y, int ldy) {
+                                      bf16* __restrict__ y, int ldy, int vec) {
   pdl_launch_dependents();
   pdl_wait();
-  const long long total = (long long)M * N / 2;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
-       i += (long long)gridDim.x * blockDim.x) {
-    const long long e = i * 2;
-    const int m = (int)(e / N), n = (int)(e % N);
-    float2 acc = *reinterpret_cast<const float2*>(partial + e);
-    for (int s = 1; s < splits; ++s) {
-      const float2 v = *reinterpret_cast<const float2*>(partial + (size_t)s * M * N + e);
-      acc.x += v.x; acc.y += v.y;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const long long first = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const size_t split_stride = (size_t)M * N;
+  if (vec) {
+    const long long total = (long long)M * N / 2;
+    for (long long i = first; i < total; i += stride) {
+      const long long e = i * 2;
+      const int m = (int)(e / N), n = (int)(e % N);
+      float2 acc = *reinterpret_cast<const float2*>(partial + e);
+      for (int s = 1; s < splits; ++s) {
+        const float2 v = *reinterpret_cast<const float2*>(partial + s * split_stride + e);
+        acc.x += v.x; acc.y += v.y;
+      }
+      *reinterpret_cast<bf162*>(y + (size_t)m * ldy + n) = __floats2bfloat162_rn(acc.x, acc.y);
     }
-    *reinterpret_cast<bf162*>(y + (size_t)m * ldy + n) = __floats2bfloat162_rn(acc.x, acc.y);
+  } else {
+    const long long total = (long long)M * N;
+    for (long long e = first; e < total; e += stride) {
+      const int m = (int)(e / N), n = (int)(e % N);
+      float acc = partial[e];
+      for (int s = 1; s < splits; ++s) acc += partial[s * split_stride + e];
+      y[(size_t)m * ldy + n] = __float2bfloat16_rn(acc);
+    }
   }
 }
 
 cudaError_t qlinear_reduce_splits(const float* partial, int splits, int M, int N, bf16* y, int ldy,
                                   cudaStream_t s) {
-  const long long total = (long long)M * N / 2;
+  const int vec = (N % 2 == 0 && ldy % 2 == 0 && (reinterpret_cast<uintptr_t>(partial) & 7) == 0 &&
+                   (reinterpret_cast<uintptr_t>(y) & 3) == 0) ? 1 : 0;
+  const long long total = vec ? (long long)M * N / 2 : (long long)M * N;
   const int threads = 256;
-  const int blocks = (int)std::min<long long>((total + threads - 1) / threads, 148LL * 8);
-  return launch_k(qlinear_reduce_kernel, dim3(blocks), dim3(threads), 0, s, partial, splits, M, N, y, ldy);
+  const int blocks = (int)std::max<long long>(1, std::min<long long>((total + threads - 1) / threads, 148LL * 8));
+  return launch_k(qlinear_reduce_kernel, dim3(blocks), dim3(threads), 0, s, partial, splits, M, N, y, ldy, vec);
 }
 
 }  // namespace kc

@@ -1,5 +1,5 @@
 """CPU checks of bench.py's bookkeeping: every workload names a model preset that exists, and the algorithmic bytes and
-flops of the headline verify step are the figures the roofline and DESIGN.md quote (weights once, K/V once per sequence).
+flops of the headline verify step are the figures the roofline quotes (weights once, K/V once per sequence).
 Nothing here touches a GPU or the oracle."""
 import importlib.util
 from pathlib import Path
