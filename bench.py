@@ -69,29 +69,71 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs (reads only)."""
+    """Samples SM clocks, power and clock-event reasons WHILE the timed region runs (reads only, nothing is set):
+    NVML from a thread every 5 ms; nvidia-smi in a loop when the NVML binding is missing."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = {"hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40, "sw_power_cap": 0x4}
 
     def __init__(self, device: int):
-        self.device, self.proc, self.lines = device, None, []
+        self.device, self.proc, self.lines, self.samples, self.stop_flag, self.nvml = device, None, [], [], False, None
+
+    def _physical_index(self):
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            ids = [v.strip() for v in vis.split(",") if v.strip()]
+            if self.device < len(ids) and ids[self.device].isdigit():
+                return int(ids[self.device])
+        return self.device
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
-                                          "-i", str(self.device)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            import pynvml
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(self._physical_index())
+            self.max_sm = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.nvml = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50",
+                                          "-i", str(self._physical_index())], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except Exception:
             self.proc = None
+
+    def _poll(self):
+        n = self.nvml
+        while not self.stop_flag:
+            try:
+                self.samples.append((n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM),
+                                     n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle),
+                                     n.nvmlDeviceGetPowerUsage(self.handle) / 1000.0))
+            except Exception:
+                pass
+            time.sleep(0.005)
 
     def _read(self):
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
     def stop(self) -> dict:
+        if self.nvml:
+            self.stop_flag = True
+            self.thread.join(timeout=2)
+            sm = sorted(s[0] for s in self.samples)
+            mask = 0
+            for s_ in self.samples:
+                mask |= int(s_[1])
+            reasons = sorted(k for k, bit in self.REASONS.items() if mask & bit)
+            return {"sm_mhz": float(sm[len(sm) // 2]) if sm else None, "sm_max_mhz": float(self.max_sm), "reasons": reasons,
+                    "samples": len(sm), "power_w_max": max((s_[2] for s_ in self.samples), default=None), "source": "nvml, 5 ms period"}
         if not self.proc:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no NVML binding and no nvidia-smi"], "samples": 0}
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
@@ -111,7 +153,7 @@ class ClockSampler:
                     reasons.add(name)
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
-                "samples": len(sm)}
+                "samples": len(sm), "source": "nvidia-smi, 50 ms period"}
 
 
 def algorithmic(cfg, batch, k, mean_ctx):
@@ -174,9 +216,8 @@ class Workload:
         self.model = api.CudaModel(self.ctx, cfg, ck, max_step_tokens=max_step, max_step_seqs=self.batch + 1,
                                    tp_rank=rank if self.tp > 1 else 0, tp_world=self.tp)
         self.cpu_sample = None
-        if keep_cpu_sample:   # layer 0 + embedding + final norm + head on the host, for the CPU baseline
-            keep = {n: t.cpu() for n, t in ck.items() if not n.startswith("model.layers.") or n.startswith("model.layers.0.")}
-            self.cpu_sample = keep
+        if keep_cpu_sample:   # the checkpoint on the host, for the CPU baseline (packed: about an eighth of bf16)
+            self.cpu_sample = {n: t.cpu() for n, t in ck.items()}
         del ck
         torch.cuda.empty_cache()
         self.build_s = time.time() - t0
@@ -306,56 +347,141 @@ def roofline_pass(w: Workload, base, steps: int = 4):
 
 # --------------------------------------------------------------------------------------
 # CPU arm: the oracle (a restatement of the reference's op graph; the reference's own MLX CPU path cannot
-# be built or installed where this runs) timed on the host cores over a bounded sample of the same step
+# be built or installed where this runs) timed on the host cores over a bounded sample of the same workload
 # --------------------------------------------------------------------------------------
 
 def cpu_reference(name: str, tensors, ctxs, steps: int, warmup: int, budget_s: float = 150.0):
-    """Times one transformer layer (and once, the head) of the verify step at the full batch on the host cores and
-    extrapolates to the whole step: step_s = head_s + num_layers * layer_s. tensors: layer 0 + embedding + norm + head."""
+    """Times the reference's own shape of the verify step on the host cores: ONE forward per speculating sequence
+    (crates/kiln-engine/src/engine.rs:2164-2172, 2240-2271 — the reference never batches verify across sequences),
+    i.e. (k + 1) rows of one sequence at its context through every layer, the head and the greedy rows. One timed step
+    = one such forward; sequences of the batch are taken in turn. Nothing is extrapolated: a batch round on the CPU is
+    `batch` of these forwards one after the other, each using every core. tensors: the whole checkpoint on the host."""
     import numpy as np
+    import torch
     from kiln_b200 import api
-    from kiln_b200.synth import PRESETS, synth_checkpoint, truncated
+    from kiln_b200.synth import PRESETS, synth_checkpoint
     from oracle import oracle as O
     preset, batch, k, lo, hi, gen = WORKLOADS[name][:6]
     cfg = PRESETS[preset]
-    cfg1 = truncated(cfg, 1)
+    cores = os.cpu_count() or 1
+    threads = O.set_threads(cores)   # launchers export OMP_NUM_THREADS=1 to their ranks: set it explicitly
     if tensors is None:
-        tensors = synth_checkpoint(cfg, seed=0, device="cpu", num_layers=1)
-    om = O.OracleModel(cfg1, tensors)
+        dev = "cuda" if torch.cuda.is_available() else "cpu"   # the generator is the same on either device
+        tensors = {n: t.cpu() for n, t in synth_checkpoint(cfg, seed=0, device=dev).items()}
+        if dev == "cuda":
+            torch.cuda.empty_cache()
+    om = O.OracleModel(cfg, tensors)
     bs = 16
     if ctxs is None:
         rng = np.random.default_rng(1000)
         ctxs = [int(x) + gen // 2 for x in rng.integers(lo, hi + 1, size=batch)]
-    nblk = [-(-(c + k + 1) // bs) for c in ctxs]
-    okv = O.OracleKv(1, cfg.num_key_value_heads, cfg.head_dim, sum(nblk) + 1, bs)
-    seqs, at = [], 0
-    for c, nb in zip(ctxs, nblk):
-        seqs.append(api.SeqStep(k + 1, c, k + 1, list(range(at, at + nb))))
-        at += nb
+    nblk = -(-(max(ctxs) + k + 1) // bs)
+    okv = O.OracleKv(cfg.num_hidden_layers, cfg.num_key_value_heads, cfg.head_dim, nblk + 1, bs)
     rng = np.random.default_rng(7)
-    ids = rng.integers(0, cfg.vocab_size, size=batch * (k + 1)).tolist()
-    step = api.StepBatch(ids, seqs)
-    cores = os.cpu_count() or 1
-    t0 = time.perf_counter()
-    om.forward_step(step, okv, want_logits=True)
-    layer_head_s = time.perf_counter() - t0
-    layer_times = []
+    times = []
     t_begin = time.perf_counter()
     for i in range(warmup + steps):
+        c = ctxs[i % len(ctxs)]
+        ids = rng.integers(0, cfg.vocab_size, size=k + 1).tolist()
+        step = api.StepBatch(ids, [api.SeqStep(k + 1, c, k + 1, list(range(nblk)))])
         t0 = time.perf_counter()
-        om.forward_step(step, okv, want_logits=False)
+        logits = om.forward_step(step, okv, want_logits=True)
+        O.greedy_rows(logits, True)
         dt = time.perf_counter() - t0
         if i >= warmup:
-            layer_times.append(dt)
-        if time.perf_counter() - t_begin > budget_s and len(layer_times) >= 1:
+            times.append(dt)
+        if time.perf_counter() - t_begin > budget_s and len(times) >= 1:
             break
-    layer_s = sorted(layer_times)[len(layer_times) // 2]
-    head_s = max(layer_head_s - layer_s, 0.0)
-    step_s = head_s + cfg.num_hidden_layers * layer_s
-    return {"step_s": step_s, "layer_s": layer_s, "head_s": head_s, "cores": cores, "timed": len(layer_times),
-            "sample": (f"1 of {cfg.num_hidden_layers} layers at the full batch ({batch * (k + 1)} rows, per-sequence contexts of the "
-                       f"GPU run) timed {len(layer_times)}x (median), lm_head + sampling rows timed once; "
-                       f"step = head + {cfg.num_hidden_layers} x layer")}
+    fwd_s = sorted(times)[len(times) // 2]
+    return {"forward_s": fwd_s, "mean_forward_s": sum(times) / len(times), "cores": cores, "threads": threads, "timed": len(times),
+            "sample": (f"one sequence's verify forward per step ({k + 1} rows at that sequence's context, all {cfg.num_hidden_layers} "
+                       f"layers + head + greedy rows): the reference verifies one forward per sequence; {len(times)} forwards timed, "
+                       f"median; a batch round = {batch} such forwards, nothing extrapolated")}
+
+
+GEMM_KERNEL = "qlinear_umma_ta_kernel (affine-dequant GEMM, tcgen05, A operand in TMEM)"
+TP_WORKLOAD = "llama-3-70b-8l-w4g64-verify-k4-bs64-tp"
+
+
+def pin_rank_to_cores(local_rank: int, world: int) -> None:
+    """Gives every rank of a multi-GPU run its own contiguous share of the cores this process may use, so that the
+    ranks' launch threads do not share cores (each rank issues a few hundred launches per step from one thread)."""
+    try:
+        cores = sorted(os.sched_getaffinity(0))
+        per = len(cores) // world
+        if per >= 2:
+            os.sched_setaffinity(0, set(cores[local_rank * per:(local_rank + 1) * per]))
+    except (AttributeError, OSError):
+        pass
+
+
+def status_word(ctx) -> int:
+    """The context's device status word (0 = no bounded wait gave up); never raises."""
+    try:
+        return int(ctx.device_status())
+    except Exception as e:   # the call reports a non-zero word as an error; the word is in its message
+        import re
+        m = re.search(r"0x([0-9a-fA-F]+)", str(e))
+        return int(m.group(1), 16) if m else -1
+
+
+def check_pass(w: "Workload", base) -> dict:
+    """Speculation on, to completion, twice: equal to the speculation-off continuation `base`, and equal to itself."""
+    t0 = time.time()
+    arrivals = w.submit_on(base)
+    fin = w.engine.run_to_completion(arrivals)
+    on_s = time.time() - t0
+    same = [fin[a][0] == cont for a, cont in zip(arrivals, base)]
+    first_bad = [(i, next((j for j, (x, y) in enumerate(zip(fin[a][0], cont)) if x != y), min(len(fin[a][0]), len(cont))),
+                  len(fin[a][0]), len(cont), fin[a][1])
+                 for i, (a, cont) in enumerate(zip(arrivals, base)) if fin[a][0] != cont][:4]
+    arrivals2 = w.submit_on(base)
+    fin2 = w.engine.run_to_completion(arrivals2)
+    on_twice_equal = all(fin2[b][0] == fin[a][0] for a, b in zip(arrivals, arrivals2))
+    st = w.engine.spec_stats()
+    return {"spec_on_equals_off": {"sequences_checked": len(same), "identical": all(same), "mismatching": len(same) - sum(same),
+                                   "first_mismatches(seq, position, len_on, len_off, finish)": first_bad},
+            "speculation_on_twice_equal": on_twice_equal, "launches": w.ctx.launch_count(), "iterations": w.engine.iterations,
+            "speculation_on_s": round(on_s, 2), "proposed": st["proposed_total"], "accepted": st["accepted_total"],
+            "rollback_rounds": st["rollback_rounds_total"], "cache": w.engine.cache_stats(), "device_status": status_word(w.ctx)}
+
+
+def tp_record(rank: int, local_rank: int, world: int, dist, barrier) -> dict:
+    """The tensor-parallel configuration on all `world` GPUs: the 70B layer shapes (8 of the 80 layers, so that it loads
+    in seconds), batch 64, k = 4, prompts 1024-4096. Every rank holds a slice of every layer and all ranks serve the same
+    requests. Reports the parity properties (speculation on == off, two speculation-on passes equal, device status) and
+    the step time (max over ranks) with its per-class split and the bytes each rank receives from its peers per step."""
+    import torch
+    from kiln_b200.replicas import combine_over_ranks
+    t0 = time.time()
+    w = Workload(TP_WORKLOAD, rank, local_rank, keep_cpu_sample=False, world=world, dist=dist)
+    base = w.run_off()
+    chk = check_pass(w, base)
+    records, _, arrivals, _ = timed_steps(w, base, 8, 3, barrier, None)
+    dev_ms = sum(r["dev_ms"] for r in records)
+    wall_ms = sum(r["wall_ms"] for r in records)
+    tokens = sum(r["tokens"] for r in records) if rank == 0 else 0
+    prof, _ = roofline_pass(w, base, 2)
+    if arrivals:
+        w.engine.run_to_completion(arrivals)
+    ok = chk["spec_on_equals_off"]["identical"] and chk["speculation_on_twice_equal"] and chk["device_status"] == 0
+    tot = combine_over_ranks(dist, f"cuda:{local_rank}", dev_ms, wall_ms, tokens, ok, world)
+    st = torch.tensor([float(chk["device_status"])], dtype=torch.float64, device=f"cuda:{local_rank}")
+    dist.all_reduce(st, op=dist.ReduceOp.MAX)
+    cfg = w.cfg
+    rows = w.batch * (w.k + 1)
+    rec = {"workload": TP_WORKLOAD, "ranks": world, "ms_per_step": tot.device_ms / len(records),
+           "verified_tok_s": tot.tokens / (tot.device_ms * 1e-3), "e2e_tok_s": tot.tokens / (tot.wall_ms * 1e-3),
+           "kernel_classes_ms_per_step_rank0": {k2: round(v[0], 4) for k2, v in prof.items()},
+           "spec_on_equals_off": chk["spec_on_equals_off"]["identical"], "sequences_checked": chk["spec_on_equals_off"]["sequences_checked"],
+           "speculation_on_twice_equal": chk["speculation_on_twice_equal"], "all_ranks_ok": tot.all_identical,
+           "device_status_max_over_ranks": int(st[0]),
+           "exchange": "all-gather of every rank's bf16 [rows, hidden] sublayer output after o_proj and down_proj (NCCL), summed "
+                       "in rank order in fp32 by the consumer kernel",
+           "peer_bytes_received_per_rank_per_step": int(2 * cfg.num_hidden_layers * (world - 1) * rows * cfg.hidden_size * 2),
+           "seconds": round(time.time() - t0, 1)}
+    w.close()
+    return rec
 
 
 def main():
@@ -369,6 +495,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="llama-3.1-8b-w4g64-verify-k5-bs32", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-tp-record", action="store_true",
+                    help="at --gpus N > 1, skip the tensor-parallel sub-record that follows the replica measurement")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -386,14 +514,17 @@ def main():
             return
         r = cpu_reference(args.workload, None, None, args.steps, warmup)
         commit = 1 + sum(0.7 ** i for i in range(1, k + 1))
-        val = batch * commit / r["step_s"]
-        line = {"impl": "reference", "metric": metric, "value": val, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps,
-                "warmup": warmup, "ms_per_step": r["step_s"] * 1e3, "higher_is_better": True, "scaling": "weak",
+        val = commit / r["forward_s"]
+        line = {"impl": "reference", "metric": metric, "value": val, "unit": "tok/s", "n_gpus": args.gpus, "steps": r["timed"],
+                "warmup": warmup, "ms_per_step": r["mean_forward_s"] * 1e3, "p50_step_ms": r["forward_s"] * 1e3,
+                "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config,
-                "cpu_baseline": {"value": val, "unit": "tok/s", "cores": r["cores"], "kind": "port", "sample": r["sample"]},
+                "cpu_baseline": {"value": val, "unit": "tok/s", "cores": r["cores"], "threads": r["threads"], "kind": "port",
+                                 "sample": r["sample"]},
                 "e2e": {"value": val, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-                "note": ("CPU restatement of the reference's op graph (oracle/): the reference's MLX CPU path cannot be built here; "
-                         f"tokens per step = batch x expected commit {commit:.3f} at p = 0.7")}
+                "note": ("CPU restatement of the reference's op graph (oracle/): the reference's MLX CPU path cannot be built here. "
+                         f"One step = one sequence's verify forward; tokens per step = expected commit {commit:.3f} at p = 0.7. "
+                         "It does not grow with --gpus: it is a host-cores baseline.")}
         print(json.dumps(line))
         return
 
@@ -402,6 +533,7 @@ def main():
     if world > 1:
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        pin_rank_to_cores(local_rank, world)
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
     want_cpu = rank == 0 and world == 1 and not args.no_cpu_baseline and not args.check_only
@@ -412,29 +544,10 @@ def main():
         t0 = time.time()
         base = w.run_off()
         off_s = time.time() - t0
-        t0 = time.time()
-        arrivals = w.submit_on(base)
-        fin = w.engine.run_to_completion(arrivals)
-        on_s = time.time() - t0
-        same = [fin[a][0] == cont for a, cont in zip(arrivals, base)]
-        first_bad = [(i, next((j for j, (x, y) in enumerate(zip(fin[a][0], cont)) if x != y), min(len(fin[a][0]), len(cont))),
-                      len(fin[a][0]), len(cont), fin[a][1])
-                     for i, (a, cont) in enumerate(zip(arrivals, base)) if fin[a][0] != cont][:4]
-        # a second speculation-on pass over the same requests: equal to the first unless something is not deterministic
-        arrivals2 = w.submit_on(base)
-        fin2 = w.engine.run_to_completion(arrivals2)
-        on_twice_equal = all(fin2[b][0] == fin[a][0] for a, b in zip(arrivals, arrivals2))
-        st = w.engine.spec_stats()
-        print(json.dumps({"check_only": True, "workload": args.workload, "rank": rank,
-                          "spec_on_equals_off": {"sequences_checked": len(same), "identical": all(same),
-                                                 "mismatching": len(same) - sum(same),
-                                                 "first_mismatches(seq, position, len_on, len_off, finish)": first_bad},
-                          "speculation_on_twice_equal": on_twice_equal, "launches": w.ctx.launch_count(),
-                          "iterations": w.engine.iterations,
-                          "generated_tokens": sum(len(c) for c in base), "speculation_off_s": round(off_s, 2),
-                          "speculation_on_s": round(on_s, 2), "proposed": st["proposed_total"], "accepted": st["accepted_total"],
-                          "rollback_rounds": st["rollback_rounds_total"], "cache": w.engine.cache_stats(),
-                          "device_status": w.ctx.device_status()}))
+        out = check_pass(w, base)
+        out.update({"check_only": True, "workload": args.workload, "rank": rank, "speculation_off_s": round(off_s, 2),
+                    "generated_tokens": sum(len(c) for c in base)})
+        print(json.dumps(out))
         w.close()
         if dist:
             dist.destroy_process_group()
@@ -449,16 +562,10 @@ def main():
         torch.cuda.synchronize()
 
     sampler = ClockSampler(local_rank) if rank == 0 else None
-    launches0 = None
-    records, (checked, identical), arrivals, outs = None, (0, True), None, None
-    # launches are counted over the timed region only
     w.ctx.sync()
-    pre = w.ctx.launch_count()
     records, (checked, identical), arrivals, outs = timed_steps(w, base, args.steps, warmup, barrier, sampler)
     barrier()
     clocks = sampler.stop() if sampler else None
-    post = w.ctx.launch_count()
-    # launches of warm-up / non-full iterations are inside [pre, post] too: scale by the per-step count measured below
     dev_ms = sum(r["dev_ms"] for r in records)
     wall_ms = sum(r["wall_ms"] for r in records)
     tokens = sum(r["tokens"] for r in records)
@@ -471,62 +578,87 @@ def main():
         for a, cont in zip(arrivals, base):
             checked += 1
             identical &= (outs.get(a, []) + fin[a][0]) == cont
+    device_status = status_word(w.ctx)
 
     from kiln_b200.replicas import combine_over_ranks
+    step_ms = sorted(r["dev_ms"] for r in records)
+    per_rank = None
+    if dist:   # every rank's own figures, so that a slow rank or a slow host path shows in the line
+        mine = torch.tensor([step_ms[len(step_ms) // 2], step_ms[-1], dev_ms / len(records), wall_ms / len(records), float(device_status)],
+                            dtype=torch.float64, device=f"cuda:{local_rank}")
+        allr = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(allr, mine)
+        per_rank = [{"rank": i, "p50_step_ms": round(float(t[0]), 4), "max_step_ms": round(float(t[1]), 4),
+                     "mean_step_ms": round(float(t[2]), 4), "mean_wall_ms": round(float(t[3]), 4), "device_status": int(t[4])}
+                    for i, t in enumerate(allr)]
     if w.tp > 1 and rank != 0:
         tokens = 0   # every tensor-parallel rank verified the same tokens: count them once
     tot = combine_over_ranks(dist, f"cuda:{local_rank}", dev_ms, wall_ms, tokens, identical, world)
     dev_ms, wall_ms, tokens, identical = tot.device_ms, tot.wall_ms, tot.tokens, tot.all_identical
+    tp_rec = None
+    main_tp = w.tp
+    cfg_main, mean_prompt, build_s = w.cfg, w.mean_prompt, w.build_s
+    cpu_ctxs = [len(p) + gen // 2 for p in w.prompts]
+    cpu_sample = w.cpu_sample
+    w.close()
+    del w
+    torch.cuda.empty_cache()
+    if dist and main_tp == 1 and not args.no_tp_record:
+        # the configuration that shards (BASELINE config 5's layer shapes, batch, k and prompt lengths), on all N GPUs
+        tp_rec = tp_record(rank, local_rank, world, dist, barrier)
     if rank != 0:
-        w.close()
         if dist:
             dist.destroy_process_group()
         return
 
     pk = peaks()
     steps = len(records)
-    step_ms = sorted(r["dev_ms"] for r in records)
-    mean_ctx = w.mean_prompt + gen / 2.0
-    alg = algorithmic(w.cfg, batch, k, mean_ctx)
+    mean_ctx = mean_prompt + gen / 2.0
+    alg = algorithmic(cfg_main, batch, k, mean_ctx)
     gemm_ms, gemm_n = prof.get("gemm", (0.0, 0))
     # per-GPU rate: under tensor parallelism every rank multiplies 1 / tp of the weights
-    gemm_tflops = alg["gemm_flops"] / w.tp / (gemm_ms * 1e-3) / 1e12 if gemm_ms else None
+    gemm_tflops = alg["gemm_flops"] / main_tp / (gemm_ms * 1e-3) / 1e12 if gemm_ms else None
     p50 = step_ms[len(step_ms) // 2]
+    value = tokens / (dev_ms * 1e-3)
     line = {
-        "metric": metric, "value": tokens / (dev_ms * 1e-3), "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warmup,
-        "ms_per_step": dev_ms / steps, "p50_step_ms": p50, "higher_is_better": True,
-        "scaling": "strong" if w.tp > 1 else "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic", "config": config, "clocks": clocks,
+        "metric": metric, "value": value, "value_per_gpu": value / world, "unit": "tok/s", "n_gpus": world, "steps": steps,
+        "warmup": warmup, "ms_per_step": dev_ms / steps, "p50_step_ms": p50, "higher_is_better": True,
+        "scaling": "strong" if main_tp > 1 else "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic", "config": config, "clocks": clocks, "device_status": device_status,
         "e2e": {"value": tokens / (wall_ms * 1e-3), "unit": "tok/s", "ms_per_step": wall_ms / steps,
                 "h2d_bytes_per_step": int(batch * (k + 1) * 4 * 4 + batch * (mean_ctx / 16 + 2) * 4 + batch * 16 + batch * 12 + batch * (k + 1) * 8),
-                "d2h_bytes_per_step": int(batch * (k + 1) * 4 + batch * 8)},
+                "d2h_bytes_per_step": int(batch * (k + 1) * 4 + batch * 8 + 4)},
         "gpu_launches": int(launches_per_step * steps),
-        "roofline": {"kernel": "qlinear_umma_ta_kernel (affine-dequant GEMM, tcgen05, A operand in TMEM)", "bound": "tensor",
+        "roofline": {"kernel": GEMM_KERNEL, "bound": "tensor",
                      "achieved": gemm_tflops, "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
                      "frac": (gemm_tflops / pk["bf16_tflops_sustained"]) if gemm_tflops else None,
-                     "traffic": (GEMM_DRAM_TRAFFIC_PER_WEIGHT_BYTE * alg["weight_bytes"] / w.tp / gemm_n) if gemm_n else None,
+                     "traffic": (GEMM_DRAM_TRAFFIC_PER_WEIGHT_BYTE * alg["weight_bytes"] / main_tp / gemm_n) if gemm_n else None,
                      "traffic_unit": "bytes per launch (ncu dram read+write of one launch, scaled by weight bytes)",
-                     "algorithmic_bytes_per_launch": (alg["weight_bytes"] / w.tp / gemm_n) if gemm_n else None,
+                     "algorithmic_bytes_per_launch": (alg["weight_bytes"] / main_tp / gemm_n) if gemm_n else None,
                      "peak_source": pk["source"] + " (sustained: the kernel runs inside a long step)",
                      "launches_per_step": gemm_n, "ms_per_step": gemm_ms,
-                     "algorithmic_flops_per_launch": alg["gemm_flops"] / w.tp / gemm_n if gemm_n else None},
+                     "algorithmic_flops_per_launch": alg["gemm_flops"] / main_tp / gemm_n if gemm_n else None},
         "step_roofline": {"bound": "hbm", "algorithmic_bytes_per_step": alg["bytes"], "achieved": alg["bytes"] / (p50 * 1e-3) / 1e9,
-                          "peak": pk["hbm_gbs"] * w.tp, "unit": "GB/s", "frac": alg["bytes"] / (p50 * 1e-3) / 1e9 / (pk["hbm_gbs"] * w.tp),
+                          "peak": pk["hbm_gbs"] * main_tp, "unit": "GB/s", "frac": alg["bytes"] / (p50 * 1e-3) / 1e9 / (pk["hbm_gbs"] * main_tp),
                           "frac_of_nominal_8tbs": alg["bytes"] / (p50 * 1e-3) / 8e12, "mean_context": mean_ctx},
         "kernel_classes_ms_per_step": {k2: round(v[0], 4) for k2, v in prof.items()},
         "kernel_classes_launches_per_step": {k2: v[1] for k2, v in prof.items()},
         "acceptance": {"proposed": sum(r["proposed"] for r in records), "accepted": sum(r["accepted"] for r in records),
-                       "tokens_per_step": tokens / steps / (1 if w.tp > 1 else world)},
+                       "tokens_per_step": tokens / steps / (1 if main_tp > 1 else world)},
         "spec_on_equals_off": {"sequences_checked": checked, "identical": bool(identical)},
-        "setup_s": {"build_model": round(w.build_s, 1), "speculation_off_run": round(off_s, 1)},
+        "setup_s": {"build_model": round(build_s, 1), "speculation_off_run": round(off_s, 1)},
     }
+    if per_rank:
+        line["per_rank"] = per_rank
+    if tp_rec:
+        line["tp"] = tp_rec
     if want_cpu:
-        ctxs = [len(p) + gen // 2 for p in w.prompts]
-        r = cpu_reference(args.workload, w.cpu_sample, ctxs, 3, 0, budget_s=60.0)
-        line["cpu_baseline"] = {"value": (tokens / steps) / r["step_s"], "unit": "tok/s", "cores": r["cores"], "kind": "port",
-                                "sample": r["sample"], "ms_per_step": r["step_s"] * 1e3}
+        r = cpu_reference(args.workload, cpu_sample, cpu_ctxs, 6, 1, budget_s=45.0)
+        per_seq_tokens = (tokens / steps) / batch
+        line["cpu_baseline"] = {"value": per_seq_tokens / r["forward_s"], "unit": "tok/s", "cores": r["cores"], "threads": r["threads"],
+                                "kind": "port", "sample": r["sample"], "ms_per_forward": r["forward_s"] * 1e3,
+                                "ms_per_batch_round": r["forward_s"] * 1e3 * batch}
     print(json.dumps(line))
-    w.close()
     if dist:
         dist.destroy_process_group()
 

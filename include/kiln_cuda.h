@@ -76,7 +76,10 @@ KC_API const char* kc_last_error(void);
 KC_API int64_t kc_live_objects(void);
 
 /* Blocks until all work queued on the context's stream has finished
- * (the `eval` boundary, crates/kiln-engine/src/engine.rs:2302-2310). */
+ * (the `eval` boundary, crates/kiln-engine/src/engine.rs:2302-2310). Returns KC_ERR_TIMEOUT, and clears
+ * the device status word, when a kernel of that work gave up a bounded wait: results queued since the
+ * previous synchronisation are then not valid. kc_verify_step and kc_draft_chain, which synchronise
+ * themselves, report the same way. */
 KC_API int kc_sync(kc_ctx_t ctx);
 
 /* The context's CUDA stream as a cudaStream_t, for callers that time with
@@ -93,7 +96,8 @@ KC_API int kc_device_status(kc_ctx_t ctx, uint32_t* status);
 KC_API int64_t kc_launch_count(kc_ctx_t ctx);
 
 /* Device time of the most recent kc_verify_step on this context, in milliseconds: CUDA events on the
- * context's stream, from just before the step's metadata copy to just after its result copy. */
+ * context's stream, from just before the step's metadata copy is queued (after the host has packed it)
+ * to just after its result copy. */
 KC_API double kc_last_step_ms(kc_ctx_t ctx);
 
 /* Optional per-class device timing: while enabled, every launch is bracketed by CUDA events on the

@@ -88,6 +88,10 @@ KH_API uint64_t kh_radix_insert_partial_child(kh_radix_t r, uint64_t parent, con
 KH_API int64_t kh_radix_upgrade_partial(kh_radix_t r, uint64_t node, const uint32_t* tokens, uint64_t n, uint32_t block);
 KH_API void kh_radix_set_resident(kh_radix_t r, uint64_t node, uint32_t block);
 KH_API void kh_radix_touch(kh_radix_t r, uint64_t node);
+/* The cold-tier flag of a node (radix.rs: set_on_ssd / node_on_ssd): an evicted node that has it stays in the tree
+ * without a block, so a later walk can find and reload it. The slab files themselves are not part of this library. */
+KH_API void kh_radix_set_on_ssd(kh_radix_t r, uint64_t node);
+KH_API int32_t kh_radix_node_on_ssd(kh_radix_t r, uint64_t node);
 KH_API int64_t kh_radix_evict_candidate(kh_radix_t r, kh_bm_t bm);
 KH_API int64_t kh_radix_evict(kh_radix_t r, kh_bm_t bm, uint64_t node);
 KH_API void kh_radix_prune_subtree(kh_radix_t r, kh_bm_t bm, uint64_t node);

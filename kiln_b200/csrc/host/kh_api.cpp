@@ -142,6 +142,8 @@ int64_t kh_radix_upgrade_partial(kh_radix_t r, uint64_t node, const uint32_t* to
 }
 void kh_radix_set_resident(kh_radix_t r, uint64_t node, uint32_t block) { r->p->set_resident(node, block); }
 void kh_radix_touch(kh_radix_t r, uint64_t node) { r->p->touch(node); }
+void kh_radix_set_on_ssd(kh_radix_t r, uint64_t node) { r->p->set_on_ssd(node); }
+int32_t kh_radix_node_on_ssd(kh_radix_t r, uint64_t node) { return r->p->node_on_ssd(node) ? 1 : 0; }
 int64_t kh_radix_evict_candidate(kh_radix_t r, kh_bm_t bm) { return r->p->evict_candidate(*bm->p); }
 int64_t kh_radix_evict(kh_radix_t r, kh_bm_t bm, uint64_t node) { return r->p->evict(*bm->p, node); }
 void kh_radix_prune_subtree(kh_radix_t r, kh_bm_t bm, uint64_t node) { r->p->prune_subtree(*bm->p, node); }

@@ -948,7 +948,10 @@ int validate_step(kc_model* m, kc_kv* kv, const uint32_t* token_ids, int32_t n, 
 }
 
 // Packs the metadata on the host and queues the single host->device copy.
-int upload_meta(kc_model* m, kc_kv* kv, const uint32_t* token_ids, const kc_seq_step* seqs, const StepPlan& p) {
+// `before_copy` (optional) is recorded on the stream after the host-side packing and before the copy is queued: the
+// device span of a step starts there, so host packing time is not counted as device time.
+int upload_meta(kc_model* m, kc_kv* kv, const uint32_t* token_ids, const kc_seq_step* seqs, const StepPlan& p,
+                cudaEvent_t before_copy = nullptr) {
   kc_ctx* c = m->ctx;
   const MetaLayout& L = p.lay;
   if (L.total > m->meta_cap) {
@@ -997,6 +1000,7 @@ int upload_meta(kc_model* m, kc_kv* kv, const uint32_t* token_ids, const kc_seq_
     for (int t = s.len - s.sample_rows + 1; t < s.len; ++t) v_draft[dat++] = token_ids[row + t];
     row += s.len;
   }
+  if (before_copy) CK(cudaEventRecord(before_copy, c->stream));
   CK(cudaMemcpyAsync(m->meta_dev, hbuf, L.total, cudaMemcpyHostToDevice, c->stream));
   CK(cudaEventRecord(m->meta_ev[slot], c->stream));
   return KC_OK;
@@ -1140,8 +1144,7 @@ extern "C" int kc_verify_step(kc_model_t m, kc_kv_t kv, const uint32_t* token_id
   if (rc) return rc;
   kc_ctx* c = m->ctx;
   CK(cudaSetDevice(c->device));
-  CK(cudaEventRecord(c->step_a, c->stream));
-  if ((rc = upload_meta(m, kv, token_ids, seqs, p))) return rc;
+  if ((rc = upload_meta(m, kv, token_ids, seqs, p, c->step_a))) return rc;
   if ((rc = run_forward(m, kv, reinterpret_cast<const uint32_t*>(m->meta_dev + p.lay.tokens), p, true))) return rc;
   if (p.n_sampled > 0) {
     LAUNCH(c, KC_PROF_SAMPLE, 1, launch_greedy_rows(m->logits, p.n_sampled, m->d.vocab_size, 1, m->row_tokens, c->stream));

@@ -20,7 +20,7 @@ __device__ __forceinline__ ArgMax better(ArgMax a, ArgMax b) {
 
 // sample_from_row + Sampler::sample, greedy lane (crates/kiln-engine/src/engine.rs:879-901,
 // crates/kiln-engine/src/sampler.rs:100-104): logprobs = logits - logsumexp(logits) in the
-// logits dtype, then argmax. The logsumexp accumulates in fp32 and is rounded to bf16 before
+// logits dtype, then argmax. The logsumexp accumulates in double and is rounded to bf16 before
 // the subtraction; the subtraction result is rounded to bf16, which can merge neighbouring
 // logits into ties — hence the explicit lowest-index rule.
 // normalize == 0: argmax of the raw row (crates/kiln-models/src/draft.rs:379-381).
@@ -28,54 +28,55 @@ __global__ void __launch_bounds__(1024)
 greedy_rows_kernel(const bf16* __restrict__ logits, int vocab, int normalize, uint32_t* __restrict__ tokens) {
   pdl_launch_dependents();
   pdl_wait();
-  __shared__ float red_m[32], red_s[32];
+  __shared__ float red_m[32];
+  __shared__ double red_s[32];
   __shared__ ArgMax red_a[32];
   __shared__ float s_lse;
   const bf16* row = logits + (size_t)blockIdx.x * vocab;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   const bool vec = (vocab & 7) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0;   // rows start on 16-byte boundaries
   if (normalize) {
-    float m = -INFINITY, s = 0.f;
+    // Pass 1: the row maximum (exact). Pass 2: sum of exp(x - max), every term from the full-precision expf, the
+    // running sums in double, so that the logsumexp — max + float(log(sum)), then one rounding to bf16 — lands on
+    // the same bf16 value as a double-precision evaluation unless it sits within about 1e-6 of a rounding boundary.
+    float m = -INFINITY;
     if (vec) {
-      // 8 logits per 16-byte load; the running (max, sum) is rescaled once per vector
       for (int i = threadIdx.x * 8; i < vocab; i += blockDim.x * 8) {
         float x[8];
         load8_bf16(row + i, x);
-        float vm = x[0];
 #pragma unroll
-        for (int k = 1; k < 8; ++k) vm = fmaxf(vm, x[k]);
-        if (vm > m) { s *= __expf(m - vm); m = vm; }
-#pragma unroll
-        for (int k = 0; k < 8; ++k) s += __expf(x[k] - m);
+        for (int k = 0; k < 8; ++k) m = fmaxf(m, x[k]);
       }
     } else {
-      for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        const float x = __bfloat162float(row[i]);
-        if (x > m) { s = s * __expf(m - x) + 1.f; m = x; }
-        else s += __expf(x - m);
-      }
+      for (int i = threadIdx.x; i < vocab; i += blockDim.x) m = fmaxf(m, __bfloat162float(row[i]));
     }
-    // merge (m, s) pairs
+    m = warp_max(m);
+    if (lane == 0) red_m[warp] = m;
+    __syncthreads();
+    m = lane < nw ? red_m[lane] : -INFINITY;
+    m = warp_max(m);                       // every thread now holds the row maximum
+    double sum = 0.0;
+    if (vec) {
+      for (int i = threadIdx.x * 8; i < vocab; i += blockDim.x * 8) {
+        float x[8];
+        load8_bf16(row + i, x);
+        float part = 0.f;                  // eight terms in fp32 (each at most 1), then into the double sum
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float m2 = __shfl_xor_sync(0xffffffffu, m, o), s2 = __shfl_xor_sync(0xffffffffu, s, o);
-      const float mm = fmaxf(m, m2);
-      s = (m == -INFINITY ? 0.f : s * __expf(m - mm)) + (m2 == -INFINITY ? 0.f : s2 * __expf(m2 - mm));
-      m = mm;
+        for (int k = 0; k < 8; ++k) part += expf(x[k] - m);
+        sum += (double)part;
+      }
+    } else {
+      for (int i = threadIdx.x; i < vocab; i += blockDim.x) sum += (double)expf(__bfloat162float(row[i]) - m);
     }
-    if (lane == 0) { red_m[warp] = m; red_s[warp] = s; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane == 0) red_s[warp] = sum;
     __syncthreads();
     if (warp == 0) {
-      m = lane < nw ? red_m[lane] : -INFINITY;
-      s = lane < nw ? red_s[lane] : 0.f;
+      sum = lane < nw ? red_s[lane] : 0.0;
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        const float m2 = __shfl_xor_sync(0xffffffffu, m, o), s2 = __shfl_xor_sync(0xffffffffu, s, o);
-        const float mm = fmaxf(m, m2);
-        s = (m == -INFINITY ? 0.f : s * __expf(m - mm)) + (m2 == -INFINITY ? 0.f : s2 * __expf(m2 - mm));
-        m = mm;
-      }
-      if (lane == 0) s_lse = bf16_round(m + logf(s));
+      for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      if (lane == 0) s_lse = bf16_round(m + (float)log(sum));
     }
     __syncthreads();
   }

@@ -92,6 +92,7 @@ _SIGNATURES = {
     "kh_radix_insert_partial_child": (_U64, [_P, _U64, _U32P, _U64]),
     "kh_radix_upgrade_partial": (_I64, [_P, _U64, _U32P, _U64, C.c_uint32]),
     "kh_radix_set_resident": (None, [_P, _U64, C.c_uint32]), "kh_radix_touch": (None, [_P, _U64]),
+    "kh_radix_set_on_ssd": (None, [_P, _U64]), "kh_radix_node_on_ssd": (_I32, [_P, _U64]),
     "kh_radix_evict_candidate": (_I64, [_P, _P]), "kh_radix_evict": (_I64, [_P, _P, _U64]),
     "kh_radix_prune_subtree": (None, [_P, _P, _U64]), "kh_radix_resident_blocks": (_U64, [_P]), "kh_radix_reset": (None, [_P]),
     "kh_engine_default_config": (None, [C.POINTER(KhEngineConfig)]),
@@ -331,6 +332,12 @@ class RadixCache:
 
     def touch(self, node: int) -> None:
         lib().kh_radix_touch(self._h, node)
+
+    def set_on_ssd(self, node: int) -> None:
+        lib().kh_radix_set_on_ssd(self._h, node)
+
+    def node_on_ssd(self, node: int) -> bool:
+        return bool(lib().kh_radix_node_on_ssd(self._h, node))
 
     def evict_candidate(self, mgr: BlockManager) -> Optional[int]:
         r = int(lib().kh_radix_evict_candidate(self._h, mgr._h))

@@ -32,6 +32,7 @@
 // oracle/bookkeeping.py and IS pinned by the reference's in-tree unit tests.
 #include <algorithm>
 #include <cmath>
+#include <omp.h>
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
@@ -453,6 +454,13 @@ KO_API int ko_forward_step(ko_model* mp, ko_kv* kv, const uint32_t* token_ids, i
   }
   for (size_t i = 0; i < lg.size(); ++i) logits_out[i] = f2b(lg[i]);
   return 0;
+}
+
+// Worker threads of the OpenMP regions in this file: the timed CPU baseline sets them explicitly, because launchers
+// such as torchrun export OMP_NUM_THREADS=1 to every rank. Returns the count now in force.
+KO_API int ko_set_threads(int n) {
+  if (n > 0) omp_set_num_threads(n);
+  return omp_get_max_threads();
 }
 
 // Greedy token per row (engine.rs:899-900 + sampler.rs:102-104 when normalize, draft.rs:379-381 otherwise).

@@ -55,6 +55,11 @@ def lib() -> C.CDLL:
     return _lib
 
 
+def set_threads(n: int) -> int:
+    """Sets the OpenMP thread count of the oracle (0: leave as is) and returns the count in force."""
+    return int(lib().ko_set_threads(int(n)))
+
+
 def set_weight_class(cls: int) -> None:
     """0 = MLX's row-vector (qmv) arithmetic class, 1 = its tile (qmm) class; see kiln_oracle.cpp."""
     lib().ko_set_weight_class(int(cls))

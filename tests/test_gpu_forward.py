@@ -18,7 +18,7 @@ from kiln_b200 import api
 from kiln_b200.synth import PRESETS, synth_checkpoint
 from oracle import oracle as O
 from oracle.bookkeeping import BlockManager, BlockTable, settle_walk
-from tests.conftest import cosine
+from tests.conftest import cosine, parity
 
 pytestmark = pytest.mark.gpu
 
@@ -39,13 +39,6 @@ def load(ctx, name, num_blocks=64):
 # Logits bar per model. 2e-2 is the north-star bar; on the 2048-wide model rounding noise alone is larger: the
 # oracle's own two MLX arithmetic classes are 3.6e-2 apart on it, so it is held to 4e-2.
 BAR = {"tiny-llama-h2048": 4e-2}
-
-
-def within(got, want, bar):
-    """The logits bar: max-abs <= `bar`, plus one bf16 spacing at the value's own magnitude — two bf16 logits of
-    magnitude 4 or more cannot be closer than 0.03 unless they are equal, whatever computed them."""
-    g, w = got.float(), want.float()
-    return float(((g - w).abs() - (bar + w.abs() * 2 ** -7)).max()) <= 0
 
 
 def prompts(cfg, lens, seed):
@@ -74,10 +67,8 @@ def test_logits_and_kv_match_oracle(ctx, name):
     got = model.forward_step(batch, kv)
     ctx.sync()
     got = got.cpu()
-    assert within(got, want, BAR.get(name, 2e-2))
-    assert cosine(got, want) >= 0.9999
-    assert within(got, want_rowvec, 2 * BAR.get(name, 2e-2))
-    assert cosine(got, want_rowvec) >= 0.9999
+    assert parity(f"{name} prefill logits vs oracle (tile class)", got, want, BAR.get(name, 2e-2))
+    assert parity(f"{name} prefill logits vs oracle (row-vector class)", got, want_rowvec, 2 * BAR.get(name, 2e-2))
     # then a mixed step: two verify segments (k = 4) and one plain decode
     g = torch.Generator().manual_seed(2)
     seqs, ids = [], []
@@ -93,8 +84,7 @@ def test_logits_and_kv_match_oracle(ctx, name):
     ctx.sync()
     got = got.cpu()
     assert got.shape == want.shape == (11, cfg.vocab_size)
-    assert within(got, want, BAR.get(name, 2e-2))
-    assert cosine(got, want) >= 0.9999
+    assert parity(f"{name} verify-step logits vs oracle (tile class)", got, want, BAR.get(name, 2e-2))
     # greedy tokens from IDENTICAL logits are bit-exact
     assert np.array_equal(api.greedy_rows(ctx, got.cuda()).cpu().numpy().astype(np.uint32), O.greedy_rows(got))
     # K/V rows written by both steps agree with the oracle's pools (bf16 values within 2 ulp)

@@ -91,3 +91,59 @@ def test_rope_kv_write_and_block_io(ctx):
     assert kv.read_block_bytes(5) == kv.read_block_bytes(4)
     kv.write_block_bytes(0, kv.read_block_bytes(1))
     assert kv.read_block_bytes(0) == kv.read_block_bytes(1)
+
+
+def _bf16_neighbours(v: float):
+    """The bf16 value at or below v and the next one above it (v > 0)."""
+    assert v > 0
+    bits = int(torch.tensor(v, dtype=torch.float32).to(torch.bfloat16).view(torch.int16))
+    if float(torch.tensor(bits, dtype=torch.int16).view(torch.bfloat16)) > v:
+        bits -= 1
+    lo, hi = (float(torch.tensor(b, dtype=torch.int16).view(torch.bfloat16)) for b in (bits, bits + 1))
+    assert lo <= v < hi
+    return lo, hi
+
+
+def _boundary_rows(vocab: int, n: int, seed: int) -> torch.Tensor:
+    """Rows whose logsumexp sits within about 1e-4 of a bf16 rounding boundary (the midpoint of two neighbouring bf16
+    values): one low-weight logit is stepped through its bf16 values until the row's float64 logsumexp is as close to
+    the midpoint as its spacing allows. A row like this decides whether an fp32 logsumexp rounds the way a double one does."""
+    g = torch.Generator().manual_seed(seed)
+    rows = []
+    while len(rows) < n:
+        x = torch.empty(vocab).normal_(0, 2.0, generator=g).to(torch.bfloat16)
+        lse = float(torch.logsumexp(x.double(), 0))
+        lo, hi = _bf16_neighbours(lse)
+        mid = 0.5 * (lo + hi)
+        j = int(torch.randint(0, vocab, (1,), generator=g))
+        rest = torch.logsumexp(torch.cat((x[:j], x[j + 1:])).double(), 0)
+        # candidates for x[j]: the bf16 values in a band 3..7 below the logsumexp (weight e^-3 .. e^-7 of the sum)
+        cand = torch.arange(lse - 7.0, lse - 3.0, 2 ** -6).to(torch.bfloat16).unique()
+        lses = torch.logaddexp(rest, cand.double())
+        best = int((lses - mid).abs().argmin())
+        if abs(float(lses[best]) - mid) < 2e-4:
+            x[j] = cand[best]
+            rows.append(x)
+    return torch.stack(rows)
+
+
+@pytest.mark.parametrize("vocab", [128256, 152064, 256000])
+def test_greedy_rows_by_the_thousand(ctx, vocab):
+    """4096 random rows per vocabulary size of the benchmark models, plus rows built so that the logsumexp lies next
+    to a bf16 rounding boundary: the device's tokens equal the oracle's (double-precision logsumexp) on every row."""
+    torch.manual_seed(vocab)
+    chunk, total, bad = 512, 4096, 0
+    for c in range(total // chunk):
+        scale = (0.5, 1.0, 2.0, 4.0)[c % 4]
+        x = (torch.randn(chunk, vocab, device="cuda") * scale).to(torch.bfloat16)
+        if c == 0:
+            x[:, 7] = x.max(dim=1).values           # an exact tie with the row maximum in every row
+        got = api.greedy_rows(ctx, x, True).cpu().numpy().astype(np.uint32)
+        want = O.greedy_rows(x.cpu(), True)
+        bad += int((got != want).sum())
+        got_r = api.greedy_rows(ctx, x, False).cpu().numpy().astype(np.uint32)
+        assert np.array_equal(got_r, O.greedy_rows(x.cpu(), False))
+    assert bad == 0, f"{bad} of {total} rows picked another token than the oracle"
+    edge = _boundary_rows(vocab, 24, vocab)
+    got = api.greedy_rows(ctx, edge.cuda(), True).cpu().numpy().astype(np.uint32)
+    assert np.array_equal(got, O.greedy_rows(edge, True)), "a row next to a logsumexp rounding boundary rounded the other way"
