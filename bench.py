@@ -70,7 +70,7 @@ def peaks():
 
 class ClockSampler:
     """Samples SM clocks, power and clock-event reasons WHILE the timed region runs (reads only, nothing is set):
-    NVML from a thread every 5 ms; nvidia-smi in a loop when the NVML binding is missing."""
+    NVML from a polling thread; nvidia-smi in a loop when the NVML binding is missing."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
     REASONS = {"hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40, "sw_power_cap": 0x4}
@@ -107,15 +107,17 @@ class ClockSampler:
             self.proc = None
 
     def _poll(self):
-        n = self.nvml
+        n, i, power = self.nvml, 0, 0.0
         while not self.stop_flag:
             try:
+                if i % 8 == 0:   # the power query is the slow one
+                    power = n.nvmlDeviceGetPowerUsage(self.handle) / 1000.0
                 self.samples.append((n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM),
-                                     n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle),
-                                     n.nvmlDeviceGetPowerUsage(self.handle) / 1000.0))
+                                     n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle), power))
             except Exception:
                 pass
-            time.sleep(0.005)
+            i += 1
+            time.sleep(0.002)
 
     def _read(self):
         for line in self.proc.stdout:
@@ -131,7 +133,7 @@ class ClockSampler:
                 mask |= int(s_[1])
             reasons = sorted(k for k, bit in self.REASONS.items() if mask & bit)
             return {"sm_mhz": float(sm[len(sm) // 2]) if sm else None, "sm_max_mhz": float(self.max_sm), "reasons": reasons,
-                    "samples": len(sm), "power_w_max": max((s_[2] for s_ in self.samples), default=None), "source": "nvml, 5 ms period"}
+                    "samples": len(sm), "power_w_max": max((s_[2] for s_ in self.samples), default=None), "source": "nvml polling thread"}
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no NVML binding and no nvidia-smi"], "samples": 0}
         self.proc.terminate()

@@ -423,7 +423,7 @@ static int run_qlinear(kc_ctx* c, const QWeight& w, const ActOperand& x, int M, 
     QLinearLaunch l;
     l.w = &w; l.x = &x; l.row0 = row0; l.M = std::min(QL_MAX_M, M - row0);
     l.y = y; l.ldy = ldy; l.partial = partial; l.status = c->status;
-    LAUNCH(c, KC_PROF_GEMM, 1, qlinear_umma(l, c->stream));
+    LAUNCH(c, KC_PROF_GEMM, qlinear_launches(w, l.M), qlinear_umma(l, c->stream));
     if (w.splits > 1 && !defer)
       LAUNCH(c, KC_PROF_GEMM_REDUCE, 1, qlinear_reduce_splits(partial, w.splits, l.M, w.N, y + (size_t)row0 * ldy, ldy, c->stream));
   }
@@ -443,7 +443,7 @@ static int run_gated(kc_ctx* c, const QWeight& w, const ActOperand& x, int M, bf
     l.w = &w; l.x = &x; l.row0 = row0; l.M = rows;
     l.y = gu; l.ldy = 2 * F; l.partial = partial; l.status = c->status;
     if (interleaved) { l.glu = gelu ? 2 : 1; l.act = act; l.ld_act = F; l.glu_done = &done; }
-    LAUNCH(c, KC_PROF_GEMM, 1, qlinear_umma(l, c->stream));
+    LAUNCH(c, KC_PROF_GEMM, qlinear_launches(w, rows), qlinear_umma(l, c->stream));
     if (done) continue;
     if (w.splits > 1)
       LAUNCH(c, KC_PROF_GEMM_REDUCE, 1, qlinear_reduce_splits(partial, w.splits, rows, w.N, gu + (size_t)row0 * 2 * F, 2 * F, c->stream));

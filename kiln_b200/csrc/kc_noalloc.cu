@@ -85,7 +85,7 @@ extern "C" int kc_quantized_matmul_static(kc_ctx_t c, kc_qweight_t q, const void
     l.y = y; l.ldy = w.N; l.partial = scratch; l.status = cv.status;
     // launches are counted once they are queued; this entry point takes no part in kc_profile_* timing
     e = qlinear_umma(l, cv.stream);
-    if (e == cudaSuccess) ctx_count_launches(c, 0, 1);
+    if (e == cudaSuccess) ctx_count_launches(c, 0, qlinear_launches(w, l.M));
     if (e == cudaSuccess && w.splits > 1) {
       e = qlinear_reduce_splits(scratch, w.splits, l.M, w.N, y + (size_t)row0 * w.N, w.N, cv.stream);
       if (e == cudaSuccess) ctx_count_launches(c, 1, 1);

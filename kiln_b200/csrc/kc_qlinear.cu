@@ -1,16 +1,18 @@
 // Affine-dequant GEMM for sm_100a. See kc_qlinear.cuh for the data layout.
 //
-// qlinear_umma_kernel — one CTA per (128-row weight tile, k-split):
+// qlinear_umma_ta_kernel — one CTA per (one or two 128-row weight tiles, k-split), 20 warps:
 //   warp 0      bulk-copies the weight records (cp.async.bulk, mbarrier tx)
 //   warp 1      TMA-loads the activation k-blocks (cp.async.bulk.tensor, 128B swizzle)
-//   warp 2      allocates TMEM, issues tcgen05.mma (weights = A/M side, activations = B/N side)
-//   warps 4-11  unpack the 4/8-bit words, apply scale/bias, write the bf16 A
-//               tile in the K-major 128-byte-swizzled layout the MMA reads;
-//               afterwards drain TMEM (tcgen05.ld) into y or the split-K partials.
+//   warps 2-3   allocate TMEM, issue tcgen05.mma (weights = A/M side from TENSOR MEMORY, activations = B/N side
+//               from shared memory)
+//   warps 4-19  unpack the 4/8-bit words, apply scale/bias in registers and write the bf16 A operand into tensor
+//               memory with tcgen05.st; afterwards drain the accumulators (tcgen05.ld) into y, the split-K
+//               partials or the gated activation.
 // The accumulator D[n, m] lives in TMEM: lane = weight row n, column = activation row m.
 // Every output element depends only on its own activation row and on a k order
 // fixed by (N, K), which is what lets verify rows share a step with other rows
-// and still reproduce the bits of a one-row decode.
+// and still reproduce the bits of a one-row decode. Launches of more rows than one accumulator set holds are cut
+// into row chunks, each its own launch over the same weights: rows are independent, so no bit changes.
 #include "kc_qlinear.cuh"
 
 #include <algorithm>
@@ -255,27 +257,6 @@ __device__ __forceinline__ uint32_t umma_idesc_bf16(int m, int n) {
   return d;
 }
 
-__device__ __forceinline__ void umma_bf16_ss(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
-                                             uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// Same instruction with the two shared-memory descriptors given as (low word, shared high word).
-__device__ __forceinline__ void umma_bf16_ss2(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t d_hi,
-                                              uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
-      "mov.b64 da, {%1, %3};\n\t"
-      "mov.b64 db, {%2, %3};\n\t"
-      "setp.ne.b32 p, %5, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
-      ::"r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(d_hi), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                    smem_u32(bar))
@@ -325,7 +306,8 @@ struct QlKernelParams {
   bf16* act; int ld_act;
   uint32_t tmem_cols;    // power of two >= max(32, NT * m_pad)
   bf16* y; int ldy;
-  float* partial;
+  float* partial;        // [splits][part_M][N]; this launch writes rows part_row0 .. part_row0 + M
+  int part_M, part_row0;
   uint32_t* status;
 };
 
@@ -411,7 +393,7 @@ __device__ __forceinline__ void ql_epilogue(const QlKernelParams& p, uint8_t* sm
           for (int c = 0; c < 4 && n + c < p.N; ++c) dst[c] = __float2bfloat16_rn(e[c]);
         }
       } else {
-        float* dst = p.partial + ((size_t)split * p.M + m) * p.N + n;
+        float* dst = p.partial + ((size_t)split * p.part_M + p.part_row0 + m) * p.N + n;
         if (vec_ok && n + 3 < p.N) {
           *reinterpret_cast<float4*>(dst) = f;
         } else {
@@ -423,245 +405,20 @@ __device__ __forceinline__ void ql_epilogue(const QlKernelParams& p, uint8_t* sm
   }
 }
 
-// BITS: 4 or 8. GPK: scale/bias pairs per row per k-block (1 or 2). NT: 128-row weight tiles per CTA, all
-// multiplied against the same activation k-block (NT * m_pad TMEM columns), which divides the activation
-// traffic from L2 by NT. NT is free to depend on the row count: it changes which CTA computes an output
-// element, never the order in which that element's k-blocks are accumulated.
-//
-// KC: 64-feature k-blocks per pipeline stage (1 or 2). The per-stage cost of the MMA issuer and of the barrier
-// hand-offs does not depend on how much a stage holds, so a CTA with a single tile (NT == 1) takes two k-blocks per
-// stage; they are multiplied in ascending k order into the same accumulator, so no bit changes.
-//
-// Warp roles: 0 = weight-record producer (bulk copies), 1 = activation producer (TMA), 2 = MMA issuer and
-// TMEM owner, 3 = second MMA issuer when the CTA owns several tiles, 4..19 = two dequantiser groups of eight warps that take alternate k-blocks (the waits,
-// the proxy fence and the barrier round trip of one group hide behind the other group's arithmetic), then
-// all sixteen drain TMEM.
-template <int BITS, int GPK, int NT, int KC>
-__global__ void __launch_bounds__(QL_THREADS, 1)
-qlinear_umma_kernel(const __grid_constant__ CUtensorMap map16, const __grid_constant__ CUtensorMap map64,
-                    const QlKernelParams p) {
-  constexpr uint32_t PACKED = QL_TILE_N * (QL_KB * BITS / 8);
-  extern __shared__ uint8_t smem_raw[];
-  // 1024-byte alignment for the swizzled tiles.
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  const int AS = p.a_stages, RS = p.r_stages;
-  const uint32_t b_bytes = (uint32_t)p.m_pad * 128u;
-  constexpr int UNITS = NT * KC;                      // (k-block, tile) units of one stage, k-block major
-  const uint32_t a_stage = UNITS * QL_A_BYTES;
-  const uint32_t bk_bytes = b_bytes;                   // one activation k-block
-  const uint32_t b_stage = KC * bk_bytes;
-  const uint32_t r_stage = UNITS * p.raw_stride;
-  uint8_t* sA = smem;
-  uint8_t* sB = sA + (size_t)AS * a_stage;
-  uint8_t* sR = sB + (size_t)AS * b_stage;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sR + (size_t)RS * r_stage);
-  uint64_t* raw_full = bars;
-  uint64_t* raw_empty = raw_full + RS;
-  uint64_t* b_full = raw_empty + RS;
-  uint64_t* a_ready = b_full + AS;
-  uint64_t* ab_empty = a_ready + AS;
-  uint64_t* acc_full = ab_empty + AS;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile0 = blockIdx.x * NT, split = blockIdx.y;
-  const int nt_live = min(NT, p.n_tiles - tile0);   // tiles this CTA really owns
-  const int kb0 = split * p.kb_per_split;
-  const int nkb = p.kb_per_split / KC;                 // pipeline iterations (stages) of this CTA
-  // MMA issue is split by tile between warps 2 and 3 (independent accumulators, so no ordering between them):
-  // one thread's issue rate, sharing its scheduler with dequantiser warps, does not keep the tensor pipe fed.
-  constexpr int T_SPLIT = (NT + 1) / 2;
-  const int n_issuers = nt_live > T_SPLIT ? 2 : 1;
-
-  pdl_launch_dependents();
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < RS; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], QL_DQ_GROUP_WARPS); }
-    for (int i = 0; i < AS; ++i) { mbar_init(&b_full[i], 1); mbar_init(&a_ready[i], QL_DQ_GROUP_WARPS); mbar_init(&ab_empty[i], n_issuers); }
-    mbar_init(acc_full, n_issuers);
-    mbar_fence_init();
-  }
-  if (warp == 2) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                 "r"(p.tmem_cols)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
-  if (warp == 1 && lane == 0) { tma_prefetch_desc(&map16); tma_prefetch_desc(&map64); }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-
-  if (warp == 0) {
-    // ---- weight record producer: one bulk copy per owned tile per k-block ----
-    if (lane == 0) {
-      RingPos rp;
-      for (int i = 0; i < nkb; ++i, rp.advance(RS)) {
-        const int rs = rp.stage; const uint32_t ph = rp.phase;
-        if (!mbar_wait(&raw_empty[rs], ph ^ 1, p.status, KC_DEV_QLINEAR | 1)) break;
-        // the records of this CTA's tiles for one k-block are neighbours in memory: one copy per k-block
-        mbar_arrive_expect_tx(&raw_full[rs], p.record_bytes * nt_live * KC);
-#pragma unroll
-        for (int kc = 0; kc < KC; ++kc)
-          bulk_g2s(sR + (size_t)rs * r_stage + (size_t)kc * NT * p.raw_stride,
-                   p.records + (((size_t)(tile0 / QL_TILE_GROUP) * p.kblocks + kb0 + i * KC + kc) * QL_TILE_GROUP + tile0 % QL_TILE_GROUP) * p.record_bytes,
-                   p.record_bytes * nt_live, &raw_full[rs]);
-      }
-    }
-  } else if (warp == 1) {
-    // ---- activation producer: the first access of this kernel to memory written by earlier kernels ----
-    if (lane == 0) {
-      pdl_wait();
-      const int n64 = p.m_pad / 64, n16 = (p.m_pad % 64) / 16;
-      RingPos ap;
-      for (int i = 0; i < nkb; ++i, ap.advance(AS)) {
-        const int as = ap.stage; const uint32_t ph = ap.phase;
-        if (!mbar_wait(&ab_empty[as], ph ^ 1, p.status, KC_DEV_QLINEAR | 2)) break;
-        mbar_arrive_expect_tx(&b_full[as], b_stage);
-#pragma unroll
-        for (int kc = 0; kc < KC; ++kc) {
-          uint8_t* dst = sB + (size_t)as * b_stage + (size_t)kc * bk_bytes;
-          const int x = (kb0 + i * KC + kc) * QL_KB;
-          if (p.b_single) {
-            tma_load_2d(dst, &map16, x, p.row0, &b_full[as]);   // map16 then is the map whose box spans all m_pad rows
-          } else {
-            int row = 0;
-            for (int j = 0; j < n64; ++j, row += 64) tma_load_2d(dst + row * 128, &map64, x, p.row0 + row, &b_full[as]);
-            for (int j = 0; j < n16; ++j, row += 16) tma_load_2d(dst + row * 128, &map16, x, p.row0 + row, &b_full[as]);
-          }
-        }
-      }
-    }
-  } else if (warp == 2 || warp == 3) {
-    // ---- MMA issuers: one thread each; the per-k-block instruction count is the serial part of the pipeline,
-    //      so descriptors are kept as 32-bit halves (only the 14-bit start-address field changes) ----
-    const int t_lo = warp == 2 ? 0 : T_SPLIT, t_hi = warp == 2 ? min(T_SPLIT, nt_live) : nt_live;
-    if (lane == 0 && t_lo < t_hi) {
-      const int n0 = p.m_pad > 256 ? 256 : p.m_pad;
-      const int n1 = p.m_pad - n0;   // a second accumulator only when NT == 1 and m_pad > 256
-      const uint32_t idesc0 = umma_idesc_bf16(QL_TILE_N, n0);
-      const uint32_t idesc1 = n1 ? umma_idesc_bf16(QL_TILE_N, n1) : 0;
-      const uint32_t col_stride = (uint32_t)(p.m_pad + 31) & ~31u;   // accumulators start on 32-column boundaries
-      const uint64_t proto = umma_smem_desc_sw128(0);
-      const uint32_t d_hi = (uint32_t)(proto >> 32), d_lo = (uint32_t)proto;
-      const uint32_t a_lo0 = d_lo | ((smem_u32(sA) >> 4) & 0x3FFF), b_lo0 = d_lo | ((smem_u32(sB) >> 4) & 0x3FFF);
-      const uint32_t a_step = a_stage >> 4, b_step = b_stage >> 4;
-      uint32_t acc = 0;
-      RingPos ap;
-      // The barrier tests for k-block i + 1 are issued before the MMAs of k-block i and read after them, so
-      // their latency hides behind the issue of the current k-block instead of idling the tensor pipe.
-      bool a_ok = mbar_test_wait(&a_ready[0], 0), b_ok = mbar_test_wait(&b_full[0], 0);
-      for (int i = 0; i < nkb; ++i) {
-        const int as = ap.stage; const uint32_t ph = ap.phase;
-        if (!a_ok && !mbar_wait(&a_ready[as], ph, p.status, KC_DEV_QLINEAR | 3)) break;
-        if (!b_ok && !mbar_wait(&b_full[as], ph, p.status, KC_DEV_QLINEAR | 4)) break;
-        // No tcgen05 fence here: the operands are ordinary shared memory made visible to the async proxy by the
-        // writers' proxy fence and the mbarrier hand-off; a tcgen05.fence would only order this batch of MMAs
-        // behind the completion of the previous one.
-        const uint32_t a_lo = a_lo0 + as * a_step, b_lo = b_lo0 + as * b_step;
-        ap.advance(AS);
-        if (i + 1 < nkb) { a_ok = mbar_test_wait(&a_ready[ap.stage], ap.phase); b_ok = mbar_test_wait(&b_full[ap.stage], ap.phase); }
-#pragma unroll
-        for (int kc = 0; kc < KC; ++kc) {
-          const uint32_t b_kc = b_lo + kc * (bk_bytes >> 4);
-#pragma unroll
-          for (int t = 0; t < NT; ++t) {
-            if (t >= t_lo && t < t_hi) {
-              const uint32_t a_u = a_lo + (kc * NT + t) * (QL_A_BYTES >> 4);
-#pragma unroll
-              for (int ks = 0; ks < QL_KB / 16; ++ks) {
-                // advancing K by 16 bf16 = 32 bytes inside the swizzle row: +2 in the address field
-                umma_bf16_ss2(tmem_base + t * col_stride, a_u + 2 * ks, b_kc + 2 * ks, d_hi, idesc0, ks == 0 ? acc : 1u);
-                if (NT == 1 && n1)
-                  umma_bf16_ss2(tmem_base + 256, a_u + 2 * ks, b_kc + (256 * 128 >> 4) + 2 * ks, d_hi, idesc1, ks == 0 ? acc : 1u);
-              }
-            }
-          }
-          acc = 1u;
-        }
-        umma_commit(&ab_empty[as]);
-      }
-      umma_commit(acc_full);
-    }
-  } else if (warp >= QL_DQ_WARP0) {
-    // ---- dequantisers: thread = (row r, half hf of the k-block's 64 features) of every owned tile: one 16- or
-    //      32-byte load of packed weights, one (scale, bias) pair, four 16-byte stores of bf16 ----
-    const int td = threadIdx.x - QL_DQ_WARP0 * 32;  // 0..511
-    const int grp = td / QL_DQ_GROUP_THREADS;
-    const int tg = td - grp * QL_DQ_GROUP_THREADS;  // 0..255 inside the group
-    const int hf = tg & 1, r = tg >> 1;             // half 0..1, row 0..127
-    const int gi = (GPK == 2) ? hf : 0;
-    // shared-memory offsets that do not change with the k-block
-    const uint32_t raw_off = r * (QL_KB * BITS / 8) + hf * (QL_KB * BITS / 16);   // 16 (w4) or 32 (w8) bytes per half row
-    const uint32_t sb_off = PACKED + (r * GPK + gi) * 4;
-    uint32_t a_off[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) a_off[j] = r * 128 + (((4 * hf + j) ^ (r & 7)) << 4);
-    bool ok = true;
-    RingPos rp, ap;
-    for (int g = 0; g < grp; ++g) { rp.advance(RS); ap.advance(AS); }
-    for (int i = grp; i < nkb && ok; i += QL_DQ_GROUPS) {
-      const int rs = rp.stage; const uint32_t rph = rp.phase;
-      const int as = ap.stage; const uint32_t aph = ap.phase;
-      ok = __all_sync(0xffffffffu, mbar_wait(&raw_full[rs], rph, p.status, KC_DEV_QLINEAR | 5));
-      if (!ok) break;
-      ok = __all_sync(0xffffffffu, mbar_wait(&ab_empty[as], aph ^ 1, p.status, KC_DEV_QLINEAR | 6));
-      if (!ok) break;
-#pragma unroll
-      for (int u = 0; u < UNITS; ++u) {
-        if ((u % NT) < nt_live) {
-          const uint8_t* rec = sR + (size_t)rs * r_stage + (size_t)u * p.raw_stride;
-          uint8_t* a = sA + (size_t)as * a_stage + (size_t)u * QL_A_BYTES;
-          const bf162 sb = *reinterpret_cast<const bf162*>(rec + sb_off);
-          uint4 v[4];
-          if (BITS == 4) {
-            const uint4 q = *reinterpret_cast<const uint4*>(rec + raw_off);
-            v[0] = dequant8_w4(q.x, sb); v[1] = dequant8_w4(q.y, sb); v[2] = dequant8_w4(q.z, sb); v[3] = dequant8_w4(q.w, sb);
-          } else {
-            const uint4 q0 = *reinterpret_cast<const uint4*>(rec + raw_off);
-            const uint4 q1 = *reinterpret_cast<const uint4*>(rec + raw_off + 16);
-            v[0] = dequant8_w8(q0.x, q0.y, sb); v[1] = dequant8_w8(q0.z, q0.w, sb);
-            v[2] = dequant8_w8(q1.x, q1.y, sb); v[3] = dequant8_w8(q1.z, q1.w, sb);
-          }
-#pragma unroll
-          for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(a + a_off[j]) = v[j];
-        }
-      }
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) { mbar_arrive(&raw_empty[rs]); mbar_arrive(&a_ready[as]); }
-#pragma unroll
-      for (int g = 0; g < QL_DQ_GROUPS; ++g) { rp.advance(RS); ap.advance(AS); }
-    }
-    // ---- epilogue: TMEM -> per-warp transpose in shared memory -> row-contiguous vector stores ----
-    pdl_wait();   // the stores below may overwrite what an earlier kernel still reads
-    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(acc_full, 0, p.status, KC_DEV_QLINEAR | 7));
-    if (ok) ql_epilogue<NT>(p, smem, warp, lane, tmem_base, tile0, nt_live, split);
-  }
-  __syncwarp();
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 2) {
-    tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(p.tmem_cols)
-                 : "memory");
-  }
-}
-
-
 // ---------------------------------------------------------------------------
-// The same GEMM with the dequantised weights handed to the tensor core through TENSOR MEMORY instead of shared
-// memory (tcgen05.mma with the A operand in TMEM). Measured reason: an M = 128, N = 192 MMA needs 97 cycles when run
-// alone, but the k-block of the kernel above took ≈ 1140 cycles for eight of them — its 154 KB of shared-memory
-// traffic per k-block (32 KB of bf16 weights written, 32 KB read back by the MMAs, the activation k-block read once
-// per tile, the copies) is what the 128 B/clk shared memory can move in that time. Here a dequantiser thread owns one
-// weight row (= one TMEM lane) of one unit, expands its 64 weights in registers and writes them with one tcgen05.st
-// (column c = weights 2c and 2c + 1), so the MMAs read only the activation k-block from shared memory and the A ring
-// costs no shared memory at all. Units per stage are fixed at two: two tiles of one k-block (NT == 2), or two
-// k-blocks of one tile (NT == 1). Accumulation order per output element is unchanged.
+// The kernel. The dequantised weights reach the tensor core through TENSOR MEMORY (tcgen05.mma with the A operand in
+// TMEM), not through shared memory. Measured reason: an M = 128, N = 192 MMA needs 97 cycles when run alone, but a
+// kernel that staged the bf16 weights in shared memory took about 1140 cycles per k-block of eight of them — its 154 KB
+// of shared-memory traffic per k-block (32 KB of bf16 weights written, 32 KB read back by the MMAs, the activation
+// k-block read once per tile, the copies) is what the 128 B/clk shared memory can move in that time. Here a
+// dequantiser thread owns one weight row (= one TMEM lane) of one unit, expands its 64 weights in registers and writes
+// them with one tcgen05.st (column c = weights 2c and 2c + 1), so the MMAs read only the activation k-block from shared
+// memory and the A ring costs no shared memory at all. Units per stage are fixed at two: two tiles of one k-block
+// (NT == 2), or two k-blocks of one tile (NT == 1; a split with an odd number of k-blocks ends with a one-unit
+// stage). NT is free to depend on the row count: it changes which CTA computes an output element, never the order in
+// which that element's k-blocks are accumulated.
 //
 // TMEM columns: [NT accumulators of round32(m_pad)] [a_stages x 2 units x 32 columns of bf16 pairs].
-// Warp roles as above; warp 3 issues the second tile's MMAs when NT == 2.
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo, uint32_t d_hi, uint32_t idesc,
                                              uint32_t accumulate) {
@@ -714,7 +471,8 @@ qlinear_umma_ta_kernel(const __grid_constant__ CUtensorMap map_rows, const QlKer
   const int tile0 = blockIdx.x * NT, split = blockIdx.y;
   const int nt_live = min(NT, p.n_tiles - tile0);
   const int kb0 = split * p.kb_per_split;
-  const int nst = p.kb_per_split / KC;                  // pipeline stages of this CTA
+  const int nst = (p.kb_per_split + KC - 1) / KC;       // pipeline stages of this CTA
+  const int tail_kc = p.kb_per_split - (nst - 1) * KC;  // k-blocks of the last stage (1 or KC)
   const int n_issuers = (NT == 2 && nt_live == 2) ? 2 : 1;
   const uint32_t col_stride = (uint32_t)(p.m_pad + 31) & ~31u;
   const uint32_t a_col0 = NT * col_stride;              // first column of the A ring
@@ -746,9 +504,11 @@ qlinear_umma_ta_kernel(const __grid_constant__ CUtensorMap map_rows, const QlKer
       RingPos rp;
       for (int i = 0; i < nst; ++i, rp.advance(RS)) {
         if (!mbar_wait(&raw_empty[rp.stage], rp.phase ^ 1, p.status, KC_DEV_QLINEAR | 1)) { ok = false; break; }
-        mbar_arrive_expect_tx(&raw_full[rp.stage], p.record_bytes * nt_live * KC);
+        const int kcs = i == nst - 1 ? tail_kc : KC;
+        mbar_arrive_expect_tx(&raw_full[rp.stage], p.record_bytes * nt_live * kcs);
 #pragma unroll
         for (int kc = 0; kc < KC; ++kc)
+          if (kc < kcs)
           bulk_g2s(sR + (size_t)rp.stage * r_stage + (size_t)kc * NT * p.raw_stride,
                    p.records + (((size_t)(tile0 / QL_TILE_GROUP) * p.kblocks + kb0 + i * KC + kc) * QL_TILE_GROUP + tile0 % QL_TILE_GROUP) * p.record_bytes,
                    p.record_bytes * nt_live, &raw_full[rp.stage]);
@@ -761,9 +521,11 @@ qlinear_umma_ta_kernel(const __grid_constant__ CUtensorMap map_rows, const QlKer
       RingPos bp;
       for (int i = 0; i < nst; ++i, bp.advance(SB)) {
         if (!mbar_wait(&b_empty[bp.stage], bp.phase ^ 1, p.status, KC_DEV_QLINEAR | 2)) { ok = false; break; }
-        mbar_arrive_expect_tx(&b_full[bp.stage], b_stage);
+        const int kcs = i == nst - 1 ? tail_kc : KC;
+        mbar_arrive_expect_tx(&b_full[bp.stage], kcs * bk_bytes);
 #pragma unroll
         for (int kc = 0; kc < KC; ++kc)
+          if (kc < kcs)
           tma_load_2d(sB + (size_t)bp.stage * b_stage + (size_t)kc * bk_bytes, &map_rows, (kb0 + i * KC + kc) * QL_KB, p.row0,
                       &b_full[bp.stage]);
       }
@@ -788,7 +550,7 @@ qlinear_umma_ta_kernel(const __grid_constant__ CUtensorMap map_rows, const QlKer
         const uint32_t a_t = tmem_base + a_col0 + ap.stage * (UNITS * 32);
 #pragma unroll
         for (int u = 0; u < UNITS; ++u) {
-          if (u == 0 ? mine0 : mine1) {
+          if ((u == 0 ? mine0 : mine1) && (NT == 2 || u == 0 || i < nst - 1 || tail_kc == KC)) {
             const int t = NT == 2 ? u : 0, kc = NT == 2 ? 0 : u;
             const uint32_t b_u = b_lo + kc * (bk_bytes >> 4);
 #pragma unroll
@@ -820,7 +582,8 @@ qlinear_umma_ta_kernel(const __grid_constant__ CUtensorMap map_rows, const QlKer
       ok = __all_sync(0xffffffffu, mbar_wait(&raw_full[rp.stage], rp.phase, p.status, KC_DEV_QLINEAR | 5));
       if (!ok) break;
       uint32_t v[32];
-      if (live) {
+      const bool unit_live = live && (NT == 2 || unit == 0 || i < nst - 1 || tail_kc == KC);
+      if (unit_live) {
         const uint8_t* rec = sR + (size_t)rp.stage * r_stage;
         bf162 sb[GPK];
 #pragma unroll
@@ -878,67 +641,40 @@ qlinear_umma_ta_kernel(const __grid_constant__ CUtensorMap map_rows, const QlKer
   }
 }
 
-template <int BITS, int GPK, int NT, int KC>
-static cudaError_t launch_umma(const QLinearLaunch& l, QlKernelParams& p, cudaStream_t s) {
-  const QWeight& w = *l.w;
-  uint32_t cols = 32;
-  while ((int)cols < (NT == 1 ? p.m_pad : NT * ((p.m_pad + 31) & ~31))) cols <<= 1;
-  p.tmem_cols = cols;
-  // Shared memory plan: the A+B ring first (2..4 stages), what is left goes to the raw-record ring.
-  const size_t budget = (size_t)212 * 1024;
-  const size_t ab = (size_t)KC * ((size_t)NT * QL_A_BYTES + (size_t)p.m_pad * 128);
-  const size_t rstage = (size_t)KC * NT * p.raw_stride;
-  int as = (int)std::min<size_t>(4, (budget - 3 * rstage) / ab);
-  if (as < 2) as = 2;
-  as = std::min(as, std::max(2, p.kb_per_split / KC));
-  const size_t left = budget > (size_t)as * ab ? budget - (size_t)as * ab : 0;
-  int rs = (int)std::min<size_t>(24, left / rstage);
-  if (rs < 2) rs = 2;
-  p.a_stages = as; p.r_stages = rs;
-  const size_t smem = 1024 + (size_t)as * ab + (size_t)rs * rstage + (2 * rs + 3 * as + 1) * 8 + 16;
-  if (smem > 227 * 1024) return cudaErrorInvalidValue;
-  static DeviceOnce configured;   // the attribute belongs to the device's copy of the kernel
-  if (configured.first_on_current_device()) {
-    cudaError_t e = cudaFuncSetAttribute(qlinear_umma_kernel<BITS, GPK, NT, KC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    if (e != cudaSuccess) { configured.forget_current_device(); return e; }
-  }
-  dim3 grid((w.n_tiles + NT - 1) / NT, w.splits);
-  const CUtensorMap* first = &l.x->map16;
-  p.b_single = 0;
-  if (p.m_pad <= 256) {
-    first = act_operand_rows_map(l.x, p.m_pad);
-    if (!first) return cudaErrorInvalidValue;
-    p.b_single = 1;
-  }
-  return launch_k(qlinear_umma_kernel<BITS, GPK, NT, KC>, grid, dim3(QL_THREADS), smem, s, *first, l.x->map64, p);
-}
-
-// Launch of the kernel that keeps its A ring in tensor memory. Returns cudaErrorNotSupported when the geometry does not
-// fit (the caller then uses the shared-memory kernel).
-template <int BITS, int GPK, int NT>
-static cudaError_t launch_umma_ta(const QLinearLaunch& l, QlKernelParams& p, cudaStream_t s) {
-  constexpr int KC = NT == 1 ? 2 : 1;
-  const QWeight& w = *l.w;
-  const int col_stride = (p.m_pad + 31) & ~31;
-  const int acc_cols = NT * col_stride;
+// Ring depths and shared memory of one launch geometry; ok == false when it does not fit tensor or shared memory.
+struct TaPlan { bool ok; int sa, sb, rs; uint32_t tmem_cols; size_t smem; };
+static TaPlan plan_ta(int nt, int m_pad, uint32_t raw_stride) {
+  TaPlan t{};
+  const int kc = nt == 1 ? 2 : 1;
+  const int col_stride = (m_pad + 31) & ~31;
+  const int acc_cols = nt * col_stride;
   int sa = (512 - acc_cols) / 64;            // two units of 32 columns per stage
   if (sa > 4) sa = 4;
-  if (sa < 2 || p.m_pad > 256 || p.kb_per_split % KC) return cudaErrorNotSupported;
+  if (sa < 2 || m_pad > 256) return t;
   uint32_t cols = 32;
   while ((int)cols < acc_cols + sa * 64) cols <<= 1;
-  p.tmem_cols = cols;
   const size_t budget = (size_t)212 * 1024;
-  const size_t b_stage = (size_t)KC * p.m_pad * 128;
-  const size_t rstage = (size_t)2 * p.raw_stride;
-  int sb = (int)std::min<size_t>(4, (budget - 6 * rstage) / b_stage);
-  if (sb < 2) return cudaErrorNotSupported;
+  const size_t b_stage = (size_t)kc * m_pad * 128;
+  const size_t rstage = (size_t)2 * raw_stride;
+  if (budget < 6 * rstage + 2 * b_stage) return t;
+  const int sb = (int)std::min<size_t>(4, (budget - 6 * rstage) / b_stage);
   int rs = (int)std::min<size_t>(24, (budget - (size_t)sb * b_stage) / rstage);
-  if (rs < 3) return cudaErrorNotSupported;
+  if (sb < 2 || rs < 3) return t;
   // the epilogue's per-warp transpose buffers reuse the ring memory from its start
   while ((size_t)sb * b_stage + (size_t)rs * rstage < (size_t)QL_DQ_WARPS * QL_EPI_STAGE_BYTES) ++rs;
-  p.a_stages = sa; p.b_stages = sb; p.r_stages = rs;
   const size_t smem = 1024 + (size_t)sb * b_stage + (size_t)rs * rstage + (2 * rs + 2 * sb + 2 * sa + 1) * 8 + 16;
-  if (smem > 227 * 1024) return cudaErrorNotSupported;
+  if (smem > 227 * 1024) return t;
+  t.ok = true; t.sa = sa; t.sb = sb; t.rs = rs; t.tmem_cols = cols; t.smem = smem;
+  return t;
+}
+
+template <int BITS, int GPK, int NT>
+static cudaError_t launch_umma_ta(const QLinearLaunch& l, QlKernelParams& p, cudaStream_t s) {
+  const QWeight& w = *l.w;
+  const TaPlan t = plan_ta(NT, p.m_pad, p.raw_stride);
+  if (!t.ok) return cudaErrorInvalidValue;   // the caller sized the row chunk with plan_ta
+  p.tmem_cols = t.tmem_cols;
+  p.a_stages = t.sa; p.b_stages = t.sb; p.r_stages = t.rs;
   static DeviceOnce configured;   // the attribute belongs to the device's copy of the kernel
   if (configured.first_on_current_device()) {
     cudaError_t e = cudaFuncSetAttribute(qlinear_umma_ta_kernel<BITS, GPK, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
@@ -948,66 +684,64 @@ static cudaError_t launch_umma_ta(const QLinearLaunch& l, QlKernelParams& p, cud
   if (!rows) return cudaErrorInvalidValue;
   p.b_single = 1;
   dim3 grid((w.n_tiles + NT - 1) / NT, w.splits);
-  return launch_k(qlinear_umma_ta_kernel<BITS, GPK, NT>, grid, dim3(QL_THREADS), smem, s, *rows, p);
-}
-
-// Two A/B stages and three raw stages of the given geometry within the shared-memory budget?
-static bool ql_fits(int nt, int kc, int m_pad, uint32_t raw_stride) {
-  const size_t ab = (size_t)kc * ((size_t)nt * QL_A_BYTES + (size_t)m_pad * 128);
-  const size_t rstage = (size_t)kc * nt * raw_stride;
-  return 2 * ab + 3 * rstage <= (size_t)212 * 1024;
+  return launch_k(qlinear_umma_ta_kernel<BITS, GPK, NT>, grid, dim3(QL_THREADS), t.smem, s, *rows, p);
 }
 
 template <int BITS, int GPK>
 static cudaError_t launch_umma_nt(const QLinearLaunch& l, QlKernelParams& p, int nt, cudaStream_t s) {
-  // first choice: the kernel with its A ring in tensor memory (two tiles per CTA up to 192 rows, else one tile with two
-  // k-blocks per stage up to 256 rows); its launcher declines geometries that do not fit
-  if (nt >= 2 && p.m_pad <= 192) {
-    const cudaError_t e = launch_umma_ta<BITS, GPK, 2>(l, p, s);
-    if (e != cudaErrorNotSupported) return e;
-  } else if (nt == 1 && p.m_pad <= 256) {
-    const cudaError_t e = launch_umma_ta<BITS, GPK, 1>(l, p, s);
-    if (e != cudaErrorNotSupported) return e;
-  }
-  switch (nt) {   // the caller has lowered nt until its stages fit shared memory (wide 8-bit records, many rows)
-    case 4: return launch_umma<BITS, GPK, 4, 1>(l, p, s);
-    case 2: return launch_umma<BITS, GPK, 2, 1>(l, p, s);
-    default: break;
-  }
-  // one tile per CTA: two k-blocks per stage when the split holds an even number of them and two such stages fit
-  if (p.kb_per_split % 2 == 0 && p.kb_per_split >= 4 && ql_fits(1, 2, p.m_pad, p.raw_stride))
-    return launch_umma<BITS, GPK, 1, 2>(l, p, s);
-  return launch_umma<BITS, GPK, 1, 1>(l, p, s);
+  return nt == 2 ? launch_umma_ta<BITS, GPK, 2>(l, p, s) : launch_umma_ta<BITS, GPK, 1>(l, p, s);
 }
 
-// Weight tiles per CTA: as many as TMEM holds for this row count, but never so many that the grid drops
-// under about 0.7 CTAs per SM (measured: 112 CTAs of two tiles beat 224 CTAs of one on 148 SMs).
-static int plan_tiles_per_cta(const QWeight& w, int m_pad, int sm_count) {
-  int nt = m_pad <= 128 ? 4 : (m_pad <= 256 ? 2 : 1);
-  while (nt > 1 && ((w.n_tiles + nt - 1) / nt) * w.splits * 10 < sm_count * 7) nt >>= 1;
-  return nt;
+// Weight tiles per CTA: two when the grid then still has about 0.7 CTAs per SM (measured: 112 CTAs of two tiles beat
+// 224 CTAs of one on 148 SMs — the activation k-block is read from L2 once per CTA), else one.
+static int plan_tiles_per_cta(const QWeight& w, int sm_count) {
+  return ((w.n_tiles + 1) / 2) * w.splits * 10 >= sm_count * 7 ? 2 : 1;
+}
+
+// The most rows one launch of this weight takes: what the accumulators (two tiles: 192 columns each, one tile: 256)
+// and the rings of the weight's record size leave room for.
+static int plan_row_cap(int nt, uint32_t raw_stride) {
+  static const int caps[] = {256, 192, 128, 64, 32, 16};
+  for (int c : caps)
+    if (plan_ta(nt, c, raw_stride).ok) return c;
+  return 0;
 }
 
 cudaError_t qlinear_umma(const QLinearLaunch& l, cudaStream_t s) {
   const QWeight& w = *l.w;
   if (l.M < 1 || l.M > QL_MAX_M) return cudaErrorInvalidValue;
-  QlKernelParams p;
-  p.records = w.records; p.record_bytes = w.record_bytes;
-  p.N = w.N; p.n_tiles = w.n_tiles; p.kblocks = w.kblocks;
-  p.M = l.M; p.m_pad = (l.M + 15) & ~15; p.row0 = l.row0;
-  if (l.row0 % 16 || l.row0 + p.m_pad > l.x->rows) return cudaErrorInvalidValue;
-  p.splits = w.splits; p.kb_per_split = w.kblocks / w.splits;
-  p.raw_stride = w.record_bytes;
-  p.y = l.y; p.ldy = l.ldy; p.partial = l.partial; p.status = l.status;
-  int nt = plan_tiles_per_cta(w, p.m_pad, w.sm_count);
-  while (nt > 1 && !ql_fits(nt, 1, p.m_pad, p.raw_stride)) nt >>= 1;
+  if (l.row0 % 16 || l.row0 + ((l.M + 15) & ~15) > l.x->rows) return cudaErrorInvalidValue;
+  const int nt = plan_tiles_per_cta(w, w.sm_count);
+  const int cap = plan_row_cap(nt, w.record_bytes);
+  if (cap == 0) return cudaErrorInvalidValue;
   // the gated activation is fused when a CTA owns whole (gate, up) tile pairs and writes final values
-  const bool glu = l.glu && nt >= 2 && w.splits == 1 && (w.n_tiles & 1) == 0 && (w.N % (2 * QL_TILE_N)) == 0 && l.act &&
+  const bool glu = l.glu && nt == 2 && w.splits == 1 && (w.n_tiles & 1) == 0 && (w.N % (2 * QL_TILE_N)) == 0 && l.act &&
                    (l.ld_act & 3) == 0 && (reinterpret_cast<uintptr_t>(l.act) & 7) == 0;
-  p.glu = glu ? l.glu : 0; p.act = l.act; p.ld_act = l.ld_act;
   if (l.glu_done) *l.glu_done = glu ? 1 : 0;
-  if (w.bits == 4) return w.gpk == 2 ? launch_umma_nt<4, 2>(l, p, nt, s) : launch_umma_nt<4, 1>(l, p, nt, s);
-  return w.gpk == 2 ? launch_umma_nt<8, 2>(l, p, nt, s) : launch_umma_nt<8, 1>(l, p, nt, s);
+  // equal row chunks (multiples of 16 rows): fewer accumulator columns per chunk leave more A stages
+  const int chunks = (l.M + cap - 1) / cap;
+  const int per = (((l.M + chunks - 1) / chunks) + 15) & ~15;
+  for (int r0 = 0; r0 < l.M; r0 += per) {
+    QlKernelParams p;
+    p.records = w.records; p.record_bytes = w.record_bytes;
+    p.N = w.N; p.n_tiles = w.n_tiles; p.kblocks = w.kblocks;
+    p.M = std::min(per, l.M - r0); p.m_pad = (p.M + 15) & ~15; p.row0 = l.row0 + r0;
+    p.splits = w.splits; p.kb_per_split = w.kblocks / w.splits;
+    p.raw_stride = w.record_bytes;
+    p.y = l.y; p.ldy = l.ldy; p.partial = l.partial; p.part_M = l.M; p.part_row0 = r0; p.status = l.status;
+    p.glu = glu ? l.glu : 0; p.act = l.act; p.ld_act = l.ld_act;
+    cudaError_t e;
+    if (w.bits == 4) e = w.gpk == 2 ? launch_umma_nt<4, 2>(l, p, nt, s) : launch_umma_nt<4, 1>(l, p, nt, s);
+    else e = w.gpk == 2 ? launch_umma_nt<8, 2>(l, p, nt, s) : launch_umma_nt<8, 1>(l, p, nt, s);
+    if (e != cudaSuccess) return e;
+  }
+  return cudaSuccess;
+}
+
+int qlinear_launches(const QWeight& w, int M) {
+  const int nt = plan_tiles_per_cta(w, w.sm_count);
+  const int cap = plan_row_cap(nt, w.record_bytes);
+  return cap ? (M + cap - 1) / cap : 0;
 }
 
 // ---------------------------------------------------------------------------

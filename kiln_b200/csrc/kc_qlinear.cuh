@@ -28,7 +28,7 @@ namespace kc {
 
 constexpr int QL_TILE_N = 128;  // output features per tile = UMMA M
 constexpr int QL_KB = 64;       // input features per k-block = one 128-byte swizzle row of bf16
-constexpr int QL_MAX_M = 512;   // activation rows per launch (TMEM columns)
+constexpr int QL_MAX_M = 512;   // activation rows per qlinear_umma call (one slab of the split-K workspace)
 constexpr int QL_TILE_GROUP = 4;  // tiles whose records are interleaved per k-block (the most one CTA owns)
 
 struct QWeight {
@@ -89,8 +89,11 @@ void qweight_free(QWeight* w);
 // *err) if the driver entry point is unavailable or rejects the geometry.
 bool act_operand_init(ActOperand* op, const bf16* ptr, int rows, int K, const char** err);
 
-// The GEMM (tcgen05 + TMEM + TMA). Returns a CUDA error.
+// The GEMM (tcgen05 + TMEM + TMA). Returns a CUDA error. A launch of more rows than the accumulators hold (192 with
+// two weight tiles per CTA, 256 with one) is issued as several kernels over equal row chunks.
 cudaError_t qlinear_umma(const QLinearLaunch& l, cudaStream_t s);
+// Kernels qlinear_umma issues for M rows of this weight.
+int qlinear_launches(const QWeight& w, int M);
 
 // out[m, n] = bf16(sum over splits of partial[s][m][n]) in split order.
 cudaError_t qlinear_reduce_splits(const float* partial, int splits, int M, int N, bf16* y, int ldy,
