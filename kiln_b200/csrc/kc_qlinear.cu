@@ -79,14 +79,12 @@ __global__ void qweight_retile_kernel(uint8_t* __restrict__ records, const uint3
 }
 
 int qlinear_plan_splits(int n_tiles, int kblocks, int sm_count) {
+  // As many k-splits as fill the SMs with one-tile CTAs, each keeping at least 8 k-blocks; none when two-tile CTAs
+  // already fill them. Splits need not divide the k-blocks evenly (the kernel cuts [K s / S, K (s + 1) / S)).
   if (n_tiles * 2 >= sm_count) return 1;
-  static const int cand[] = {16, 12, 8, 6, 4, 3, 2};
-  for (int s : cand) {
-    if (kblocks % s) continue;
-    if (kblocks / s < 8) continue;
-    if (n_tiles * s <= sm_count) return s;
-  }
-  return 1;
+  int s = sm_count / n_tiles;
+  s = std::min(s, std::min(16, kblocks / 8));
+  return std::max(s, 1);
 }
 
 cudaError_t qweight_build(QWeight* out, const uint32_t* w, const bf16* scales, const bf16* biases,
@@ -298,7 +296,7 @@ struct QlKernelParams {
   int N, n_tiles, kblocks;
   int M, m_pad;          // live rows, rows rounded up to 16
   int row0;              // first activation row
-  int splits, kb_per_split;
+  int splits;
   int a_stages, r_stages, b_stages;   // b_stages: activation ring of the kernel that keeps its A ring in TMEM
   uint32_t raw_stride;   // distance between the records of neighbouring tiles in a raw stage (= record_bytes)
   int b_single;          // 1: the first tensor map's box spans all m_pad rows (one TMA operation per k-block)
@@ -470,9 +468,11 @@ qlinear_umma_ta_kernel(const __grid_constant__ CUtensorMap map_rows, const QlKer
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile0 = blockIdx.x * NT, split = blockIdx.y;
   const int nt_live = min(NT, p.n_tiles - tile0);
-  const int kb0 = split * p.kb_per_split;
-  const int nst = (p.kb_per_split + KC - 1) / KC;       // pipeline stages of this CTA
-  const int tail_kc = p.kb_per_split - (nst - 1) * KC;  // k-blocks of the last stage (1 or KC)
+  // splits may be uneven: split s takes k-blocks [K s / S, K (s + 1) / S) — a fixed function of the weight's shape
+  const int kb0 = (int)((long long)p.kblocks * split / p.splits);
+  const int nkb = (int)((long long)p.kblocks * (split + 1) / p.splits) - kb0;
+  const int nst = (nkb + KC - 1) / KC;                  // pipeline stages of this CTA
+  const int tail_kc = nkb - (nst - 1) * KC;             // k-blocks of the last stage (1 or KC)
   const int n_issuers = (NT == 2 && nt_live == 2) ? 2 : 1;
   const uint32_t col_stride = (uint32_t)(p.m_pad + 31) & ~31u;
   const uint32_t a_col0 = NT * col_stride;              // first column of the A ring
@@ -726,7 +726,7 @@ cudaError_t qlinear_umma(const QLinearLaunch& l, cudaStream_t s) {
     p.records = w.records; p.record_bytes = w.record_bytes;
     p.N = w.N; p.n_tiles = w.n_tiles; p.kblocks = w.kblocks;
     p.M = std::min(per, l.M - r0); p.m_pad = (p.M + 15) & ~15; p.row0 = l.row0 + r0;
-    p.splits = w.splits; p.kb_per_split = w.kblocks / w.splits;
+    p.splits = w.splits;
     p.raw_stride = w.record_bytes;
     p.y = l.y; p.ldy = l.ldy; p.partial = l.partial; p.part_M = l.M; p.part_row0 = r0; p.status = l.status;
     p.glu = glu ? l.glu : 0; p.act = l.act; p.ld_act = l.ld_act;
