@@ -40,7 +40,9 @@ if str(ROOT) not in sys.path:
 WORKLOADS = {
     # name: (preset, batch, k, prompt_lo, prompt_hi, generated)
     "llama-3.1-8b-w4g64-verify-k5-bs32": ("llama-3.1-8b", 32, 5, 512, 2048, 256),
-    "llama-3.2-1b-w4g64-verify-k4-bs1": ("llama-3.2-1b", 1, 4, 128, 128, 64),
+    # the reference's own CPU-runnable case: 1B target + its first 4 layers as the draft model (own weights, own pool),
+    # batch 1, k = 4: speculation runs through the real draft lane (kc_draft_chain), not the scripted drafter
+    "llama-3.2-1b-w4g64-verify-k4-bs1": ("llama-3.2-1b", 1, 4, 128, 128, 64, {"draft_layers": 4}),
     # parity-sized cases (speculation on == off at full size), not headline numbers: 64 requests that share a
     # 1024-token prefix (radix cache + copy-on-write) with 256-token unique suffixes; Gemma-2 with 6144-token prompts
     # (sliding window 4096 on even layers, attention and final-logit softcaps)
@@ -486,6 +488,117 @@ def tp_record(rank: int, local_rank: int, world: int, dist, barrier) -> dict:
     return rec
 
 
+def draft_lane_line(args, metric, config, warmup):
+    """The 1B configuration with the REAL draft model: the target's first `draft_layers` layers with their own pool
+    (crates/kiln-models/src/draft.rs:128-162), proposing k tokens per round through kc_draft_chain. One step = one engine
+    iteration = one propose (k chained draft decode forwards) + one (k + 1)-row verify forward + the settle walk.
+    Reports verified tok/s with speculation on, the speculation-off rate beside it, and the draft lane's time per
+    proposed token against its HBM floor (the draft's weight bytes at the measured copy bandwidth)."""
+    import torch
+    from kiln_b200 import api, host
+    from kiln_b200.synth import PRESETS, synth_checkpoint, truncated
+    preset, batch, k, lo, hi, gen = WORKLOADS[args.workload][:6]
+    extras = WORKLOADS[args.workload][6]
+    cfg = PRESETS[preset]
+    dcfg = truncated(cfg, extras["draft_layers"])
+    torch.cuda.set_device(0)
+    ctx = api.Context(0)
+    ck = synth_checkpoint(cfg, seed=0, device="cuda:0")
+    dck = {n: t for n, t in ck.items() if not n.startswith("model.layers.") or int(n.split(".")[2]) < dcfg.num_hidden_layers}
+    max_step = 256
+    model = api.CudaModel(ctx, cfg, ck, max_step_tokens=max_step, max_step_seqs=4)
+    dmodel = api.CudaModel(ctx, dcfg, dck, max_step_tokens=max_step, max_step_seqs=4)
+    del ck, dck
+    bs, nb = 16, 64 + (hi + gen + 64) // 16
+    kv = api.PagedKv(ctx, model.kv_spec(nb, bs))
+    dkv = api.PagedKv(ctx, dmodel.kv_spec(nb, bs))
+    ec = host.EngineConfig(block_size=bs, num_blocks=nb, max_batch_tokens=max_step, prefill_chunk=128, prefill_fine_chunk=128,
+                           prefix_cache=True, deterministic_decode_width=32, gamma=k, spec_max_batch=4, spec_min_acceptance=0.0,
+                           max_key_len=0, batch_verify=True)
+    eng = host.Engine(ec, host.StepModel.from_cuda(model, kv))
+    import numpy as np
+    rng = np.random.default_rng(1000)
+    prompt = rng.integers(0, cfg.vocab_size, size=lo, dtype=np.int64).tolist()
+
+    def run(n_requests, timed):
+        """Generates `gen` tokens n_requests times (each request re-hits the prefix cache); returns per-step records."""
+        recs, outs = [], []
+        for _ in range(n_requests):
+            a = eng.submit(prompt, gen)
+            toks, fk, first = [], None, True
+            while fk is None:
+                s0 = eng.spec_stats()
+                t0 = time.perf_counter()
+                eng.step()
+                t1 = time.perf_counter()
+                s1 = eng.spec_stats()
+                new, fk = eng.take_output(a)
+                toks += new
+                if timed and not first and new:   # the first iteration of a request is its (cached) prefill
+                    recs.append({"wall_ms": (t1 - t0) * 1e3, "dev_ms": ctx.last_step_ms(), "tokens": len(new),
+                                 "proposed": s1["proposed_total"] - s0["proposed_total"], "accepted": s1["accepted_total"] - s0["accepted_total"]})
+                first = False
+            outs.append(toks)
+        return recs, outs
+
+    _, base = run(1, False)                       # speculation off: the greedy continuation, and fills the prefix cache
+    off_recs, off_outs = run(2 + warmup // 8, True)
+    draft = host.DraftModel(dmodel, dkv, nb, bs)
+    eng.set_drafter(draft)
+    run(1, False)                                  # warm-up with the drafter attached
+    ctx.draft_stats(reset=True)
+    sampler = ClockSampler(0)
+    sampler.start()
+    n_req = max(1, -(-args.steps * 3 // gen))      # about `steps` rounds at ~3 tokens per round
+    torch.cuda.profiler.start()                     # lets `ncu --profile-from-start off` list the timed region only
+    recs, outs = run(n_req, True)
+    torch.cuda.profiler.stop()
+    clocks = sampler.stop()
+    d_ms, d_tok, d_calls = ctx.draft_stats()
+    identical = all(o == base[0] for o in outs + off_outs)
+    status = status_word(ctx)
+    pk = peaks()
+    tokens = sum(r["tokens"] for r in recs)
+    wall = sum(r["wall_ms"] for r in recs)
+    dev = sum(r["dev_ms"] for r in recs)            # device span of the verify forwards only
+    off_tokens, off_wall = sum(r["tokens"] for r in off_recs), sum(r["wall_ms"] for r in off_recs)
+
+    def qb(o, i, c):
+        return o * i * c.bits / 8 + 2 * o * (i // c.group_size) * 2
+    def weight_bytes(c):
+        per = qb(c.num_attention_heads * c.head_dim, c.hidden_size, c) + 2 * qb(c.num_key_value_heads * c.head_dim, c.hidden_size, c) + \
+            qb(c.hidden_size, c.num_attention_heads * c.head_dim, c) + 2 * qb(c.intermediate_size, c.hidden_size, c) + qb(c.hidden_size, c.intermediate_size, c)
+        return c.num_hidden_layers * per + qb(c.vocab_size, c.hidden_size, c)
+    floor_us = weight_bytes(dcfg) / (pk["hbm_gbs"] * 1e9) * 1e6
+    draft_us = d_ms * 1e3 / max(d_tok, 1)
+    verify_ms = sorted(r["dev_ms"] for r in recs)[len(recs) // 2]
+    verify_floor_ms = weight_bytes(cfg) / (pk["hbm_gbs"] * 1e9) * 1e3
+    line = {
+        "metric": metric, "value": tokens / (wall * 1e-3), "unit": "tok/s", "n_gpus": 1, "steps": len(recs), "warmup": warmup,
+        "ms_per_step": wall / len(recs), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "config": dict(config, draft=f"real draft model: first {dcfg.num_hidden_layers} layers of the target, own pool, kc_draft_chain"),
+        "clocks": clocks, "device_status": status,
+        "note": "batch 1: a step is latency-bound, so value is the end-to-end rate (wall clock of Engine::step: draft chain + verify + host)",
+        "e2e": {"value": tokens / (wall * 1e-3), "unit": "tok/s", "ms_per_step": wall / len(recs),
+                "h2d_bytes_per_step": int((k + 1) * 16 + (hi / 16 + 8) * 4 + k * 64), "d2h_bytes_per_step": int((k + 1) * 4 + 8 + k * 4)},
+        "speculation_off": {"tok_s": off_tokens / (off_wall * 1e-3), "ms_per_step": off_wall / max(len(off_recs), 1)},
+        "speedup_on_over_off": (tokens / wall) / (off_tokens / off_wall),
+        "draft_lane": {"us_per_proposed_token": draft_us, "hbm_floor_us": floor_us, "frac_of_hbm_floor": floor_us / draft_us,
+                       "proposed_tokens": d_tok, "chains": d_calls,
+                       "draft_weight_bytes": weight_bytes(dcfg), "peak_source": pk["source"]},
+        "verify_forward": {"p50_device_ms": verify_ms, "hbm_floor_ms": verify_floor_ms, "frac_of_hbm_floor": verify_floor_ms / verify_ms,
+                           "rows": k + 1, "target_weight_bytes": weight_bytes(cfg)},
+        "acceptance": {"proposed": sum(r["proposed"] for r in recs), "accepted": sum(r["accepted"] for r in recs),
+                       "tokens_per_step": tokens / len(recs)},
+        "spec_on_equals_off": {"sequences_checked": len(outs) + len(off_outs), "identical": bool(identical)},
+        "gpu_launches": int(ctx.launch_count()),
+    }
+    print(json.dumps(line))
+    eng = None
+    draft = None
+    model.close(); dmodel.close(); kv.close(); dkv.close(); ctx.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -528,6 +641,11 @@ def main():
                          f"One step = one sequence's verify forward; tokens per step = expected commit {commit:.3f} at p = 0.7. "
                          "It does not grow with --gpus: it is a host-cores baseline.")}
         print(json.dumps(line))
+        return
+
+    if len(WORKLOADS[args.workload]) > 6 and WORKLOADS[args.workload][6].get("draft_layers") and not args.check_only:
+        if rank == 0:
+            draft_lane_line(args, metric, config, warmup)
         return
 
     import torch

@@ -272,6 +272,12 @@ KC_API int kc_draft_chain(kc_model_t model, kc_kv_t kv, uint32_t first_token, in
                           const uint32_t* blocks, int32_t n_blocks, int32_t gamma,
                           uint32_t* proposal_out);
 
+/* Accounting of the draft lane on this context: wall-clock milliseconds spent inside kc_draft_chain (launches,
+ * the device work and the read-back of the proposal), tokens proposed and calls, since the context was created or
+ * the last reset. The reference's counterpart is the per-request spec_tokens_proposed counter plus its perf lane
+ * (crates/kiln-models/tests/spec_throughput.rs:106-147). */
+KC_API int kc_draft_stats(kc_ctx_t ctx, double* ms_out, int64_t* tokens_out, int64_t* calls_out, int32_t reset);
+
 /* ---- single ops, exported for parity tests and for callers composing their
  *      own graphs (the kiln_mlx::ops / fast call sites of nn.rs) ------------ */
 

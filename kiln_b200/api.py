@@ -231,6 +231,12 @@ class Context:
         check(L.lib().kc_device_status(self._h, C.byref(st)))
         return st.value
 
+    def draft_stats(self, reset: bool = False):
+        """(milliseconds inside kc_draft_chain, tokens proposed, calls) since creation or the last reset."""
+        ms, tok, calls = C.c_double(0), C.c_int64(0), C.c_int64(0)
+        check(L.lib().kc_draft_stats(self._h, C.byref(ms), C.byref(tok), C.byref(calls), int(reset)))
+        return float(ms.value), int(tok.value), int(calls.value)
+
     def launch_count(self) -> int:
         return int(L.lib().kc_launch_count(self._h))
 

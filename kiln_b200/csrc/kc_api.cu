@@ -11,6 +11,7 @@
 
 #include <algorithm>
 #include <atomic>
+#include <chrono>
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
@@ -86,6 +87,9 @@ struct kc_ctx {
   std::vector<Span> spans;
   std::vector<cudaEvent_t> event_pool;
   int64_t class_launches[KC_PROFILE_CLASSES] = {0, 0, 0, 0, 0};
+  // draft lane accounting (kc_draft_chain): host wall time of the calls and tokens proposed
+  double draft_ms = 0.0;
+  int64_t draft_tokens = 0, draft_calls = 0;
   cudaEvent_t take_event() {
     if (!event_pool.empty()) { cudaEvent_t e = event_pool.back(); event_pool.pop_back(); return e; }
     cudaEvent_t e = nullptr;
@@ -294,6 +298,15 @@ extern "C" int kc_profile_read(kc_ctx_t c, double* ms_out, int64_t* launches_out
     c->event_pool.push_back(sp.b);
   }
   c->spans.clear();
+  return KC_OK;
+}
+
+extern "C" int kc_draft_stats(kc_ctx_t c, double* ms_out, int64_t* tokens_out, int64_t* calls_out, int32_t reset) {
+  if (!c) return fail(KC_ERR_INVALID, "kc_draft_stats: NULL");
+  if (ms_out) *ms_out = c->draft_ms;
+  if (tokens_out) *tokens_out = c->draft_tokens;
+  if (calls_out) *calls_out = c->draft_calls;
+  if (reset) { c->draft_ms = 0.0; c->draft_tokens = 0; c->draft_calls = 0; }
   return KC_OK;
 }
 
@@ -1185,6 +1198,7 @@ extern "C" int kc_draft_chain(kc_model_t m, kc_kv_t kv, uint32_t first_token, in
   if (gamma < 1 || gamma > 64) return fail(KC_ERR_INVALID, "kc_draft_chain: gamma %d", gamma);
   kc_ctx* c = m->ctx;
   CK(cudaSetDevice(c->device));
+  const auto t_begin = std::chrono::steady_clock::now();
   // Step j feeds one token at position offset + j; its input is the previous step's raw argmax,
   // read on the device (row_tokens[j-1]) — the lazy feed of draft.rs:382-386.
   for (int j = 0; j < gamma; ++j) {
@@ -1203,6 +1217,8 @@ extern "C" int kc_draft_chain(kc_model_t m, kc_kv_t kv, uint32_t first_token, in
   CK(cudaStreamSynchronize(c->stream));
   RC(status_verdict(c, "kc_draft_chain"));
   memcpy(proposal_out, m->result_host, (size_t)gamma * 4);
+  c->draft_ms += std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t_begin).count();
+  c->draft_tokens += gamma; c->draft_calls += 1;
   return KC_OK;
 }
 

@@ -193,7 +193,10 @@ def test_draft_chain_matches_stepwise_decode(ctx):
     p = prompts(cfg, [30], 4)[0]
     blocks = [7, 2, 9]
     model.verify_step(api.StepBatch(p[:-1], [api.SeqStep(29, 0, 0, blocks)]), kv)
+    ctx.draft_stats(reset=True)
     chain = model.draft_chain(kv, p[-1], 29, blocks, 5)
+    ms, tokens, calls = ctx.draft_stats()
+    assert (tokens, calls) == (5, 1) and ms > 0
     kv2 = api.PagedKv(ctx, model.kv_spec(64, BS))
     model.verify_step(api.StepBatch(p[:-1], [api.SeqStep(29, 0, 0, blocks)]), kv2)
     tok, step = p[-1], []
