@@ -27,6 +27,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import statistics
 import subprocess
 import sys
 import threading
@@ -253,10 +254,48 @@ class Workload:
         self.ctx.close()
 
     def run_off(self):
-        """Phase 1: speculation off, to completion. Returns the greedy continuation of every prompt."""
-        arrivals = [self.engine.submit(p, self.gen) for p in self.prompts]
-        out = self.engine.run_to_completion(arrivals)
-        return [out[a][0] for a in arrivals]
+        """Phase 1: speculation off, to completion. Returns the greedy continuation of every prompt. Plain decode is
+        the path every request takes when speculation stands down (engine.rs:1428-1475); the first half of the
+        generation runs it pipelined (step N + 1 launched from step N's unread tokens), the second half synchronously,
+        and `plain_decode` keeps the time per full-batch decode step of each (end of one engine step to the end of the
+        next, host work included)."""
+        eng = self.engine
+        arrivals = [eng.submit(p, self.gen) for p in self.prompts]
+        out = {a: [] for a in arrivals}
+        done = set()
+        spans = {True: [], False: []}
+        pipelined, last_end = True, None
+        eng.set_pipelined(True)
+        for _ in range(1000000):
+            if len(done) == len(arrivals):
+                break
+            eng.step()
+            now = time.perf_counter()
+            emitted = 0
+            for a in arrivals:
+                if a in done:
+                    continue
+                toks, kind = eng.take_output(a)
+                out[a] += toks
+                emitted += len(toks)
+                if kind is not None:
+                    done.add(a)
+            if last_end is not None and emitted == len(arrivals) and not done:
+                spans[pipelined].append((now - last_end) * 1e3)
+            last_end = time.perf_counter()
+            if pipelined and len(out[arrivals[0]]) >= self.gen // 2:
+                pipelined = False
+                eng.set_pipelined(False)
+                last_end = None
+        eng.set_pipelined(True)
+        med = lambda v: float(statistics.median(v[2:])) if len(v) > 4 else None
+        p_ms, s_ms = med(spans[True]), med(spans[False])
+        self.plain_decode = {"pipelined_ms_per_step": p_ms, "synchronous_ms_per_step": s_ms,
+                             "steps_timed": [max(0, len(spans[True]) - 2), max(0, len(spans[False]) - 2)],
+                             "pipelined_tok_s": len(arrivals) / (p_ms * 1e-3) if p_ms else None,
+                             "synchronous_tok_s": len(arrivals) / (s_ms * 1e-3) if s_ms else None,
+                             "rows_per_step": len(arrivals)}
+        return [out[a] for a in arrivals]
 
     def submit_on(self, base, p_accept=0.7, seed=0):
         """Phase 2 submission: scripted drafter with injected acceptance; every prompt is a prefix-cache hit."""
@@ -767,6 +806,7 @@ def main():
                        "tokens_per_step": tokens / steps / (1 if main_tp > 1 else world)},
         "spec_on_equals_off": {"sequences_checked": checked, "identical": bool(identical)},
         "setup_s": {"build_model": round(build_s, 1), "speculation_off_run": round(off_s, 1)},
+        "plain_decode": getattr(w, "plain_decode", None),
     }
     if per_rank:
         line["per_rank"] = per_rank

@@ -264,6 +264,19 @@ KC_API int kc_verify_step(kc_model_t model, kc_kv_t kv, const uint32_t* token_id
                           uint32_t* row_tokens_out, int32_t* n_committed_out,
                           int32_t* n_accepted_out);
 
+/* Pipelined plain decode (crates/kiln-engine/src/engine.rs:1428-1455 pipelined_turn, 1656-1744 build_pipelined,
+ * 1748-1766 apply_inflight). kc_decode_launch queues ONE decode forward — every segment feeds one row and samples it,
+ * greedy over normalised logits as in kc_verify_step — and returns at once with a ticket. feed[i] >= 0 takes
+ * sequence i's input id from row feed[i] of the PREVIOUS launch's sampled tokens, which are still on the device
+ * (StepInput::Lazy, step.rs:45-56); feed[i] < 0 takes token_ids[i]. kc_decode_collect blocks until the launch with
+ * that ticket has finished and copies its n tokens out (Array::item_u32 of the deferred rows); only the two most
+ * recent launches can be collected, and a launch that is never collected costs nothing. A bounded wait that gave up
+ * in that launch makes collect return KC_ERR_TIMEOUT. The caller must not reuse a block a launch writes to for
+ * another sequence except through later calls on the same context, which are ordered behind it on the stream. */
+KC_API int kc_decode_launch(kc_model_t model, kc_kv_t kv, const uint32_t* token_ids, const int32_t* feed,
+                            const kc_seq_step* seqs, int32_t n_seqs, uint64_t* ticket_out);
+KC_API int kc_decode_collect(kc_model_t model, uint64_t ticket, uint32_t* row_tokens_out, int32_t n);
+
 /* The draft lane of DraftModel::propose (draft.rs:354-388): `gamma` chained
  * single-token decode forwards for ONE sequence, each feeding the previous raw
  * argmax without a host round trip. blocks must already cover offset+gamma

@@ -116,6 +116,17 @@ typedef struct {
   int32_t vocab;
 } kh_step_model;
 
+/* The pipelined plain-decode seam (engine.rs:1428-1475, 1656-1766: pipelined_turn, build_pipelined, apply_inflight).
+ * launch queues one decode forward (one sampled row per sequence) without waiting and returns a ticket; feed[i] >= 0
+ * takes sequence i's input id from row feed[i] of the previous launch, still on the device (StepInput::Lazy,
+ * step.rs:45-56); feed[i] < 0 takes ids[i]. collect blocks until that launch's tokens are on the host. launch has
+ * the signature of kc_decode_launch, collect of kc_decode_collect; model and kv are those of the step model. */
+typedef struct {
+  int (*launch)(void* model, void* kv, const uint32_t* ids, const int32_t* feed, const kh_seq_step* seqs, int32_t n_seqs,
+                uint64_t* ticket);
+  int (*collect)(void* model, uint64_t ticket, uint32_t* row_tokens, int32_t n);
+} kh_decode_pipeline;
+
 /* trait Drafter (drafter.rs:125-147). A non-zero return from begin/propose is a DraftError: never fatal to the request. */
 typedef struct {
   void* user;
@@ -145,6 +156,10 @@ KH_API void kh_engine_default_config(kh_engine_config* out);   /* EngineConfig::
 KH_API int kh_engine_create(const kh_engine_config* cfg, const kh_step_model* model, kh_engine_t* out);
 KH_API void kh_engine_free(kh_engine_t e);
 KH_API int kh_engine_set_drafter(kh_engine_t e, const kh_drafter* d);
+/* Without this call the engine never pipelines (every step is read back before the next is built). p = NULL turns
+ * pipelining off again; a step already in flight is read back at the next kh_engine_step. */
+KH_API int kh_engine_set_pipeline(kh_engine_t e, const kh_decode_pipeline* p);
+KH_API uint64_t kh_engine_pipelined_steps(kh_engine_t e);    /* Engine::pipelined_steps (engine.rs:1160-1163) */
 /* Engine::submit (engine.rs:1294-1363); greedy requests only. */
 KH_API int kh_engine_submit(kh_engine_t e, const uint32_t* prompt, uint64_t n, uint64_t max_tokens, const uint32_t* stop_tokens,
                             uint64_t n_stop, uint64_t* arrival_out);

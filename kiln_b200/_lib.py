@@ -75,6 +75,9 @@ _SIGNATURES = {
     "kc_verify_accept": (C.c_int, [_P, _P, _P, _P, _P, _P, C.c_int32, C.c_int32, _P, _P, _P]),
     "kc_verify_step": (C.c_int, [_P, _P, C.POINTER(C.c_uint32), C.c_int32, C.POINTER(KcSeqStep), C.c_int32,
                                  C.POINTER(C.c_uint32), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
+    "kc_decode_launch": (C.c_int, [_P, _P, C.POINTER(C.c_uint32), C.POINTER(C.c_int32), C.POINTER(KcSeqStep), C.c_int32,
+                                   C.POINTER(C.c_uint64)]),
+    "kc_decode_collect": (C.c_int, [_P, C.c_uint64, C.POINTER(C.c_uint32), C.c_int32]),
     "kc_draft_stats": (C.c_int, [_P, C.POINTER(C.c_double), C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.c_int32]),
     "kc_draft_chain": (C.c_int, [_P, _P, C.c_uint32, C.c_int32, C.POINTER(C.c_uint32), C.c_int32, C.c_int32,
                                  C.POINTER(C.c_uint32)]),

@@ -397,6 +397,24 @@ class CudaModel:
                                      nacc.ctypes.data_as(C.POINTER(C.c_int32))))
         return rows[:n_sampled], ncom, nacc
 
+    def decode_launch(self, batch: StepBatch, kv: PagedKv, feed: Sequence[int]) -> int:
+        """Queues one pipelined decode step (engine.rs:1656-1744) and returns its ticket; feed[i] >= 0 takes sequence
+        i's input id from that row of the previous launch, still on the device."""
+        p = _PackedStep(batch)
+        f = np.ascontiguousarray(np.asarray(feed, dtype=np.int32))
+        if f.shape[0] != p.n_seqs:
+            raise ValueError("a decode step has one feed entry per sequence")
+        t = C.c_uint64(0)
+        check(L.lib().kc_decode_launch(self._h, kv._h, p.ids_p, f.ctypes.data_as(C.POINTER(C.c_int32)), p.seq_arr, p.n_seqs,
+                                       C.byref(t)))
+        return int(t.value)
+
+    def decode_collect(self, ticket: int, n: int) -> List[int]:
+        """Waits for the launch with that ticket and returns its n greedy tokens (engine.rs:1748-1766)."""
+        out = np.zeros(max(1, n), dtype=np.uint32)
+        check(L.lib().kc_decode_collect(self._h, int(ticket), out.ctypes.data_as(C.POINTER(C.c_uint32)), int(n)))
+        return [int(x) for x in out[:n]]
+
     def draft_chain(self, kv: PagedKv, first_token: int, offset: int, blocks: Sequence[int], gamma: int) -> List[int]:
         """gamma chained greedy decode forwards for one sequence (draft.rs:354-388)."""
         b = np.ascontiguousarray(np.asarray(blocks, dtype=np.uint32))

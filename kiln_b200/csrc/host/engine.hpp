@@ -5,7 +5,9 @@
 //                                      collect_proposal, maybe_stand_down}, build_seq_step,
 //                                      settle_sampled, finish, CacheState::donate,
 //                                      match_head_prefix (1294-1363, 1367-1407, 1508-1634,
-//                                      1802-2033, 2035-2417, 2736-2796, 601-778, 907-963)
+//                                      1802-2033, 2035-2417, 2736-2796, 601-778, 907-963),
+//                                      pipelined_turn, pipeline_ok, build_pipelined,
+//                                      apply_inflight (1428-1475, 1656-1766)
 //   crates/kiln-engine/src/drafter.rs  spec_gamma_at_width, trait Drafter (62-70, 125-147)
 //   crates/kiln-models/src/draft.rs    DraftModel::{begin, propose, release} (268-411)
 // The model and the drafter sit behind C function tables (the StepModel / Drafter
@@ -53,6 +55,16 @@ struct StepModelVT {
                      uint32_t* row_tokens, int32_t* n_committed, int32_t* n_accepted);
   int (*copy_block)(void* kv, uint32_t src, uint32_t dst);
   int32_t vocab;
+};
+
+// The pipelined-decode seam: launch queues one decode forward (one sampled row per sequence) without waiting for it and
+// returns a ticket; feed[i] >= 0 takes sequence i's input id from row feed[i] of the previous launch, still on the device
+// (StepInput::Lazy, step.rs:45-56), feed[i] < 0 takes ids[i]. collect blocks until that launch's tokens are on the host
+// (Array::item_u32 after async_eval). launch has the signature of kc_decode_launch, collect of kc_decode_collect.
+struct DecodePipelineVT {
+  int (*launch)(void* model, void* kv, const uint32_t* ids, const int32_t* feed, const SeqStepC* seqs, int32_t n_seqs,
+                uint64_t* ticket);
+  int (*collect)(void* model, uint64_t ticket, uint32_t* row_tokens, int32_t n);
 };
 
 // Drafter seam (drafter.rs:125-147). propose writes at most `gamma` ids; a non-zero return is a DraftError.
@@ -151,6 +163,9 @@ class Engine {
     if (cfg.prefix_cache) radix_.reset(new RadixCache(cfg.block_size, ChainHash{}));
   }
   void set_drafter(const DrafterVT& d) { drafter_ = d; has_drafter_ = true; }
+  void set_pipeline(const DecodePipelineVT& p) { pipe_ = p; has_pipe_ = true; }
+  void clear_pipeline() { has_pipe_ = false; }  // a step already in flight is still read back at the next turn
+  uint64_t pipelined_steps() const { return pipelined_total_; }  // engine.rs:1160-1163
   const SpecStats& spec_stats() const { return spec_; }
   BlockManager& block_manager() { return mgr_; }
   RadixCache* radix() { return radix_.get(); }
@@ -203,6 +218,14 @@ class Engine {
 
   // One iteration (engine.rs:1367-1407). 0 on success; on a model error every request is failed and the pools reset.
   int step() {
+    if (has_inflight_) {
+      InFlight prev = std::move(inflight_);
+      has_inflight_ = false;
+      bool still = false;
+      int rc = pipelined_turn(prev, &still);
+      if (rc != 0) { fail_all(err_); return rc; }
+      if (still) return 0;  // a new step is in flight (or its rows were all dropped): the turn is complete
+    }
     sweep_cancelled();
     admit();
     if (running_.empty()) return 0;
@@ -213,6 +236,14 @@ class Engine {
 
  private:
   typedef std::shared_ptr<Seq> SeqP;
+
+  // A decode step that has been queued on the device and not read back (engine.rs:790-793): per row the request it
+  // belongs to; the row index doubles as the feed index of the next launch.
+  struct InFlight {
+    uint64_t ticket = 0;
+    size_t width = 0;                                  // rows the launch sampled
+    std::vector<std::pair<uint64_t, int32_t>> rows;    // (arrival, row of the launch)
+  };
 
   struct DecodePlan {  // engine.rs:795-803
     size_t seq;
@@ -327,6 +358,110 @@ class Engine {
     seq.cached_tokens = std::max<uint32_t>(seq.cached_tokens, (uint32_t)served);
     cache_stats_.hits_total++;
     cache_stats_.tokens_reused_total += served;
+  }
+
+  int find_running(uint64_t arrival) const {
+    for (size_t i = 0; i < running_.size(); ++i) if (running_[i]->arrival == arrival) return (int)i;
+    return -1;
+  }
+
+  // engine.rs:1482-1500: would the next synchronous step run (or be able to run) a verify round?
+  bool spec_would_engage() const {
+    if (!has_drafter_ || cfg_.deterministic_decode_width <= 1) return false;
+    if (spec_gamma_at_width(cfg_.gamma, cfg_.spec_max_batch, running_.size()) == 0) return false;
+    for (auto& s : running_) {
+      const size_t remaining = s->max_tokens > s->generated ? s->max_tokens - s->generated : 0;
+      if (s->spec_eligible() && remaining >= 2 && (cfg_.max_key_len <= 0 || s->processed + s->fed + 2 <= (size_t)cfg_.max_key_len))
+        return true;
+    }
+    return false;
+  }
+
+  // engine.rs:1456-1475: the pipeline spans steady-state decode only. Penalties and grammars do not exist on this path.
+  // With the reference's forward grouping (batch_verify = 0) a step wider than the deterministic width is several
+  // forwards; that case stays on the synchronous path, which reproduces the grouping.
+  bool pipeline_ok() const {
+    if (!has_pipe_ || spec_would_engage() || !waiting_.empty()) return false;
+    if (!cfg_.batch_verify && running_.size() > (size_t)std::max(cfg_.deterministic_decode_width, 1)) return false;
+    for (auto& s : running_) if (!s->decoding() || s->cancel) return false;
+    return true;
+  }
+
+  // engine.rs:1434-1455.
+  int pipelined_turn(InFlight& prev, bool* still) {
+    InFlight next;
+    bool has_next = false;
+    if (pipeline_ok()) {
+      int rc = build_pipelined(prev, &next, &has_next);
+      if (rc != 0) return rc;
+    }
+    int rc = apply_inflight(prev);
+    if (rc != 0) return rc;
+    if (!has_next) { *still = false; return 0; }
+    // A sequence that stopped or was cancelled at the apply has one speculative row in flight: it is dropped unread.
+    // Its KV write went to blocks the sequence owned when the step was built; only settled rows are ever donated.
+    next.rows.erase(std::remove_if(next.rows.begin(), next.rows.end(),
+                                   [&](const std::pair<uint64_t, int32_t>& r) { return find_running(r.first) < 0; }),
+                    next.rows.end());
+    if (!next.rows.empty()) {
+      pipelined_total_++;
+      inflight_ = std::move(next);
+      has_inflight_ = true;
+    }
+    *still = true;
+    return 0;
+  }
+
+  // engine.rs:1656-1744: the next decode step, fed from prev's unread tokens.
+  int build_pipelined(const InFlight& prev, InFlight* out, bool* built) {
+    *built = false;
+    const size_t bs = mgr_.block_size();
+    std::vector<std::pair<size_t, int32_t>> included;  // (index into running_, row of prev)
+    size_t new_blocks = 0;
+    for (auto& r : prev.rows) {
+      const int i = find_running(r.first);
+      if (i < 0) return 0;
+      Seq& seq = *running_[i];
+      if ((size_t)seq.generated + 1 >= seq.max_tokens) continue;  // its final token is in prev
+      if (seq.table.num_tokens() == seq.table.blocks().size() * bs) new_blocks++;
+      included.push_back({(size_t)i, r.second});
+    }
+    if (included.empty() || mgr_.num_free() < new_blocks) return 0;  // preemption/eviction stay synchronous decisions
+    iterations_++;
+    std::vector<DecodePlan> plans(included.size());
+    std::vector<SeqStepC> seqs;
+    std::vector<uint32_t> ids(included.size(), 0);
+    std::vector<int32_t> feed;
+    for (size_t j = 0; j < included.size(); ++j) {
+      Seq& seq = *running_[included[j].first];
+      int rc = build_seq_step(seq, 1, &plans[j]);
+      if (rc < 0) return rc;
+      if (rc == 0) { err_ = "pipelined append exceeded the precounted pool"; return -1; }
+      feed.push_back(included[j].second);
+      out->rows.push_back({seq.arrival, (int32_t)j});
+    }
+    for (auto& p : plans) seqs.push_back(SeqStepC{1, (int32_t)p.offset, 1, (int32_t)p.blocks.size(), p.blocks.data()});
+    forwards_++;
+    int rc = pipe_.launch(model_.model, model_.kv, ids.data(), feed.data(), seqs.data(), (int32_t)seqs.size(), &out->ticket);
+    if (rc != 0) { err_ = "pipelined decode launch failed with status " + std::to_string(rc); return rc; }
+    out->width = included.size();
+    *built = true;
+    return 0;
+  }
+
+  // engine.rs:1748-1766: read a scheduled step back and settle it.
+  int apply_inflight(const InFlight& prev) {
+    std::vector<uint32_t> tokens(std::max<size_t>(prev.width, 1));
+    int rc = pipe_.collect(model_.model, prev.ticket, tokens.data(), (int32_t)prev.width);
+    if (rc != 0) { err_ = "pipelined decode collect failed with status " + std::to_string(rc); return rc; }
+    for (auto& r : prev.rows) {
+      const int i = find_running(r.first);
+      if (i < 0) continue;
+      settle_sampled(*running_[i], tokens[r.second]);
+    }
+    release_finished_drafts();
+    running_.erase(std::remove_if(running_.begin(), running_.end(), [](const SeqP& s) { return s->finished; }), running_.end());
+    return 0;
   }
 
   // engine.rs:1508-1596.
@@ -580,6 +715,34 @@ class Engine {
       break;
     }
 
+    // Pipeline entry (engine.rs:2272-2297): a steady-state pure-decode step defers its read-back; the next step is built
+    // from its still-unread tokens at the start of the next step() call, while the device executes this one.
+    {
+      bool all_plain = !has_prefill && plans.size() == running_.size() && !plans.empty();
+      for (auto& p : plans) all_plain = all_plain && p.sample && !p.has_draft;
+      if (all_plain && pipeline_ok()) {
+        std::vector<uint32_t> ids;
+        std::vector<int32_t> feed(plans.size(), -1);
+        std::vector<SeqStepC> seqs;
+        InFlight f;
+        for (size_t j = 0; j < plans.size(); ++j) {
+          Seq& seq = *running_[plans[j].seq];
+          ids.push_back(seq.history[seq.fed]);
+          seqs.push_back(SeqStepC{1, (int32_t)plans[j].offset, 1, (int32_t)plans[j].blocks.size(), plans[j].blocks.data()});
+          f.rows.push_back({seq.arrival, (int32_t)j});
+        }
+        forwards_++;
+        int rc = pipe_.launch(model_.model, model_.kv, ids.data(), feed.data(), seqs.data(), (int32_t)seqs.size(), &f.ticket);
+        if (rc != 0) { err_ = "pipelined decode launch failed with status " + std::to_string(rc); return rc; }
+        f.width = plans.size();
+        logits_vocab_known_ = true;
+        pipelined_total_++;
+        inflight_ = std::move(f);
+        has_inflight_ = true;
+        return 0;
+      }
+    }
+
     // FORWARD. Reference grouping: prefill first, then plain-decode groups of at most deterministic_decode_width rows,
     // then one forward per verify segment (engine.rs:2170-2271). Row-invariant backend: everything in one forward.
     std::vector<std::vector<uint32_t>> rows(plans.size());
@@ -671,6 +834,7 @@ class Engine {
     release_finished_drafts();
     running_.clear();
     waiting_.clear();
+    has_inflight_ = false;  // engine.rs:2521
     mgr_ = BlockManager(cfg_.num_blocks, cfg_.block_size);
     if (radix_) radix_->reset();
   }
@@ -679,6 +843,10 @@ class Engine {
   StepModelVT model_;
   DrafterVT drafter_{};
   bool has_drafter_ = false;
+  DecodePipelineVT pipe_{};
+  bool has_pipe_ = false, has_inflight_ = false;
+  InFlight inflight_;
+  uint64_t pipelined_total_ = 0;
   BlockManager mgr_;
   std::unique_ptr<RadixCache> radix_;
   std::deque<SeqP> waiting_;

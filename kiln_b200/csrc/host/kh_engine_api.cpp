@@ -61,6 +61,17 @@ int kh_engine_set_drafter(kh_engine_t e, const kh_drafter* d) {
   e->e->set_drafter(DrafterVT{d->user, d->begin, d->propose, d->release});
   return KH_OK;
 }
+int kh_engine_set_pipeline(kh_engine_t e, const kh_decode_pipeline* p) {
+  if (!e) return KH_ERR_ARG;
+  if (!p) { e->e->clear_pipeline(); return KH_OK; }
+  if (!p->launch || !p->collect) return KH_ERR_ARG;
+  DecodePipelineVT vt;
+  vt.launch = reinterpret_cast<decltype(vt.launch)>(p->launch);
+  vt.collect = p->collect;
+  e->e->set_pipeline(vt);
+  return KH_OK;
+}
+uint64_t kh_engine_pipelined_steps(kh_engine_t e) { return e->e->pipelined_steps(); }
 int kh_engine_submit(kh_engine_t e, const uint32_t* prompt, uint64_t n, uint64_t max_tokens, const uint32_t* stop_tokens,
                      uint64_t n_stop, uint64_t* arrival_out) {
   if (!e || (!prompt && n)) return KH_ERR_ARG;

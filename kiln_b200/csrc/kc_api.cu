@@ -151,7 +151,7 @@ struct Layer {
 
 // Per-step metadata, packed on the host and copied to the device in one transfer.
 struct MetaLayout {
-  size_t tokens, token_pos, kv_slot, sampled, tables, work, v_row_off, v_draft_off, v_draft_len, v_draft, total;
+  size_t tokens, token_pos, kv_slot, sampled, tables, work, v_row_off, v_draft_off, v_draft_len, v_draft, feed, total;
 };
 
 struct kc_model {
@@ -187,6 +187,12 @@ struct kc_model {
   // verify results
   uint32_t* row_tokens = nullptr; int32_t *n_committed = nullptr, *n_accepted = nullptr; uint32_t* committed = nullptr;
   uint8_t* result_host = nullptr;      // pinned
+  // pipelined decode: launch k keeps its sampled tokens in slot k % 2 until launch k + 2 reuses it
+  uint32_t* pipe_tokens[2] = {nullptr, nullptr};   // device [max_seqs]
+  uint32_t* pipe_host[2] = {nullptr, nullptr};     // pinned [max_seqs + 1]: tokens, then the device status word
+  cudaEvent_t pipe_ev[2] = {nullptr, nullptr};
+  int pipe_n[2] = {0, 0};
+  uint64_t pipe_ticket = 0;                        // of the most recent launch; 0 = none yet
 };
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -709,6 +715,11 @@ void free_model(kc_model* m) {
   }
   cudaFree(m->row_tokens); cudaFree(m->n_committed); cudaFree(m->n_accepted); cudaFree(m->committed);
   if (m->result_host) cudaFreeHost(m->result_host);
+  for (int i = 0; i < 2; ++i) {
+    cudaFree(m->pipe_tokens[i]);
+    if (m->pipe_host[i]) cudaFreeHost(m->pipe_host[i]);
+    if (m->pipe_ev[i]) cudaEventDestroy(m->pipe_ev[i]);
+  }
   delete m;
 }
 
@@ -864,6 +875,11 @@ extern "C" int kc_model_load(kc_ctx_t c, const kc_model_desc* desc, const kc_ten
     if (e == cudaSuccess) e = cudaMalloc(&m->committed, R * 4);
     if (e == cudaSuccess) e = cudaMallocHost(&m->result_host, R * 4 + (size_t)m->max_seqs * 8 + 64);
     for (int i = 0; i < kc_model::kStaging && e == cudaSuccess; ++i) e = cudaEventCreateWithFlags(&m->meta_ev[i], cudaEventDisableTiming);
+    for (int i = 0; i < 2 && e == cudaSuccess; ++i) {
+      e = cudaMalloc(&m->pipe_tokens[i], (size_t)m->max_seqs * 4);
+      if (e == cudaSuccess) e = cudaMallocHost(&m->pipe_host[i], ((size_t)m->max_seqs + 1) * 4);
+      if (e == cudaSuccess) e = cudaEventCreateWithFlags(&m->pipe_ev[i], cudaEventDisableTiming);
+    }
     if (e != cudaSuccess) LOAD_FAIL(fail(KC_ERR_OOM, "kc_model_load: result buffers: %s", cudaGetErrorString(e)));
   }
   CK(cudaStreamSynchronize(c->stream));
@@ -955,6 +971,7 @@ int validate_step(kc_model* m, kc_kv* kv, const uint32_t* token_ids, int32_t n, 
   L.work = put((size_t)p.n_work * 16);
   L.v_row_off = put((size_t)n_seqs * 4); L.v_draft_off = put((size_t)n_seqs * 4); L.v_draft_len = put((size_t)n_seqs * 4);
   L.v_draft = put((size_t)n * 4);
+  L.feed = put((size_t)n * 4);
   L.total = at;
   *plan = p;
   return KC_OK;
@@ -964,7 +981,7 @@ int validate_step(kc_model* m, kc_kv* kv, const uint32_t* token_ids, int32_t n, 
 // `before_copy` (optional) is recorded on the stream after the host-side packing and before the copy is queued: the
 // device span of a step starts there, so host packing time is not counted as device time.
 int upload_meta(kc_model* m, kc_kv* kv, const uint32_t* token_ids, const kc_seq_step* seqs, const StepPlan& p,
-                cudaEvent_t before_copy = nullptr) {
+                cudaEvent_t before_copy = nullptr, const int32_t* feed = nullptr) {
   kc_ctx* c = m->ctx;
   const MetaLayout& L = p.lay;
   if (L.total > m->meta_cap) {
@@ -991,6 +1008,7 @@ int upload_meta(kc_model* m, kc_kv* kv, const uint32_t* token_ids, const kc_seq_
   int32_t* v_dlen = reinterpret_cast<int32_t*>(hbuf + L.v_draft_len);
   uint32_t* v_draft = reinterpret_cast<uint32_t*>(hbuf + L.v_draft);
   memcpy(tokens, token_ids, (size_t)p.n * 4);
+  if (feed) memcpy(hbuf + L.feed, feed, (size_t)p.n * 4);
   const int BS = kv->block_size;
   int row = 0, srow = 0, w = 0, dat = 0;
   for (int i = 0; i < p.n_seqs; ++i) {
@@ -1219,6 +1237,74 @@ extern "C" int kc_draft_chain(kc_model_t m, kc_kv_t kv, uint32_t first_token, in
   memcpy(proposal_out, m->result_host, (size_t)gamma * 4);
   c->draft_ms += std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t_begin).count();
   c->draft_tokens += gamma; c->draft_calls += 1;
+  return KC_OK;
+}
+
+// Pipelined plain decode (crates/kiln-engine/src/engine.rs:1428-1455, 1656-1744). The reference builds step N + 1 from
+// step N's still-lazy sampled tokens and reads step N back afterwards (async_eval); here step N + 1 is queued on the
+// stream with a kernel that takes its input ids from step N's token buffer, and step N's tokens reach the host through
+// a pinned slot and an event, so the host never waits between the two launches.
+extern "C" int kc_decode_launch(kc_model_t m, kc_kv_t kv, const uint32_t* token_ids, const int32_t* feed,
+                                const kc_seq_step* seqs, int32_t n_seqs, uint64_t* ticket_out) {
+  if (!m || !kv || !token_ids || !feed || !seqs || !ticket_out) return fail(KC_ERR_INVALID, "kc_decode_launch: NULL argument");
+  if (n_seqs < 1 || n_seqs > m->max_seqs) return fail(KC_ERR_INVALID, "kc_decode_launch: %d sequences (at most %d)", n_seqs, m->max_seqs);
+  const int prev = (int)(m->pipe_ticket % 2);
+  bool any_feed = false;
+  std::vector<uint32_t> ids(n_seqs);
+  for (int i = 0; i < n_seqs; ++i) {
+    if (seqs[i].len != 1 || seqs[i].sample_rows != 1)
+      return fail(KC_ERR_INVALID, "kc_decode_launch: segment %d has len %d, samples %d (a decode step feeds and samples one row)", i,
+                  seqs[i].len, seqs[i].sample_rows);
+    if (feed[i] >= 0) {
+      if (m->pipe_ticket == 0 || feed[i] >= m->pipe_n[prev])
+        return fail(KC_ERR_INVALID, "kc_decode_launch: feed row %d of a previous launch with %d rows", feed[i],
+                    m->pipe_ticket ? m->pipe_n[prev] : 0);
+      any_feed = true;
+      ids[i] = 0;  // replaced on the device
+    } else {
+      ids[i] = token_ids[i];
+    }
+  }
+  StepPlan p;
+  int rc = validate_step(m, kv, ids.data(), n_seqs, seqs, n_seqs, 0, &p);
+  if (rc) return rc;
+  kc_ctx* c = m->ctx;
+  CK(cudaSetDevice(c->device));
+  if ((rc = upload_meta(m, kv, ids.data(), seqs, p, nullptr, feed))) return rc;
+  uint32_t* tokens_dev = reinterpret_cast<uint32_t*>(m->meta_dev + p.lay.tokens);
+  if (any_feed)
+    LAUNCH(c, KC_PROF_SAMPLE, 1, launch_feed_tokens(tokens_dev, reinterpret_cast<const int32_t*>(m->meta_dev + p.lay.feed),
+                                                   m->pipe_tokens[prev], n_seqs, m->pipe_n[prev], c->stream));
+  if ((rc = run_forward(m, kv, tokens_dev, p, true))) return rc;
+  const uint64_t ticket = m->pipe_ticket + 1;
+  const int slot = (int)(ticket % 2);
+  LAUNCH(c, KC_PROF_SAMPLE, 1, launch_greedy_rows(m->logits, n_seqs, m->d.vocab_size, 1, m->pipe_tokens[slot], c->stream));
+  CK(cudaMemcpyAsync(m->pipe_host[slot], m->pipe_tokens[slot], (size_t)n_seqs * 4, cudaMemcpyDeviceToHost, c->stream));
+  CK(cudaMemcpyAsync(m->pipe_host[slot] + m->max_seqs, c->status, sizeof(uint32_t), cudaMemcpyDeviceToHost, c->stream));
+  CK(cudaEventRecord(m->pipe_ev[slot], c->stream));
+  m->pipe_ticket = ticket;
+  m->pipe_n[slot] = n_seqs;
+  *ticket_out = ticket;
+  return KC_OK;
+}
+
+extern "C" int kc_decode_collect(kc_model_t m, uint64_t ticket, uint32_t* row_tokens_out, int32_t n) {
+  if (!m || !row_tokens_out) return fail(KC_ERR_INVALID, "kc_decode_collect: NULL argument");
+  if (ticket == 0 || ticket > m->pipe_ticket || ticket + 1 < m->pipe_ticket)
+    return fail(KC_ERR_INVALID, "kc_decode_collect: ticket %llu is not one of the two most recent launches (latest %llu)",
+                (unsigned long long)ticket, (unsigned long long)m->pipe_ticket);
+  const int slot = (int)(ticket % 2);
+  if (n != m->pipe_n[slot]) return fail(KC_ERR_INVALID, "kc_decode_collect: %d rows asked of a launch of %d", n, m->pipe_n[slot]);
+  kc_ctx* c = m->ctx;
+  CK(cudaSetDevice(c->device));
+  CK(cudaEventSynchronize(m->pipe_ev[slot]));
+  const uint32_t st = m->pipe_host[slot][m->max_seqs];
+  if (st) {
+    cudaMemsetAsync(c->status, 0, sizeof(uint32_t), c->stream);
+    return fail(KC_ERR_TIMEOUT, "kc_decode_collect: device status 0x%x: a bounded wait gave up (kernel 0x%x, wait %u); the tokens of "
+                "this launch and of any launch fed from it are not valid", st, st & 0xff00u, st & 0xffu);
+  }
+  memcpy(row_tokens_out, m->pipe_host[slot], (size_t)n * 4);
   return KC_OK;
 }
 

@@ -48,6 +48,8 @@ cudaError_t launch_copy_block(bf16* pool, int layers, int NB, size_t block_elems
 // Greedy token per logits row; see kc_greedy_rows in kiln_cuda.h.
 cudaError_t launch_greedy_rows(const bf16* logits, int rows, int vocab, int normalize, uint32_t* tokens,
                                cudaStream_t s);
+// tokens[i] = prev[feed[i]] where feed[i] >= 0: the device-side token feedback of kc_decode_launch.
+cudaError_t launch_feed_tokens(uint32_t* tokens, const int32_t* feed, const uint32_t* prev, int n, int prev_n, cudaStream_t s);
 // The settle walk per verify segment; see kc_verify_accept in kiln_cuda.h.
 cudaError_t launch_verify_accept(const uint32_t* row_tokens, const int32_t* seq_row_offsets, const uint32_t* draft,
                                  const int32_t* draft_offsets, const int32_t* draft_len, int n_seqs, int max_commit,

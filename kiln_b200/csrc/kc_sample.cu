@@ -146,7 +146,24 @@ __global__ void verify_accept_kernel(const uint32_t* __restrict__ row_tokens, co
   n_accepted[i] = acc;
 }
 
+// Device-side token feedback of the pipelined decode (StepInput::Lazy, crates/kiln-engine/src/step.rs:45-56;
+// engine.rs:1711-1713): row i of the step takes the token that row feed[i] of the previous step sampled.
+__global__ void feed_tokens_kernel(uint32_t* __restrict__ tokens, const int32_t* __restrict__ feed,
+                                   const uint32_t* __restrict__ prev, int n, int prev_n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int f = feed[i];
+  if (f >= 0 && f < prev_n) tokens[i] = prev[f];
+}
+
 }  // namespace
+
+cudaError_t launch_feed_tokens(uint32_t* tokens, const int32_t* feed, const uint32_t* prev, int n, int prev_n, cudaStream_t s) {
+  if (n <= 0) return cudaSuccess;
+  return launch_k(feed_tokens_kernel, dim3((n + 127) / 128), dim3(128), 0, s, tokens, feed, prev, n, prev_n);
+}
 
 cudaError_t launch_greedy_rows(const bf16* logits, int rows, int vocab, int normalize, uint32_t* tokens,
                                cudaStream_t s) {

@@ -40,6 +40,14 @@ RELEASE_FN = C.CFUNCTYPE(None, _P, C.c_uint64)
 CHAIN_FN = C.CFUNCTYPE(C.c_int, _P, _P, C.c_uint32, C.c_int32, _U32P, C.c_int32, C.c_int32, _U32P)
 
 
+LAUNCH_FN = C.CFUNCTYPE(C.c_int, _P, _P, _U32P, C.POINTER(C.c_int32), C.POINTER(KhSeqStep), C.c_int32, C.POINTER(C.c_uint64))
+COLLECT_FN = C.CFUNCTYPE(C.c_int, _P, C.c_uint64, _U32P, C.c_int32)
+
+
+class KhDecodePipeline(C.Structure):
+    _fields_ = [("launch", LAUNCH_FN), ("collect", COLLECT_FN)]
+
+
 class KhStepModel(C.Structure):
     _fields_ = [("model", _P), ("kv", _P), ("verify_step", VERIFY_FN), ("copy_block", COPY_FN), ("vocab", C.c_int32)]
 
@@ -97,6 +105,8 @@ _SIGNATURES = {
     "kh_radix_prune_subtree": (None, [_P, _P, _U64]), "kh_radix_resident_blocks": (_U64, [_P]), "kh_radix_reset": (None, [_P]),
     "kh_engine_default_config": (None, [C.POINTER(KhEngineConfig)]),
     "kh_engine_create": (C.c_int, [C.POINTER(KhEngineConfig), C.POINTER(KhStepModel), C.POINTER(_P)]),
+    "kh_engine_set_pipeline": (C.c_int, [_P, C.POINTER(KhDecodePipeline)]),
+    "kh_engine_pipelined_steps": (C.c_uint64, [_P]),
     "kh_engine_free": (None, [_P]), "kh_engine_set_drafter": (C.c_int, [_P, C.POINTER(KhDrafter)]),
     "kh_engine_submit": (C.c_int, [_P, _U32P, _U64, _U64, _U32P, _U64, C.POINTER(_U64)]),
     "kh_engine_cancel": (C.c_int, [_P, _U64]), "kh_engine_step": (C.c_int, [_P]),
@@ -411,8 +421,8 @@ class StepModel:
     crates/kiln-engine/tests/deterministic_partition.rs:41-125).
     """
 
-    def __init__(self, c_struct: KhStepModel, keep):
-        self.c, self._keep = c_struct, keep
+    def __init__(self, c_struct: KhStepModel, keep, pipeline: Optional[KhDecodePipeline] = None):
+        self.c, self._keep, self.pipeline = c_struct, keep, pipeline
 
     @classmethod
     def from_cuda(cls, model, kv) -> "StepModel":
@@ -423,11 +433,40 @@ class StepModel:
         s.verify_step = C.cast(cl.kc_verify_step, VERIFY_FN)
         s.copy_block = C.cast(cl.kc_kv_copy_block, COPY_FN)
         s.vocab = model.config.vocab_size
-        return cls(s, (model, kv))
+        pipe = KhDecodePipeline(C.cast(cl.kc_decode_launch, LAUNCH_FN), C.cast(cl.kc_decode_collect, COLLECT_FN))
+        return cls(s, (model, kv), pipe)
 
     @classmethod
-    def from_python(cls, fn, vocab: int, copy_block=None) -> "StepModel":
-        """fn(ids: list[int], seqs: list[(len, offset, sample_rows, blocks)]) -> list[int] row tokens."""
+    def from_python(cls, fn, vocab: int, copy_block=None, pipelined: bool = False) -> "StepModel":
+        """fn(ids: list[int], seqs: list[(len, offset, sample_rows, blocks)]) -> list[int] row tokens.
+
+        ``pipelined`` adds the launch/collect pair: launch runs fn at once on ids resolved through the previous launch's
+        tokens (what the device does in stream order) and keeps the result under a ticket; collect hands it out."""
+        launched = {"ticket": 0, "tokens": {}, "log": []}
+
+        def _launch(_m, _kv, ids, feed, seqs, n_seqs, ticket):
+            try:
+                prev = launched["tokens"].get(launched["ticket"], [])
+                py_ids = [prev[feed[i]] if feed[i] >= 0 else ids[i] for i in range(n_seqs)]
+                py_seqs = [(seqs[i].len, seqs[i].offset, seqs[i].sample_rows, [seqs[i].blocks[b] for b in range(seqs[i].n_blocks)])
+                           for i in range(n_seqs)]
+                launched["ticket"] += 1   # like the device, only the two most recent launches stay collectable
+                launched["tokens"] = {launched["ticket"] - 1: prev, launched["ticket"]: [int(t) for t in fn(py_ids, py_seqs)]}
+                launched["log"].append(("launch", launched["ticket"], [int(feed[i]) for i in range(n_seqs)]))
+                ticket[0] = launched["ticket"]
+                return 0
+            except Exception:
+                return 2
+
+        def _collect(_m, ticket, rows, n):
+            toks = launched["tokens"].get(int(ticket))
+            if toks is None or len(toks) != n:
+                return 2
+            for i, t in enumerate(toks):
+                rows[i] = t
+            launched["log"].append(("collect", int(ticket)))
+            return 0
+
         def _verify(_m, _kv, ids, n, seqs, n_seqs, rows, ncom, nacc):
             try:
                 py_ids = [ids[i] for i in range(n)]
@@ -448,7 +487,10 @@ class StepModel:
         v, cp = VERIFY_FN(_verify), COPY_FN(_copy)
         s = KhStepModel()
         s.model, s.kv, s.verify_step, s.copy_block, s.vocab = None, None, v, cp, vocab
-        return cls(s, (v, cp, fn, copy_block))
+        pipe = KhDecodePipeline(LAUNCH_FN(_launch), COLLECT_FN(_collect)) if pipelined else None
+        out = cls(s, (v, cp, fn, copy_block, pipe), pipe)
+        out.pipeline_log = launched["log"]
+        return out
 
 
 class Drafter:
@@ -559,15 +601,25 @@ class SeqState:
 class Engine:
     """Engine::{new, submit, step, set_drafter, spec_stats} (engine.rs:1006-1407)."""
 
-    def __init__(self, config: EngineConfig, model: StepModel):
+    def __init__(self, config: EngineConfig, model: StepModel, pipelined: bool = True):
+        """``pipelined``: use the model's launch/collect pair (when it has one) for steady-state plain decode
+        (engine.rs:1428-1475); the reference always does."""
         self.config, self._model, self._drafter = config, model, None
         self._h = _P()
         c = config.to_c()
         _check(lib().kh_engine_create(C.byref(c), C.byref(model.c), C.byref(self._h)))
+        if pipelined and model.pipeline is not None:
+            _check(lib().kh_engine_set_pipeline(self._h, C.byref(model.pipeline)))
 
     def set_drafter(self, drafter: Drafter) -> None:
         self._drafter = drafter
         _check(lib().kh_engine_set_drafter(self._h, C.byref(drafter.c)))
+
+    def set_pipelined(self, on: bool) -> None:
+        """Turns pipelined plain decode on (the model must offer launch/collect) or off."""
+        if on and self._model.pipeline is None:
+            raise ValueError("this step model has no launch/collect pair")
+        _check(lib().kh_engine_set_pipeline(self._h, C.byref(self._model.pipeline) if on else None))
 
     def submit(self, prompt: Sequence[int], max_tokens: int, stop_tokens: Sequence[int] = ()) -> int:
         a, p = _u32(prompt)
@@ -596,6 +648,7 @@ class Engine:
     num_waiting = property(lambda self: int(lib().kh_engine_num_waiting(self._h)))
     iterations = property(lambda self: int(lib().kh_engine_iterations(self._h)))
     forwards = property(lambda self: int(lib().kh_engine_forwards(self._h)))
+    pipelined_steps = property(lambda self: int(lib().kh_engine_pipelined_steps(self._h)))
 
     def take_output(self, arrival: int, cap: int = 4096) -> Tuple[List[int], Optional[str]]:
         buf = (C.c_uint32 * cap)()

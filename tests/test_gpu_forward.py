@@ -208,6 +208,76 @@ def test_draft_chain_matches_stepwise_decode(ctx):
     assert chain == step
 
 
+def test_pipelined_decode_equals_stepwise(ctx):
+    """kc_decode_launch / kc_decode_collect (engine.rs:1428-1455, 1656-1766): steps fed on the device from the previous
+    launch's unread tokens produce the tokens of synchronous decode steps; a sequence that leaves shifts the feed rows."""
+    cfg, model, kv, _, _ = load(ctx, "tiny-llama")
+    ps = prompts(cfg, [30, 17, 22], 4)
+    tables = [[7, 2, 9], [1, 3], [4, 5, 6]]
+    kv2 = api.PagedKv(ctx, model.kv_spec(64, BS))
+    firsts = []
+    for pool in (kv, kv2):
+        seqs = [api.SeqStep(len(p), 0, 1, t) for p, t in zip(ps, tables)]
+        rows, _, _ = model.verify_step(api.StepBatch(sum(ps, []), seqs), pool)
+        firsts = [int(r) for r in rows]
+    # synchronous: 6 steps; sequence 1 stops after step 2
+    alive, toks, want = [0, 1, 2], list(firsts), {0: [], 1: [], 2: []}
+    for step in range(6):
+        seqs = [api.SeqStep(1, len(ps[i]) + step, 1, tables[i]) for i in alive]
+        rows, _, _ = model.verify_step(api.StepBatch([toks[i] for i in alive], seqs), kv)
+        for i, r in zip(alive, rows):
+            toks[i] = int(r)
+            want[i].append(int(r))
+        if step == 2:
+            alive = [0, 2]
+    # pipelined: every step is launched before the previous one is collected
+    alive, got = [0, 1, 2], {0: [], 1: [], 2: []}
+    pending = None
+    for step in range(6):
+        seqs = [api.SeqStep(1, len(ps[i]) + step, 1, tables[i]) for i in alive]
+        if pending is None:
+            t = model.decode_launch(api.StepBatch([firsts[i] for i in alive], seqs), kv2, [-1] * len(alive))
+        else:
+            feed = [pending[1].index(i) for i in alive]
+            t = model.decode_launch(api.StepBatch([0] * len(alive), seqs), kv2, feed)
+            for i, r in zip(pending[1], model.decode_collect(pending[0], len(pending[1]))):
+                got[i].append(r)
+        pending = (t, list(alive))
+        if step == 2:
+            alive = [0, 2]
+    for i, r in zip(pending[1], model.decode_collect(pending[0], len(pending[1]))):
+        got[i].append(r)
+    assert got == want
+    assert ctx.device_status() == 0
+    with pytest.raises(api.KcError, match="most recent"):
+        model.decode_collect(pending[0] - 2, 2)
+    with pytest.raises(api.KcError, match="feed row"):
+        model.decode_launch(api.StepBatch([0], [api.SeqStep(1, 40, 1, tables[0])]), kv2, [5])
+    with pytest.raises(api.KcError, match="one row"):
+        model.decode_launch(api.StepBatch([0, 0], [api.SeqStep(2, 40, 1, tables[0])]), kv2, [-1])
+
+
+def test_engine_pipelines_plain_decode_on_the_device(ctx):
+    """The host engine over the CUDA model: plain decode takes the pipelined path and emits what the synchronous
+    engine emits (prefix cache on, three requests of different lengths, one with a stop token)."""
+    from kiln_b200 import host
+    cfg, model, kv, _, _ = load(ctx, "tiny-llama")
+    ps = prompts(cfg, [33, 18, 25], 6)
+    outs = []
+    for pipelined in (True, False):
+        kv.reset()
+        ec = host.EngineConfig(block_size=BS, num_blocks=64, max_batch_tokens=256, prefill_chunk=64, prefill_fine_chunk=16,
+                               prefix_cache=True, deterministic_decode_width=32, gamma=0, spec_max_batch=4,
+                               spec_min_acceptance=0.0, max_key_len=0, batch_verify=True)
+        eng = host.Engine(ec, host.StepModel.from_cuda(model, kv), pipelined=pipelined)
+        arr = [eng.submit(p, n) for p, n in zip(ps, (24, 9, 15))]
+        out = eng.run_to_completion(arr)
+        outs.append([out[a] for a in arr])
+        assert (eng.pipelined_steps > 0) == pipelined
+    assert outs[0] == outs[1]
+    assert ctx.device_status() == 0
+
+
 def test_invalid_batches_are_rejected(ctx):
     """Validation mirrors nn.rs:1309-1337; errors come back as status + message, never an abort."""
     cfg, model, kv, _, _ = load(ctx, "tiny-llama")
