@@ -527,6 +527,51 @@ def tp_record(rank: int, local_rank: int, world: int, dist, barrier) -> dict:
     return rec
 
 
+def stream_gemv_records(ctx, pk):
+    """The weight-streaming lane by itself on the decode shapes (at most 8 activation rows): time per call (the lane's
+    kernel plus the reduction of its partials) from CUDA events on the library's stream around a run of back-to-back
+    calls, against the weight bytes (mlx layout: packed words + bf16 scales
+    and biases) at the measured copy bandwidth. Three copies of each weight are used in turn, so no launch finds its
+    weight in L2 (3 x 66 MB > 126 MB); the tensor-core lane is timed beside it on the same inputs."""
+    import torch
+    from kiln_b200 import api
+    out = []
+    for label, n, k in (("llama-3.1-8b gate_up 28672x4096 w4g64", 28672, 4096), ("llama-3.1-8b down 4096x14336 w4g64", 4096, 14336),
+                        ("llama-3.2-1b gate_up 16384x2048 w4g64", 16384, 2048)):
+        g = torch.Generator(device="cuda").manual_seed(n + k)
+        copies = max(3, -(-3 * 66_000_000 // (n * k // 2)))
+        ws = []
+        for _ in range(copies):
+            w = torch.randint(-2 ** 31, 2 ** 31 - 1, (n, k // 8), dtype=torch.int32, device="cuda", generator=g)
+            sc = (torch.rand(n, k // 64, device="cuda", generator=g) * 0.01 + 0.001).to(torch.bfloat16)
+            bi = (torch.rand(n, k // 64, device="cuda", generator=g) * -0.08).to(torch.bfloat16)
+            ws.append(api.QuantizedWeight(ctx, w, sc, bi, 4, 64))
+        nbytes = n * k // 2 + 2 * n * (k // 64) * 2
+        for rows in (1, 8):
+            x = torch.randn(16, k, device="cuda", generator=g).to(torch.bfloat16)
+            y = torch.empty(rows, n, dtype=torch.bfloat16, device="cuda")
+            torch.cuda.synchronize()
+            rec = {"weight": label, "rows": rows, "weight_bytes": nbytes}
+            lib_stream = torch.cuda.ExternalStream(ctx.stream)   # the events must sit on the stream the kernels run on
+            for lane, fn in (("stream", "kc_quantized_matmul_stream"), ("tensor", "kc_quantized_matmul")):
+                call = getattr(api.L.lib(), fn)
+                for i in range(2 * copies):   # warm-up: every copy twice
+                    api.check(call(ctx._h, ws[i % copies]._h, x.data_ptr(), rows, y.data_ptr()))
+                reps = 8 * copies
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(lib_stream)
+                for i in range(reps):
+                    api.check(call(ctx._h, ws[i % copies]._h, x.data_ptr(), rows, y.data_ptr()))
+                e1.record(lib_stream)
+                ctx.sync()
+                us = e0.elapsed_time(e1) * 1e3 / reps
+                rec[lane] = {"us": round(us, 2), "GB/s": round(nbytes / us * 1e-3, 1), "frac_of_hbm": round(nbytes / us * 1e-3 / pk["hbm_gbs"], 3)}
+            out.append(rec)
+        for q in ws:
+            q.close()
+    return out
+
+
 def draft_lane_line(args, metric, config, warmup):
     """The 1B configuration with the REAL draft model: the target's first `draft_layers` layers with their own pool
     (crates/kiln-models/src/draft.rs:128-162), proposing k tokens per round through kc_draft_chain. One step = one engine
@@ -547,6 +592,7 @@ def draft_lane_line(args, metric, config, warmup):
     max_step = 256
     model = api.CudaModel(ctx, cfg, ck, max_step_tokens=max_step, max_step_seqs=4)
     dmodel = api.CudaModel(ctx, dcfg, dck, max_step_tokens=max_step, max_step_seqs=4)
+    dmodel.set_stream_lane(True)     # the draft's chained decode forwards take the weight-streaming kernels
     del ck, dck
     bs, nb = 16, 64 + (hi + gen + 64) // 16
     kv = api.PagedKv(ctx, model.kv_spec(nb, bs))
@@ -612,6 +658,8 @@ def draft_lane_line(args, metric, config, warmup):
     draft_us = d_ms * 1e3 / max(d_tok, 1)
     verify_ms = sorted(r["dev_ms"] for r in recs)[len(recs) // 2]
     verify_floor_ms = weight_bytes(cfg) / (pk["hbm_gbs"] * 1e9) * 1e3
+    launches = int(ctx.launch_count())
+    gemv = stream_gemv_records(ctx, pk)
     line = {
         "metric": metric, "value": tokens / (wall * 1e-3), "unit": "tok/s", "n_gpus": 1, "steps": len(recs), "warmup": warmup,
         "ms_per_step": wall / len(recs), "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
@@ -624,13 +672,15 @@ def draft_lane_line(args, metric, config, warmup):
         "speedup_on_over_off": (tokens / wall) / (off_tokens / off_wall),
         "draft_lane": {"us_per_proposed_token": draft_us, "hbm_floor_us": floor_us, "frac_of_hbm_floor": floor_us / draft_us,
                        "proposed_tokens": d_tok, "chains": d_calls,
-                       "draft_weight_bytes": weight_bytes(dcfg), "peak_source": pk["source"]},
+                       "draft_weight_bytes": weight_bytes(dcfg), "peak_source": pk["source"],
+                       "lane": "weight-streaming kernels (kc_model_set_stream_lane) for the chained one-row forwards"},
+        "stream_gemv": gemv,
         "verify_forward": {"p50_device_ms": verify_ms, "hbm_floor_ms": verify_floor_ms, "frac_of_hbm_floor": verify_floor_ms / verify_ms,
                            "rows": k + 1, "target_weight_bytes": weight_bytes(cfg)},
         "acceptance": {"proposed": sum(r["proposed"] for r in recs), "accepted": sum(r["accepted"] for r in recs),
                        "tokens_per_step": tokens / len(recs)},
         "spec_on_equals_off": {"sequences_checked": len(outs) + len(off_outs), "identical": bool(identical)},
-        "gpu_launches": int(ctx.launch_count()),
+        "gpu_launches": launches,
     }
     print(json.dumps(line))
     eng = None

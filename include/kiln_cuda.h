@@ -182,6 +182,14 @@ KC_API void kc_model_free(kc_model_t model);
 KC_API int kc_envelope(kc_model_t model, int32_t* max_gamma, int32_t* max_key_len,
                        int32_t* det_width);
 
+/* Switches the weight-streaming lane on or off for this model: forwards of at most 8 rows (a draft model's chained
+ * decode steps, crates/kiln-models/src/draft.rs:354-388) then read every weight straight from global memory into
+ * registers instead of going through the tensor-core pipeline, whose set-up dominates such a step. Off by default,
+ * and meant for draft models: a row's bits differ between the two lanes, so a target model whose decode steps
+ * (few rows) and verify steps (more than 8 rows) must agree bit for bit keeps it off. Not available on a
+ * tensor-parallel slice. */
+KC_API int kc_model_set_stream_lane(kc_model_t model, int32_t on);
+
 /* Bytes of quantised weight storage held on the device. */
 KC_API int64_t kc_model_weight_bytes(kc_model_t model);
 
@@ -305,6 +313,14 @@ KC_API void kc_qweight_free(kc_qweight_t w);
 /* y[m, out] (bf16, device) = x[m, in] (bf16, device) · dequant(W)ᵀ. */
 KC_API int kc_quantized_matmul(kc_ctx_t ctx, kc_qweight_t w, const void* x_dev, int32_t m,
                                void* y_dev);
+
+/* The same product for at most 8 rows through the weight-streaming lane: the kernels a model runs for its decode
+ * forwards once kc_model_set_stream_lane switched the lane on. MLX likewise serves small batches with its own
+ * row-vector kernels (quantized_matmul dispatches qmv below a row threshold), and this lane computes in their
+ * arithmetic class: per group, scale * sum(x q) + bias * sum(x) in fp32, no weight rounded to bf16. As there, the two
+ * lanes agree to rounding, not bit for bit. */
+KC_API int kc_quantized_matmul_stream(kc_ctx_t ctx, kc_qweight_t w, const void* x_dev, int32_t m,
+                                      void* y_dev);
 
 /* kc_quantized_matmul without any allocation behind it. No counterpart in the
  * reference (MLX owns every buffer there); added for callers that cannot let a

@@ -423,6 +423,10 @@ class CudaModel:
                                      int(b.shape[0]), int(gamma), out.ctypes.data_as(C.POINTER(C.c_uint32))))
         return [int(x) for x in out]
 
+    def set_stream_lane(self, on: bool = True) -> None:
+        """Forwards of at most 8 rows take the weight-streaming kernels (kc_model_set_stream_lane): for draft models."""
+        check(L.lib().kc_model_set_stream_lane(self._h, int(on)))
+
     def envelope(self):
         """(max_gamma, max_key_len or 0 = unbounded, deterministic width) as the backend provides them."""
         g, k, w = C.c_int32(), C.c_int32(), C.c_int32()
@@ -503,6 +507,16 @@ class QuantizedWeight:
         y = torch.empty(m, self.out_features, dtype=torch.bfloat16, device=x.device)
         torch.cuda.current_stream().synchronize()
         check(L.lib().kc_quantized_matmul(self.ctx._h, self._h, xp.data_ptr(), m, y.data_ptr()))
+        self.ctx.sync()
+        return y
+
+    def matmul_stream(self, x: torch.Tensor) -> torch.Tensor:
+        """The same product for at most 8 rows through the weight-streaming lane (kc_quantized_matmul_stream)."""
+        assert x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[1] == self.in_features
+        x = x.contiguous()
+        y = torch.empty(x.shape[0], self.out_features, dtype=torch.bfloat16, device=x.device)
+        torch.cuda.current_stream().synchronize()
+        check(L.lib().kc_quantized_matmul_stream(self.ctx._h, self._h, x.data_ptr(), x.shape[0], y.data_ptr()))
         self.ctx.sync()
         return y
 

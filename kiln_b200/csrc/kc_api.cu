@@ -159,6 +159,7 @@ struct kc_model {
   kc_model_desc d{};
   int Hq = 0, Hkv = 0;                 // local (tensor-parallel) head counts
   int F = 0;                           // local intermediate size
+  bool stream_lane = false;            // forwards of at most QL_STREAM_MAX_M rows take the weight-streaming kernels
   bool glu_interleaved = false;        // gate_up rows alternate gate / up in blocks of 128 (so the GEMM can fuse the activation)
   int n_qkv = 0;
   std::vector<Layer> layers;
@@ -471,6 +472,16 @@ static int run_gated(kc_ctx* c, const QWeight& w, const ActOperand& x, int M, bf
   return KC_OK;
 }
 
+// The weight-streaming lane for at most QL_STREAM_MAX_M rows: *out describes where the result is (bf16 y, or the
+// fp32 partials of the lane for the consumer kernel to sum); without `out` they are reduced into y here.
+static int run_stream(kc_ctx* c, const QWeight& w, const bf16* x, int M, bf16* y, int ldy, float* partial, SublayerOut* out) {
+  const int pieces = qlinear_stream_pieces(w);
+  LAUNCH(c, KC_PROF_GEMM, 1, qlinear_stream(w, x, w.K, M, partial, c->status, c->stream));
+  if (!out) LAUNCH(c, KC_PROF_GEMM_REDUCE, 1, qlinear_reduce_splits(partial, pieces, M, w.N, y, ldy, c->stream));
+  else *out = SublayerOut::partials(partial, pieces, (size_t)M, w.N);
+  return KC_OK;
+}
+
 // ---------------------------------------------------------------------------
 // stand-alone quantised weight (parity tests / composed graphs)
 // ---------------------------------------------------------------------------
@@ -509,8 +520,11 @@ extern "C" int kc_qweight_create(kc_ctx_t c, const uint32_t* w, const void* scal
   q->ctx = c;
   cudaError_t e = qweight_build(&q->w, (const uint32_t*)dw, (const bf16*)ds, (const bf16*)db, out_features,
                                 in_features, bits, group_size, c->sm_count, c->stream);
-  if (e == cudaSuccess && q->w.splits > 1)
-    e = cudaMalloc(&q->partial, (size_t)q->w.splits * QL_MAX_M * q->w.N * sizeof(float));
+  if (e == cudaSuccess) {
+    const size_t need = std::max((size_t)(q->w.splits > 1 ? q->w.splits : 0) * QL_MAX_M * q->w.N,
+                                 (size_t)qlinear_stream_pieces(q->w) * QL_STREAM_MAX_M * q->w.N);
+    if (need) e = cudaMalloc(&q->partial, need * sizeof(float));
+  }
   cudaStreamSynchronize(c->stream);
   cudaFree(dw); cudaFree(ds); cudaFree(db);
   if (e != cudaSuccess) { qweight_free(&q->w); delete q; return fail(KC_ERR_CUDA, "kc_qweight_create: %s", cudaGetErrorString(e)); }
@@ -543,6 +557,19 @@ extern "C" int kc_quantized_matmul(kc_ctx_t c, kc_qweight_t q, const void* x_dev
     q->op_ptr = x_dev; q->op_rows = rows;
   }
   RC(run_qlinear(c, q->w, q->op, m, (bf16*)y_dev, q->w.N, q->partial));
+  return KC_OK;
+}
+
+// The weight-streaming lane on its own (at most 8 rows): what a model with the lane switched on runs for its decode
+// forwards (kc_model_set_stream_lane).
+extern "C" int kc_quantized_matmul_stream(kc_ctx_t c, kc_qweight_t q, const void* x_dev, int32_t m, void* y_dev) {
+  if (!c || !q || !x_dev || !y_dev) return fail(KC_ERR_INVALID, "kc_quantized_matmul_stream: NULL argument");
+  if (m < 1 || m > QL_STREAM_MAX_M) return fail(KC_ERR_INVALID, "kc_quantized_matmul_stream: m = %d (1..%d)", m, QL_STREAM_MAX_M);
+  if ((uintptr_t)x_dev % 16) return fail(KC_ERR_INVALID, "kc_quantized_matmul_stream: x must be 16-byte aligned");
+  if (q->ctx != c) return fail(KC_ERR_INVALID, "kc_quantized_matmul_stream: the weight was created on another context");
+  CK(cudaSetDevice(c->device));
+  LAUNCH(c, KC_PROF_GEMM, 1, qlinear_stream(q->w, (const bf16*)x_dev, q->w.K, m, q->partial, c->status, c->stream));
+  LAUNCH(c, KC_PROF_GEMM_REDUCE, 1, qlinear_reduce_splits(q->partial, qlinear_stream_pieces(q->w), m, q->w.N, (bf16*)y_dev, q->w.N, c->stream));
   return KC_OK;
 }
 
@@ -860,7 +887,11 @@ extern "C" int kc_model_load(kc_ctx_t c, const kc_model_desc* desc, const kc_ten
   // split-K workspace: the largest splits * N over all weights, for one 512-row slab
   {
     size_t need = 0;
-    auto acc = [&](const QWeight& w) { if (w.splits > 1) need = std::max(need, (size_t)w.splits * QL_MAX_M * w.N * sizeof(float)); };
+    auto acc = [&](const QWeight& w) {
+      if (w.splits > 1) need = std::max(need, (size_t)w.splits * QL_MAX_M * w.N * sizeof(float));
+      // the weight-streaming lane's partials, at most 8 rows
+      need = std::max(need, (size_t)qlinear_stream_pieces(w) * QL_STREAM_MAX_M * w.N * sizeof(float));
+    };
     for (auto& L : m->layers) { acc(L.qkv); acc(L.o); acc(L.gate_up); acc(L.down); }
     acc(m->head);
     if (need) { cudaError_t e = cudaMalloc(&m->partial, need); if (e != cudaSuccess) LOAD_FAIL(fail(KC_ERR_OOM, "split-K workspace: %s", cudaGetErrorString(e))); }
@@ -1093,26 +1124,36 @@ int run_forward(kc_model* m, kc_kv* kv, const uint32_t* tokens_dev, const StepPl
   const int32_t* kv_slot = reinterpret_cast<const int32_t*>(m->meta_dev + p.lay.kv_slot);
   int rc;
   if ((rc = ensure_attn_ws(m, p))) return rc;
+  const bool stream = m->stream_lane && n <= QL_STREAM_MAX_M && d.tp_world <= 1;
   LAUNCH(c, KC_PROF_ROWWISE, 1, launch_embed(m->emb_w, m->emb_s, m->emb_b, tokens_dev, n, H, d.bits, d.group_size, m->embed_scale, d.vocab_size, m->h, c->stream));
   LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, SublayerOut::none(), nullptr, m->layers[0].input_ln, nullptr, n, H, d.rms_norm_eps, nullptr, m->normed, c->stream));
   for (int l = 0; l < d.num_layers; ++l) {
     Layer& L = m->layers[l];
     SublayerOut so;
-    RC(run_qlinear(c, L.qkv, m->op_normed, n, m->qkv, m->n_qkv, m->partial, &so));
+    if (stream) RC(run_stream(c, L.qkv, m->normed, n, m->qkv, m->n_qkv, m->partial, &so));
+    else RC(run_qlinear(c, L.qkv, m->op_normed, n, m->qkv, m->n_qkv, m->partial, &so));
     LAUNCH(c, KC_PROF_ROWWISE, 1, launch_rope_kv_write(so, L.qkv_bias, m->inv_freq, token_pos, kv_slot, n, m->Hq, m->Hkv, D, d.rope_traditional, l,
                             kv->num_blocks, kv->block_size, kv->pool, m->q_rot, c->stream));
     const int window = (d.sliding_window > 0 && (l % 2 == 0)) ? d.sliding_window : 0;
     AttnParams a = attn_params(m, kv, p, l, m->q_rot, m->attn, m->attn_scale, gemma ? d.attn_logit_softcapping : 0.f, window, m->Hq);
     LAUNCH(c, KC_PROF_ATTN, 2, paged_attention(kv->map, a, D, p.tokens_per_item, p.n_work, p.max_chunks, n, c->stream));
-    RC(run_qlinear(c, L.o, m->op_attn, n, m->proj, H, m->partial, d.tp_world > 1 ? nullptr : &so));
+    if (stream) RC(run_stream(c, L.o, m->attn, n, m->proj, H, m->partial, &so));
+    else RC(run_qlinear(c, L.o, m->op_attn, n, m->proj, H, m->partial, d.tp_world > 1 ? nullptr : &so));
     if (d.tp_world > 1) {
       if ((rc = tp_allgather(m, m->proj, m->proj_ranks, n))) return rc;
       so = SublayerOut::of_ranks(m->proj_ranks, d.tp_world, (size_t)n, H);
     }
     if (gemma) LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, so, L.post_attn_ln, L.pre_ffw_ln, nullptr, n, H, d.rms_norm_eps, m->h, m->normed, c->stream));
     else LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, so, nullptr, L.post_attn_ln, nullptr, n, H, d.rms_norm_eps, m->h, m->normed, c->stream));
-    RC(run_gated(c, L.gate_up, m->op_normed, n, m->gu, m->F, gemma ? 1 : 0, m->glu_interleaved, m->act, m->partial));
-    RC(run_qlinear(c, L.down, m->op_act, n, m->proj, H, m->partial, d.tp_world > 1 ? nullptr : &so));
+    if (stream) {
+      SublayerOut gu;
+      RC(run_stream(c, L.gate_up, m->normed, n, m->gu, 2 * m->F, m->partial, &gu));
+      LAUNCH(c, KC_PROF_ROWWISE, 1, launch_glu_from(gu, n, m->F, gemma ? 1 : 0, m->glu_interleaved ? 1 : 0, m->act, c->stream));
+      RC(run_stream(c, L.down, m->act, n, m->proj, H, m->partial, &so));
+    } else {
+      RC(run_gated(c, L.gate_up, m->op_normed, n, m->gu, m->F, gemma ? 1 : 0, m->glu_interleaved, m->act, m->partial));
+      RC(run_qlinear(c, L.down, m->op_act, n, m->proj, H, m->partial, d.tp_world > 1 ? nullptr : &so));
+    }
     if (d.tp_world > 1) {
       if ((rc = tp_allgather(m, m->proj, m->proj_ranks, n))) return rc;
       so = SublayerOut::of_ranks(m->proj_ranks, d.tp_world, (size_t)n, H);
@@ -1123,7 +1164,8 @@ int run_forward(kc_model* m, kc_kv* kv, const uint32_t* tokens_dev, const StepPl
   if (want_logits && p.n_sampled > 0) {
     const int32_t* sampled = reinterpret_cast<const int32_t*>(m->meta_dev + p.lay.sampled);
     LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, SublayerOut::none(), nullptr, m->final_norm, sampled, p.n_sampled, H, d.rms_norm_eps, nullptr, m->hs, c->stream));
-    RC(run_qlinear(c, m->head, m->op_hs, p.n_sampled, m->logits, d.vocab_size, m->partial));
+    if (stream) RC(run_stream(c, m->head, m->hs, p.n_sampled, m->logits, d.vocab_size, m->partial, nullptr));
+    else RC(run_qlinear(c, m->head, m->op_hs, p.n_sampled, m->logits, d.vocab_size, m->partial));
     if (gemma && d.final_logit_softcapping > 0.f)
       LAUNCH(c, KC_PROF_ROWWISE, 1, launch_softcap(m->logits, (long long)p.n_sampled * d.vocab_size, d.final_logit_softcapping, c->stream));
   }
@@ -1131,6 +1173,13 @@ int run_forward(kc_model* m, kc_kv* kv, const uint32_t* tokens_dev, const StepPl
 }
 
 }  // namespace
+
+extern "C" int kc_model_set_stream_lane(kc_model_t m, int32_t on) {
+  if (!m) return fail(KC_ERR_INVALID, "kc_model_set_stream_lane: model is NULL");
+  if (on && m->d.tp_world > 1) return fail(KC_ERR_UNSUPPORTED, "kc_model_set_stream_lane: not available on a tensor-parallel slice");
+  m->stream_lane = on != 0;
+  return KC_OK;
+}
 
 extern "C" int kc_forward_step(kc_model_t m, kc_kv_t kv, const uint32_t* token_ids, int32_t n, const kc_seq_step* seqs,
                                int32_t n_seqs, int32_t pad_rows, void** logits_dev, int32_t* n_sampled) {

@@ -69,7 +69,21 @@ __device__ __forceinline__ void load8(const RowSource& s, size_t row, int col, f
   if (s.part) {
     const float* p0 = s.part + row * s.ld + col;
     float4 a = *reinterpret_cast<const float4*>(p0), b = *reinterpret_cast<const float4*>(p0 + 4);
-    for (int k = 1; k < s.splits; ++k) {
+    // the additions run in piece order; the loads of four pieces are issued together so that their latencies overlap
+    int k = 1;
+    for (; k + 4 <= s.splits; k += 4) {
+      float4 c[4], d[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        c[j] = *reinterpret_cast<const float4*>(p0 + (k + j) * s.split_stride);
+        d[j] = *reinterpret_cast<const float4*>(p0 + (k + j) * s.split_stride + 4);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        a.x += c[j].x; a.y += c[j].y; a.z += c[j].z; a.w += c[j].w; b.x += d[j].x; b.y += d[j].y; b.z += d[j].z; b.w += d[j].w;
+      }
+    }
+    for (; k < s.splits; ++k) {
       const float4 c = *reinterpret_cast<const float4*>(p0 + k * s.split_stride);
       const float4 d = *reinterpret_cast<const float4*>(p0 + k * s.split_stride + 4);
       a.x += c.x; a.y += c.y; a.z += c.z; a.w += c.w; b.x += d.x; b.y += d.y; b.z += d.z; b.w += d.w;
@@ -349,6 +363,25 @@ __global__ void __launch_bounds__(256) glu_kernel(const bf16* __restrict__ gu, i
   }
 }
 
+// The same activation over a GEMM output still in its consumer form (bf16, or fp32 k-split partials summed here).
+__global__ void __launch_bounds__(256) glu_from_kernel(const RowSource gu, int n, int F, int gelu, int interleaved, bf16* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int per_row = F / 8;
+  const int total = n * per_row;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const int row = i / per_row, col = (i - row * per_row) * 8;
+    const int gcol = interleaved ? (col >> 7) * 256 + (col & 127) : col;
+    const int ucol = interleaved ? gcol + 128 : F + col;
+    float g[8], u[8];
+    load8(gu, (size_t)row, gcol, g);
+    load8(gu, (size_t)row, ucol, u);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) g[k] = gelu ? act_gelu_mul(g[k], u[k]) : act_silu_mul(g[k], u[k]);
+    store8_bf16(out + (size_t)row * F + col, g);
+  }
+}
+
 // CausalLm::softcap_logits (nn.rs:1158-1169): tanh(l / cap) * cap, each op rounded to bf16.
 __global__ void softcap_kernel(bf16* __restrict__ x, long long total, float cap) {
   pdl_launch_dependents();
@@ -421,6 +454,14 @@ cudaError_t launch_glu(const bf16* gu, int n, int F, int gelu, int interleaved, 
   const long long total = (long long)n * (F / 8);
   const int blocks = (int)std::min<long long>((total + 255) / 256, 148LL * 8);
   return launch_k(glu_kernel, dim3(blocks), dim3(256), 0, s, gu, n, F, gelu, interleaved, out);
+}
+
+cudaError_t launch_glu_from(const SublayerOut& gu, int n, int F, int gelu, int interleaved, bf16* out, cudaStream_t s) {
+  if (n <= 0) return cudaSuccess;
+  if (F % 8 || (interleaved && F % 128) || gu.ld != 2 * F) return cudaErrorInvalidValue;
+  const int total = n * (F / 8);
+  const int blocks = std::max(1, std::min((total + 255) / 256, 148 * 8));
+  return launch_k(glu_from_kernel, dim3(blocks), dim3(256), 0, s, row_source(gu), n, F, gelu, interleaved, out);
 }
 
 cudaError_t launch_softcap(bf16* x, long long total, float cap, cudaStream_t s) {

@@ -41,6 +41,8 @@ cudaError_t launch_rope_kv_write(const SublayerOut& qkv, const bf16* bias, const
                                  int NB, int BS, bf16* pool, bf16* q_out, cudaStream_t s);
 
 cudaError_t launch_glu(const bf16* gu, int n, int F, int gelu, int interleaved, bf16* out, cudaStream_t s);
+// The same over a GEMM output in its consumer form (gu.ld must be 2 F).
+cudaError_t launch_glu_from(const SublayerOut& gu, int n, int F, int gelu, int interleaved, bf16* out, cudaStream_t s);
 cudaError_t launch_softcap(bf16* x, long long total, float cap, cudaStream_t s);
 cudaError_t launch_copy_block(bf16* pool, int layers, int NB, size_t block_elems, uint32_t src, uint32_t dst,
                               cudaStream_t s);

@@ -745,6 +745,320 @@ int qlinear_launches(const QWeight& w, int M) {
 }
 
 // ---------------------------------------------------------------------------
+// The weight-streaming lane: at most 8 activation rows (the draft model's chained decode forwards,
+// crates/kiln-models/src/draft.rs:354-388). Such a launch is bound by the weight bytes alone, and the tensor-core
+// kernel above spends most of its time setting up its pipelines. Here the weight is one flat list of units (one
+// k-block of one group of four neighbouring tiles: contiguous in memory) that a grid of persistent CTAs cuts into equal
+// contiguous runs; a producer warp bulk-copies a CTA's units through a shared-memory ring, and eight consumer warps,
+// 16 rows of each of the four tiles apiece, multiply them with mma.sync.m16n8k16, the activation rows riding as the 8
+// columns of the B operand (one activation fragment serves the four tiles).
+//
+// Arithmetic: MLX's row-vector class (its qmv kernels, which serve small batches there too): per quantisation group
+// y += scale * sum_k(x_k q_k) + bias * sum_k(x_k) in fp32. The MMA runs on the raw integers (a 4-bit q enters as the
+// bf16 value 128 + q, which one OR builds; the 128 is folded into the bias term), so nothing is dequantised per
+// element. The 16 k positions of an MMA are assigned to the lanes so that lane (g, t) owns input features
+// 32 h + 8 t .. + 7 of each 32-feature half h of the k-block — 4 contiguous bytes of a 4-bit row — and the activation
+// fragment is gathered with the same assignment, so the sum runs over the same products.
+//
+// A run that crosses a group boundary flushes one partial per group it touches. The partials are fp32
+// [pieces][M][N]; which CTA writes which piece of which group is a function of the weight's shape and the SM count
+// only, and the consumer kernel sums the pieces in index order, so the result does not depend on timing or on M.
+// ---------------------------------------------------------------------------
+
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+constexpr int QG_CONSUMER_WARPS = 8;                       // x 16 weight rows = the 128 rows of a tile
+constexpr int QG_THREADS = 32 * (QG_CONSUMER_WARPS + 1);   // + the producer warp
+#ifndef QG_CTAS
+#define QG_CTAS 2
+#endif
+constexpr int QG_CTAS_PER_SM = QG_CTAS;
+constexpr int QG_MAX_PIECES = 40;                          // fp32 partials per output element, at most
+constexpr int QG_MIN_UNITS = 4;                            // a CTA's run is at least this long (about 72 KB of 4-bit records)
+constexpr int QG_MAX_STAGES = QG_CTAS == 3 ? 3 : 4;
+constexpr size_t QG_RING_BYTES = QG_CTAS == 3 ? 60 * 1024 : 80 * 1024;
+
+// One unit of work = the records of one k-block of a whole tile group (QL_TILE_GROUP neighbouring tiles, contiguous in
+// memory): one bulk copy, one barrier round, one activation fragment for 4 x 128 weight rows.
+struct QgParams {
+  const uint8_t* records;
+  uint32_t record_bytes;
+  int N, n_groups, kblocks, pieces, stages;
+  const bf16* x;   // [M, ldx]
+  int ldx, M;
+  float* partial;  // [pieces][M][N]
+  uint32_t* status;
+};
+
+// The persistent CTA that owns unit r of T when G CTAs cut the list into runs [T c / G, T (c + 1) / G).
+__host__ __device__ inline long long qg_owner(long long r, long long T, long long G) { return ((r + 1) * G + T - 1) / T - 1; }
+
+// Elements (2p, 2p + 1), p = 0..3, of the lane's 8 features as bf16 pairs holding the raw integers.
+template <int BITS>
+__device__ __forceinline__ void qg_raw_pairs(const uint32_t* u, uint32_t (&e)[4]) {
+  if (BITS == 4) {
+    // The record's nibble order puts element 2p at bits 4p and element 2p + 1 at bits 16 + 4p. Two masks split the
+    // word into bytes (even nibbles: elements 0, 4, 1, 5; odd nibbles: 2, 6, 3, 7), and a byte permute sets each
+    // under 0x43: the bf16 value 128 + q, exact.
+    const uint32_t lo = u[0] & 0x0F0F0F0Fu, hi = (u[0] >> 4) & 0x0F0F0F0Fu;
+    e[0] = __byte_perm(lo, 0x43434343u, 0x4240u);   // elements 0, 1
+    e[1] = __byte_perm(hi, 0x43434343u, 0x4240u);   // elements 2, 3
+    e[2] = __byte_perm(lo, 0x43434343u, 0x4341u);   // elements 4, 5
+    e[3] = __byte_perm(hi, 0x43434343u, 0x4341u);   // elements 6, 7
+  } else {
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      const uint32_t w = u[p >> 1];
+      const int k = (p & 1) * 2;
+      // byte k under the exponent of 2^23: the float 8388608 + q, minus 2^23 = q exactly; q < 256 is exact in bf16
+      const float lo = __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540u | k)) - 8388608.f;
+      const float hi = __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540u | (k + 1))) - 8388608.f;
+      e[p] = pack_bf162(lo, hi);
+    }
+  }
+}
+
+template <int BITS, int GPK>
+__global__ void __launch_bounds__(QG_THREADS, QG_CTAS_PER_SM) qlinear_stream_kernel(const QgParams p) {
+  constexpr int ROW_BYTES = QL_KB * BITS / 8;          // bytes of one weight row in one k-block: 32 or 64
+  constexpr int PACKED = QL_TILE_N * ROW_BYTES;
+  constexpr int HALF_BYTES = ROW_BYTES / 2;            // one 32-feature half of a row
+  constexpr int LANE_WORDS = BITS / 4;                 // 32-bit words holding the lane's 8 features of a half
+  constexpr int NT = QL_TILE_GROUP;
+  extern __shared__ __align__(128) uint8_t smem[];
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int S = p.stages;
+  const uint32_t unit_bytes = NT * p.record_bytes;
+  uint8_t* ring = smem;
+  float* xs = reinterpret_cast<float*>(smem + (size_t)S * unit_bytes);               // [kblocks][GPK][8]
+  uint64_t* full = reinterpret_cast<uint64_t*>(xs + (size_t)p.kblocks * GPK * 8);
+  uint64_t* empty = full + S;
+  const long long T = (long long)p.n_groups * p.kblocks, G = gridDim.x;
+  const long long R0 = T * blockIdx.x / G, R1 = T * (blockIdx.x + 1) / G;
+  const int n_units = (int)(R1 - R0);
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < S; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], QG_CONSUMER_WARPS); }
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  if (warp == QG_CONSUMER_WARPS) {
+    // ---- producer: the weights do not depend on the kernels before this one, so it never waits for them ----
+    if (lane == 0) {
+      RingPos rp;
+      int issued = 0;
+      bool ok = true;
+      const uint8_t* src = p.records + (size_t)R0 * unit_bytes;   // units are contiguous: [group][k-block][tile in group]
+      for (int i = 0; i < n_units; ++i, rp.advance(S), src += unit_bytes) {
+        if (!mbar_wait(&empty[rp.stage], rp.phase ^ 1, p.status, KC_DEV_QLINEAR | 0x11)) { ok = false; break; }
+        mbar_arrive_expect_tx(&full[rp.stage], unit_bytes);
+        bulk_g2s(ring + (size_t)rp.stage * unit_bytes, src, unit_bytes, &full[rp.stage]);
+        ++issued;
+      }
+      if (!ok) {
+        // gave up: the copies already issued still land in this CTA's shared memory; wait for them (bounded) before leaving
+        RingPos dp;
+        for (int i = 0; i < issued; ++i, dp.advance(S))
+          if (i >= issued - S) mbar_wait(&full[dp.stage], dp.phase, p.status, KC_DEV_QLINEAR | 0x12);
+      }
+    }
+  } else {
+    // ---- consumers ----
+    const int g = lane >> 2, t = lane & 3;
+    const int r0 = warp * 16 + g;                      // this lane's weight rows in each tile: r0 and r0 + 8
+    const bool x_live = g < p.M;
+    const bf16* xr = p.x + (size_t)(x_live ? g : 0) * p.ldx + 8 * t;
+    pdl_wait();   // x comes from the kernel before; the partials below may still be read by it
+    // sum_k x_k per (k-block, group half, activation row) for the k-blocks of this CTA's run
+    {
+      const int n_kb = n_units < p.kblocks ? n_units : p.kblocks;
+      for (int i = warp; i < n_kb; i += QG_CONSUMER_WARPS) {
+        const int kb = (int)((R0 + i) % p.kblocks);
+        float sh[2] = {0.f, 0.f};
+        if (x_live) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const uint4 v = *reinterpret_cast<const uint4*>(xr + (size_t)kb * QL_KB + 32 * h);
+            const float2 a = unpack_bf162(v.x), b = unpack_bf162(v.y), c = unpack_bf162(v.z), d = unpack_bf162(v.w);
+            sh[h] = ((a.x + a.y) + (b.x + b.y)) + ((c.x + c.y) + (d.x + d.y));
+          }
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          sh[h] += __shfl_xor_sync(0xffffffffu, sh[h], 1);
+          sh[h] += __shfl_xor_sync(0xffffffffu, sh[h], 2);
+        }
+        if (t == 0) {
+          if (GPK == 2) { xs[((size_t)kb * 2 + 0) * 8 + g] = sh[0]; xs[((size_t)kb * 2 + 1) * 8 + g] = sh[1]; }
+          else xs[(size_t)kb * 8 + g] = sh[0] + sh[1];
+        }
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"(QG_CONSUMER_WARPS * 32) : "memory");
+    }
+    float acc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    int grp = (int)(R0 / p.kblocks), kb = (int)(R0 % p.kblocks);
+    long long seg0 = R0;   // first unit of the current group's segment
+    bool ok = true;
+    RingPos rp;
+    auto flush = [&](long long seg_end) {
+      // acc[j][0], [1] = weight row r0 of tile j against activation rows 2t, 2t + 1; [2], [3] = row r0 + 8
+      const long long t_first = (long long)grp * p.kblocks, t_last = t_first + p.kblocks - 1;
+      const int c_first = (int)qg_owner(t_first, T, G);
+      const int piece = (int)blockIdx.x - c_first;
+      const int n_pieces = (int)qg_owner(t_last, T, G) - c_first + 1;
+      const bool closes = seg_end == t_last + 1;       // the CTA holding a group's last unit also clears its unused slots
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int n = (grp * NT + j) * QL_TILE_N + r0 + 8 * h;
+          if (n < p.N) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int m = 2 * t + e;
+              if (m < p.M) {
+                p.partial[((size_t)piece * p.M + m) * p.N + n] = acc[j][2 * h + e];
+                if (closes)
+                  for (int q = n_pieces; q < p.pieces; ++q) p.partial[((size_t)q * p.M + m) * p.N + n] = 0.f;
+              }
+            }
+          }
+        }
+        acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+      }
+    };
+    const uint32_t lane_off = (uint32_t)r0 * ROW_BYTES + t * (4 * LANE_WORDS);
+    const uint32_t sb_off = PACKED + (uint32_t)r0 * GPK * 4;
+    // the activation fragment and the row sums of a unit are fetched one unit ahead
+    uint4 xa[2], xa_next[2];
+    float2 xsum[GPK], xsum_next[GPK];
+    auto fetch_x = [&](int kbn, uint4 (&xv)[2], float2 (&sv)[GPK]) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        xv[h] = make_uint4(0, 0, 0, 0);
+        if (x_live) xv[h] = *reinterpret_cast<const uint4*>(xr + (size_t)kbn * QL_KB + 32 * h);
+      }
+#pragma unroll
+      for (int q = 0; q < GPK; ++q) sv[q] = *reinterpret_cast<const float2*>(xs + ((size_t)kbn * GPK + q) * 8 + 2 * t);
+    };
+    fetch_x(kb, xa_next, xsum_next);
+    for (int i = 0; i < n_units; ++i, rp.advance(S)) {
+      xa[0] = xa_next[0]; xa[1] = xa_next[1];
+#pragma unroll
+      for (int q = 0; q < GPK; ++q) xsum[q] = xsum_next[q];
+      if (i + 1 < n_units) fetch_x(kb + 1 == p.kblocks ? 0 : kb + 1, xa_next, xsum_next);
+      ok = __all_sync(0xffffffffu, mbar_wait(&full[rp.stage], rp.phase, p.status, KC_DEV_QLINEAR | 0x13));
+      if (!ok) break;
+      const uint8_t* unit = ring + (size_t)rp.stage * unit_bytes;
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        const uint8_t* rec = unit + (size_t)j * p.record_bytes;
+        uint32_t u[2][2][LANE_WORDS];   // [half][row r0 / r0 + 8][words]
+        uint32_t sbw[2][GPK];
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+            const uint8_t* src = rec + lane_off + r * 8 * ROW_BYTES + h * HALF_BYTES;
+            if (LANE_WORDS == 1) u[h][r][0] = *reinterpret_cast<const uint32_t*>(src);
+            else { const uint2 v = *reinterpret_cast<const uint2*>(src); u[h][r][0] = v.x; u[h][r][LANE_WORDS - 1] = v.y; }
+          }
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+#pragma unroll
+          for (int q = 0; q < GPK; ++q) sbw[r][q] = *reinterpret_cast<const uint32_t*>(rec + sb_off + r * 8 * GPK * 4 + q * 4);
+        float raw[2][4];   // one accumulator per 32-feature half: the two MMA chains are independent
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          raw[h][0] = raw[h][1] = raw[h][2] = raw[h][3] = 0.f;
+          uint32_t e0[4], e1[4];
+          qg_raw_pairs<BITS>(u[h][0], e0);
+          qg_raw_pairs<BITS>(u[h][1], e1);
+          mma_bf16_16816(raw[h], e0[0], e1[0], e0[2], e1[2], xa[h].x, xa[h].z);
+          mma_bf16_16816(raw[h], e0[1], e1[1], e0[3], e1[3], xa[h].y, xa[h].w);
+        }
+        if (GPK == 1) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) raw[0][c] += raw[1][c];
+        }
+#pragma unroll
+        for (int q = 0; q < GPK; ++q) {
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+            const float sc = __uint_as_float(sbw[r][q] << 16), bi = __uint_as_float(sbw[r][q] & 0xFFFF0000u);
+            const float bc = BITS == 4 ? fmaf(-128.f, sc, bi) : bi;   // the 128 every 4-bit q carries
+            acc[j][2 * r + 0] = fmaf(sc, raw[q][2 * r + 0], fmaf(bc, xsum[q].x, acc[j][2 * r + 0]));
+            acc[j][2 * r + 1] = fmaf(sc, raw[q][2 * r + 1], fmaf(bc, xsum[q].y, acc[j][2 * r + 1]));
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[rp.stage]);   // the unit has been read: its slot can refill
+      if (++kb == p.kblocks) {
+        flush(R0 + i + 1);
+        kb = 0; ++grp; seg0 = R0 + i + 1;
+      }
+    }
+    if (ok && seg0 < R1) flush(R1);
+  }
+}
+
+static int qg_groups(const QWeight& w) { return (w.n_tiles + QL_TILE_GROUP - 1) / QL_TILE_GROUP; }
+
+// Persistent CTAs of the weight-streaming lane: a function of the weight's shape and the SM count only.
+static int qg_ctas(const QWeight& w) {
+  const long long T = (long long)qg_groups(w) * w.kblocks;
+  // a run is at least QG_MIN_UNITS units, and long enough that a group's k-blocks spread over at most QG_MAX_PIECES
+  // runs (each piece is one more fp32 partial the consumer kernel has to read)
+  const long long run = std::max<long long>(QG_MIN_UNITS, (w.kblocks + QG_MAX_PIECES - 2) / (QG_MAX_PIECES - 1));
+  return (int)std::max<long long>(1, std::min<long long>(T / run, (long long)QG_CTAS_PER_SM * w.sm_count));
+}
+
+int qlinear_stream_pieces(const QWeight& w) {
+  const long long T = (long long)qg_groups(w) * w.kblocks, G = qg_ctas(w);
+  int most = 1;
+  for (int grp = 0; grp < qg_groups(w); ++grp) {
+    const long long first = (long long)grp * w.kblocks;
+    most = std::max(most, (int)(qg_owner(first + w.kblocks - 1, T, G) - qg_owner(first, T, G)) + 1);
+  }
+  return most;
+}
+
+template <int BITS, int GPK>
+static cudaError_t launch_stream(const QgParams& p, int ctas, size_t smem, cudaStream_t s) {
+  static DeviceOnce configured;
+  if (configured.first_on_current_device()) {
+    cudaError_t e = cudaFuncSetAttribute(qlinear_stream_kernel<BITS, GPK>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024);
+    if (e != cudaSuccess) { configured.forget_current_device(); return e; }
+  }
+  return launch_k(qlinear_stream_kernel<BITS, GPK>, dim3(ctas), dim3(QG_THREADS), smem, s, p);
+}
+
+cudaError_t qlinear_stream(const QWeight& w, const bf16* x, int ldx, int M, float* partial, uint32_t* status, cudaStream_t s) {
+  if (M < 1 || M > QL_STREAM_MAX_M || !partial) return cudaErrorInvalidValue;
+  if ((ldx & 7) || (reinterpret_cast<uintptr_t>(x) & 15)) return cudaErrorInvalidValue;   // 16-byte activation loads
+  QgParams p;
+  p.records = w.records; p.record_bytes = w.record_bytes;
+  p.N = w.N; p.n_groups = qg_groups(w); p.kblocks = w.kblocks; p.pieces = qlinear_stream_pieces(w);
+  const size_t unit_bytes = (size_t)QL_TILE_GROUP * w.record_bytes;
+  p.stages = (int)std::max<size_t>(2, std::min<size_t>(QG_MAX_STAGES, QG_RING_BYTES / unit_bytes));
+  p.x = x; p.ldx = ldx; p.M = M; p.partial = partial; p.status = status;
+  const size_t smem = (size_t)p.stages * unit_bytes + (size_t)w.kblocks * w.gpk * 8 * sizeof(float) + 2 * p.stages * sizeof(uint64_t);
+  if (smem > 110 * 1024) return cudaErrorInvalidValue;
+  const int ctas = qg_ctas(w);
+  if (w.bits == 4) return w.gpk == 2 ? launch_stream<4, 2>(p, ctas, smem, s) : launch_stream<4, 1>(p, ctas, smem, s);
+  return w.gpk == 2 ? launch_stream<8, 2>(p, ctas, smem, s) : launch_stream<8, 1>(p, ctas, smem, s);
+}
+
+// ---------------------------------------------------------------------------
 // Split-K reduction
 // ---------------------------------------------------------------------------
 

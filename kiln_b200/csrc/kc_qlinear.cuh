@@ -29,6 +29,7 @@ namespace kc {
 constexpr int QL_TILE_N = 128;  // output features per tile = UMMA M
 constexpr int QL_KB = 64;       // input features per k-block = one 128-byte swizzle row of bf16
 constexpr int QL_MAX_M = 512;   // activation rows per qlinear_umma call (one slab of the split-K workspace)
+constexpr int QL_STREAM_MAX_M = 8;  // activation rows the weight-streaming lane takes (the 8 columns of one mma.sync)
 constexpr int QL_TILE_GROUP = 4;  // tiles whose records are interleaved per k-block (the most one CTA owns)
 
 struct QWeight {
@@ -94,6 +95,12 @@ bool act_operand_init(ActOperand* op, const bf16* ptr, int rows, int K, const ch
 cudaError_t qlinear_umma(const QLinearLaunch& l, cudaStream_t s);
 // Kernels qlinear_umma issues for M rows of this weight.
 int qlinear_launches(const QWeight& w, int M);
+
+// The weight-streaming lane for at most QL_STREAM_MAX_M rows: x bf16 [M, ldx] against dequant(W)^T, left as fp32
+// partials [qlinear_stream_pieces(w)][M][N] that the caller's consumer kernel (or qlinear_reduce_splits) sums in index
+// order. MLX's row-vector arithmetic class: scale and bias are applied per group to fp32 sums of x q and of x.
+int qlinear_stream_pieces(const QWeight& w);
+cudaError_t qlinear_stream(const QWeight& w, const bf16* x, int ldx, int M, float* partial, uint32_t* status, cudaStream_t s);
 
 // out[m, n] = bf16(sum over splits of partial[s][m][n]) in split order.
 cudaError_t qlinear_reduce_splits(const float* partial, int splits, int M, int N, bf16* y, int ldy,

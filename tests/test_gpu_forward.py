@@ -278,6 +278,43 @@ def test_engine_pipelines_plain_decode_on_the_device(ctx):
     assert ctx.device_status() == 0
 
 
+@pytest.mark.parametrize("name", ["tiny-llama", "tiny-qwen2", "tiny-gemma2", "tiny-llama-h2048"])
+def test_stream_lane_decode_logits_match_oracle(ctx, name):
+    """A model with the weight-streaming lane on (kc_model_set_stream_lane): decode forwards of 1..8 rows against the
+    oracle, and kc_draft_chain == the same steps taken one by one."""
+    cfg, model, kv, omodel, okv = load(ctx, name)
+    model.set_stream_lane(True)
+    ps = prompts(cfg, [21, 9, 30], 8)
+    tables = [[3, 8], [5], [1, 2]]
+    seqs = [api.SeqStep(len(p), 0, 1, t) for p, t in zip(ps, tables)]
+    batch = api.StepBatch(sum(ps, []), seqs)
+    O.set_weight_class(1)
+    omodel.forward_step(batch, okv)
+    model.forward_step(batch, kv)          # 60 rows: the tensor-core lane
+    g = torch.Generator().manual_seed(9)
+    ids = torch.randint(0, cfg.vocab_size, (3,), generator=g).tolist()
+    dec = api.StepBatch(ids, [api.SeqStep(1, len(p), 1, t) for p, t in zip(ps, tables)])
+    O.set_weight_class(0)                  # the streaming lane is of the row-vector class
+    want = omodel.forward_step(dec, okv)
+    got = model.forward_step(dec, kv)      # 3 rows: the streaming lane
+    ctx.sync()
+    assert parity(f"{name} stream-lane decode logits vs oracle", got.cpu(), want, BAR.get(name, 2e-2))
+    first = int(api.greedy_rows(ctx, got.clone(), normalize=False)[0])
+    chain = model.draft_chain(kv, first, len(ps[0]) + 1, tables[0], 4)
+    tok, step = first, []
+    kv2 = api.PagedKv(ctx, model.kv_spec(64, BS))
+    model.forward_step(batch, kv2)
+    model.forward_step(dec, kv2)
+    for j in range(4):
+        lg = model.forward_step(api.StepBatch([tok], [api.SeqStep(1, len(ps[0]) + 1 + j, 1, tables[0])]), kv2)
+        ctx.sync()
+        tok = int(api.greedy_rows(ctx, lg.clone(), normalize=False)[0])
+        step.append(tok)
+    assert chain == step
+    assert ctx.device_status() == 0
+    model.set_stream_lane(False)
+
+
 def test_invalid_batches_are_rejected(ctx):
     """Validation mirrors nn.rs:1309-1337; errors come back as status + message, never an abort."""
     cfg, model, kv, _, _ = load(ctx, "tiny-llama")

@@ -73,3 +73,62 @@ def test_rows_do_not_depend_on_batch_width(ctx, n, k, bits, group):
         for r, want in ref_rows.items():
             if r < m:
                 assert torch.equal(y[r:r + 1].view(torch.int16), want.view(torch.int16)), f"row {r} differs at M={m}"
+
+
+STREAM_CASES = [
+    # (N, K, bits, group, M): the weight-streaming lane, at most 8 rows
+    (256, 256, 4, 64, 1),          # one k-split
+    (200, 512, 4, 64, 5),          # N not a multiple of the 128-row tile
+    (384, 1024, 4, 32, 8),         # two groups per k-block
+    (256, 1024, 4, 128, 3),        # a group spans two k-blocks
+    (256, 512, 8, 32, 8),          # 8-bit
+    (256, 448, 8, 64, 7),          # K = 7 k-blocks: uneven k-splits
+    (1024, 4096, 4, 64, 6),        # the 8B attention-output shape: several pieces per tile
+    (28672, 4096, 4, 64, 8),       # the 8B gate_up shape
+    (4099, 2048, 4, 64, 2),        # a ragged last tile
+    (640, 14336, 4, 64, 4),        # the 8B down-projection depth: a tile's k-blocks spread over many CTAs
+    (128256, 2048, 4, 64, 1),      # the 1B head: runs that cross two tile boundaries
+]
+
+
+@pytest.mark.parametrize("n,k,bits,group,m", STREAM_CASES)
+def test_stream_lane_matches_oracle(ctx, n, k, bits, group, m):
+    """kc_quantized_matmul_stream is of MLX's row-vector class (scale and bias applied per group to fp32 sums of
+    x q and of x), the oracle's class 0; against the tensor-core lane (weights rounded to bf16 first) the distance is
+    that of the two classes."""
+    p, s, b = make(n, k, bits, group, 5)
+    x = acts(m, k, 6)
+    O.set_weight_class(0)
+    want = O.quantized_matmul(x, p, s, b, bits, group)
+    qw = api.QuantizedWeight(ctx, p.cuda(), s.cuda(), b.cuda(), bits, group)
+    got = qw.matmul_stream(x.cuda()).cpu()
+    assert parity(f"stream lane {n}x{k} w{bits}g{group} rows {m}", got, want, MAX_ABS, MIN_COS)
+    tensor = qw.matmul(x.cuda()).cpu()
+    # two arithmetic classes apart: the distance is printed, and held to what the oracle's own two classes differ by on
+    # the same inputs (plus one bf16 spacing of the largest value for the kernels' accumulation orders)
+    O.set_weight_class(1)
+    want_tile = O.quantized_matmul(x, p, s, b, bits, group)
+    O.set_weight_class(0)
+    class_gap = float((want.float() - want_tile.float()).abs().max())
+    spacing = 2.0 ** (torch.floor(torch.log2(want.float().abs().max())) - 7)
+    parity(f"stream lane vs tensor lane {n}x{k} w{bits}g{group} rows {m}", got, tensor, 1e9, MIN_COS)
+    gap = float((got.float() - tensor.float()).abs().max())
+    print(f"oracle class 0 vs class 1: max-abs {class_gap:.4g}; lanes: {gap:.4g}")
+    assert gap <= class_gap + 2 * float(spacing)
+    assert cosine(got, tensor) >= MIN_COS
+    assert ctx.device_status() == 0
+
+
+def test_stream_lane_rows_do_not_depend_on_row_count(ctx):
+    """Within the lane a row's bits do not depend on how many rows ride the call (1..8)."""
+    p, s, b = make(1024, 4096, 4, 64, 7)
+    qw = api.QuantizedWeight(ctx, p.cuda(), s.cuda(), b.cuda(), 4, 64)
+    x = acts(8, 4096, 8).cuda()
+    full = qw.matmul_stream(x).cpu()
+    for m in (1, 2, 3, 5, 7):
+        y = qw.matmul_stream(x[:m]).cpu()
+        assert torch.equal(y.view(torch.int16), full[:m].view(torch.int16))
+    one = qw.matmul_stream(x[5:6]).cpu()
+    assert torch.equal(one.view(torch.int16), full[5:6].view(torch.int16))
+    with pytest.raises(api.KcError, match="m = 9"):
+        qw.matmul_stream(acts(9, 4096, 9).cuda())
