@@ -220,6 +220,15 @@ class Workload:
         max_step = self.prefill_chunk + self.batch * (self.k + 1)
         self.model = api.CudaModel(self.ctx, cfg, ck, max_step_tokens=max_step, max_step_seqs=self.batch + 1,
                                    tp_rank=rank if self.tp > 1 else 0, tp_world=self.tp)
+        self.tp_exchange = "none"
+        if self.tp > 1:
+            self.tp_exchange = os.environ.get("KILN_TP_EXCHANGE", "peer")
+            if self.tp_exchange == "peer":   # the ranks' outputs are read in place over NVLink instead of all-gathered
+                def everyone(b):
+                    out = [None] * world
+                    dist.all_gather_object(out, b)
+                    return out
+                self.model.tp_connect(everyone)
         self.cpu_sample = None
         if keep_cpu_sample:   # the checkpoint on the host, for the CPU baseline (packed: about an eighth of bf16)
             self.cpu_sample = {n: t.cpu() for n, t in ck.items()}
@@ -254,48 +263,42 @@ class Workload:
         self.ctx.close()
 
     def run_off(self):
-        """Phase 1: speculation off, to completion. Returns the greedy continuation of every prompt. Plain decode is
-        the path every request takes when speculation stands down (engine.rs:1428-1475); the first half of the
-        generation runs it pipelined (step N + 1 launched from step N's unread tokens), the second half synchronously,
-        and `plain_decode` keeps the time per full-batch decode step of each (end of one engine step to the end of the
-        next, host work included)."""
+        """Phase 1: speculation off, to completion. Returns the greedy continuation of every prompt."""
+        arrivals = [self.engine.submit(p, self.gen) for p in self.prompts]
+        out = self.engine.run_to_completion(arrivals)
+        return [out[a][0] for a in arrivals]
+
+    def plain_decode_pass(self, steps: int = 40):
+        """Plain decode at the full batch — the path every request takes when speculation stands down
+        (engine.rs:1428-1475). Runs after run_off, so every prompt is a prefix-cache hit and the batch is full from the
+        first iteration; `steps` full-batch decode steps pipelined (step N + 1 launched from step N's unread tokens),
+        then as many synchronous, each timed from the end of one engine step to the end of the next (host work
+        included); the requests are cancelled afterwards."""
         eng = self.engine
         arrivals = [eng.submit(p, self.gen) for p in self.prompts]
-        out = {a: [] for a in arrivals}
-        done = set()
         spans = {True: [], False: []}
-        pipelined, last_end = True, None
+        for pipelined in (True, False):
+            eng.set_pipelined(pipelined)
+            last_end, guard = None, 0
+            while len(spans[pipelined]) < steps and guard < 20 * steps:
+                guard += 1
+                eng.step()
+                now = time.perf_counter()
+                emitted = sum(len(eng.take_output(a)[0]) for a in arrivals)
+                if last_end is not None and emitted == len(arrivals):
+                    spans[pipelined].append((now - last_end) * 1e3)
+                last_end = time.perf_counter()
         eng.set_pipelined(True)
-        for _ in range(1000000):
-            if len(done) == len(arrivals):
-                break
-            eng.step()
-            now = time.perf_counter()
-            emitted = 0
-            for a in arrivals:
-                if a in done:
-                    continue
-                toks, kind = eng.take_output(a)
-                out[a] += toks
-                emitted += len(toks)
-                if kind is not None:
-                    done.add(a)
-            if last_end is not None and emitted == len(arrivals) and not done:
-                spans[pipelined].append((now - last_end) * 1e3)
-            last_end = time.perf_counter()
-            if pipelined and len(out[arrivals[0]]) >= self.gen // 2:
-                pipelined = False
-                eng.set_pipelined(False)
-                last_end = None
-        eng.set_pipelined(True)
+        for a in arrivals:
+            eng.cancel(a)
+        eng.run_to_completion(arrivals)
         med = lambda v: float(statistics.median(v[2:])) if len(v) > 4 else None
         p_ms, s_ms = med(spans[True]), med(spans[False])
-        self.plain_decode = {"pipelined_ms_per_step": p_ms, "synchronous_ms_per_step": s_ms,
-                             "steps_timed": [max(0, len(spans[True]) - 2), max(0, len(spans[False]) - 2)],
-                             "pipelined_tok_s": len(arrivals) / (p_ms * 1e-3) if p_ms else None,
-                             "synchronous_tok_s": len(arrivals) / (s_ms * 1e-3) if s_ms else None,
-                             "rows_per_step": len(arrivals)}
-        return [out[a] for a in arrivals]
+        return {"pipelined_ms_per_step": p_ms, "synchronous_ms_per_step": s_ms,
+                "steps_timed": [max(0, len(spans[True]) - 2), max(0, len(spans[False]) - 2)],
+                "pipelined_tok_s": len(arrivals) / (p_ms * 1e-3) if p_ms else None,
+                "synchronous_tok_s": len(arrivals) / (s_ms * 1e-3) if s_ms else None,
+                "rows_per_step": len(arrivals)}
 
     def submit_on(self, base, p_accept=0.7, seed=0):
         """Phase 2 submission: scripted drafter with injected acceptance; every prompt is a prefix-cache hit."""
@@ -519,8 +522,11 @@ def tp_record(rank: int, local_rank: int, world: int, dist, barrier) -> dict:
            "spec_on_equals_off": chk["spec_on_equals_off"]["identical"], "sequences_checked": chk["spec_on_equals_off"]["sequences_checked"],
            "speculation_on_twice_equal": chk["speculation_on_twice_equal"], "all_ranks_ok": tot.all_identical,
            "device_status_max_over_ranks": int(st[0]),
-           "exchange": "all-gather of every rank's bf16 [rows, hidden] sublayer output after o_proj and down_proj (NCCL), summed "
-                       "in rank order in fp32 by the consumer kernel",
+           "exchange": ("peer memory: every rank's bf16 [rows, hidden] sublayer output after o_proj and down_proj is read in place over "
+                        "NVLink by the consumer kernel (flag per rank and exchange, plain peer loads) and summed in rank order in fp32"
+                        if w.tp_exchange == "peer" else
+                        "all-gather of every rank's bf16 [rows, hidden] sublayer output after o_proj and down_proj (NCCL), summed "
+                        "in rank order in fp32 by the consumer kernel"),
            "peer_bytes_received_per_rank_per_step": int(2 * cfg.num_hidden_layers * (world - 1) * rows * cfg.hidden_size * 2),
            "seconds": round(time.time() - t0, 1)}
     w.close()
@@ -764,6 +770,7 @@ def main():
     t0 = time.time()
     base = w.run_off()
     off_s = time.time() - t0
+    plain_decode = w.plain_decode_pass()
 
     def barrier():
         if dist:
@@ -856,7 +863,7 @@ def main():
                        "tokens_per_step": tokens / steps / (1 if main_tp > 1 else world)},
         "spec_on_equals_off": {"sequences_checked": checked, "identical": bool(identical)},
         "setup_s": {"build_model": round(build_s, 1), "speculation_off_run": round(off_s, 1)},
-        "plain_decode": getattr(w, "plain_decode", None),
+        "plain_decode": plain_decode,
     }
     if per_rank:
         line["per_rank"] = per_rank

@@ -374,6 +374,19 @@ KC_API int kc_rope_kv_write(kc_ctx_t ctx, kc_kv_t kv, int32_t layer, const void*
  * rounding) by the next kernel. unique_id: the 128 bytes of an ncclUniqueId
  * from rank 0. */
 KC_API int kc_tp_init(kc_ctx_t ctx, const void* unique_id, int32_t rank, int32_t world);
+
+/* The tensor-parallel exchange over peer memory instead of NCCL. After kc_model_load on every rank (one process per
+ * GPU): kc_tp_export writes this rank's KC_TP_EXPORT_BYTES of inter-process memory handles (its two output buffers
+ * and its flag array); the caller brings every rank's bytes to every rank (rank order, world x KC_TP_EXPORT_BYTES)
+ * and passes them to kc_tp_attach, which maps the peers' buffers. From then on the model's o_proj / down_proj
+ * outputs are not copied at all: a one-warp kernel publishes "exchange e done" into every rank's flag array and the
+ * consumer kernel (residual add + RMSNorm) reads every rank's rows where they were written, in rank order — plain
+ * peer loads over NVLink, no multicast. The consumer's wait for the flags is bounded like every wait of the library
+ * (KC_ERR_TIMEOUT at the next synchronisation if a rank never publishes). Without these two calls the exchange is an
+ * NCCL all-gather. All ranks must run the same sequence of forwards. */
+#define KC_TP_EXPORT_BYTES 192
+KC_API int kc_tp_export(kc_model_t model, void* handles_out);
+KC_API int kc_tp_attach(kc_model_t model, const void* handles_all);
 KC_API int kc_tp_unique_id(void* unique_id_out_128);
 
 #ifdef __cplusplus

@@ -423,6 +423,21 @@ class CudaModel:
                                      int(b.shape[0]), int(gamma), out.ctypes.data_as(C.POINTER(C.c_uint32))))
         return [int(x) for x in out]
 
+    TP_EXPORT_BYTES = 192
+
+    def tp_connect(self, all_gather) -> None:
+        """Switches this tensor-parallel slice's exchange from NCCL to peer memory (kc_tp_export / kc_tp_attach).
+        ``all_gather(b: bytes) -> list[bytes]`` must return every rank's bytes in rank order (for instance through
+        torch.distributed.all_gather_object); every rank calls this at the same point."""
+        buf = (C.c_uint8 * self.TP_EXPORT_BYTES)()
+        check(L.lib().kc_tp_export(self._h, buf))
+        everyone = all_gather(bytes(buf))
+        blob = b"".join(everyone)
+        if len(blob) != self.TP_EXPORT_BYTES * len(everyone):
+            raise ValueError("tp_connect: every rank must contribute TP_EXPORT_BYTES bytes")
+        arr = (C.c_uint8 * len(blob)).from_buffer_copy(blob)
+        check(L.lib().kc_tp_attach(self._h, arr))
+
     def set_stream_lane(self, on: bool = True) -> None:
         """Forwards of at most 8 rows take the weight-streaming kernels (kc_model_set_stream_lane): for draft models."""
         check(L.lib().kc_model_set_stream_lane(self._h, int(on)))

@@ -179,6 +179,15 @@ struct kc_model {
   float* partial = nullptr; size_t partial_bytes = 0;
   float* attn_ws = nullptr; size_t attn_ws_bytes = 0;
   float* tp_buf = nullptr;             // fp32 staging for the tensor-parallel all-reduce
+  // Tensor-parallel exchange over peer memory (kc_tp_export / kc_tp_attach): the o_proj / down_proj output of exchange e
+  // goes to tp_out[e & 1]; tp_flags[r] = the last exchange rank r has published. peer_* = every rank's buffers as
+  // mapped into this process (this rank's own pointers at index tp_rank).
+  bf16* tp_out[2] = {nullptr, nullptr};
+  uint32_t* tp_flags = nullptr;
+  bf16* peer_out[2][KC_MAX_TP] = {};
+  uint32_t* peer_flags[KC_MAX_TP] = {};
+  bool tp_p2p = false;
+  uint32_t tp_epoch = 0;
   // step metadata
   uint8_t* meta_dev = nullptr; size_t meta_cap = 0;
   static constexpr int kStaging = 4;
@@ -735,6 +744,13 @@ void free_model(kc_model* m) {
   cudaFree(m->h); cudaFree(m->normed); cudaFree(m->qkv); cudaFree(m->q_rot); cudaFree(m->attn); cudaFree(m->proj); cudaFree(m->proj_ranks);
   cudaFree(m->gu); cudaFree(m->act); cudaFree(m->hs); cudaFree(m->logits); cudaFree(m->partial); cudaFree(m->attn_ws);
   cudaFree(m->tp_buf);
+  if (m->tp_p2p)
+    for (int r = 0; r < m->d.tp_world; ++r) {
+      if (r == m->d.tp_rank) continue;
+      for (int b = 0; b < 2; ++b) if (m->peer_out[b][r]) cudaIpcCloseMemHandle(m->peer_out[b][r]);
+      if (m->peer_flags[r]) cudaIpcCloseMemHandle(m->peer_flags[r]);
+    }
+  cudaFree(m->tp_out[0]); cudaFree(m->tp_out[1]); cudaFree(m->tp_flags);
   cudaFree(m->meta_dev);
   for (int i = 0; i < kc_model::kStaging; ++i) {
     if (m->meta_host[i]) cudaFreeHost(m->meta_host[i]);
@@ -897,7 +913,13 @@ extern "C" int kc_model_load(kc_ctx_t c, const kc_model_desc* desc, const kc_ten
     if (need) { cudaError_t e = cudaMalloc(&m->partial, need); if (e != cudaSuccess) LOAD_FAIL(fail(KC_ERR_OOM, "split-K workspace: %s", cudaGetErrorString(e))); }
     m->partial_bytes = need;
   }
-  if (tp > 1) { cudaError_t e = cudaMalloc(&m->tp_buf, R * H * sizeof(float)); if (e != cudaSuccess) LOAD_FAIL(fail(KC_ERR_OOM, "tp buffer")); }
+  if (tp > 1) {
+    cudaError_t e = cudaMalloc(&m->tp_buf, R * H * sizeof(float));
+    for (int b = 0; b < 2 && e == cudaSuccess; ++b) e = cudaMalloc(&m->tp_out[b], R * H * sizeof(bf16));
+    if (e == cudaSuccess) e = cudaMalloc(&m->tp_flags, KC_MAX_TP * sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMemsetAsync(m->tp_flags, 0, KC_MAX_TP * sizeof(uint32_t), c->stream);
+    if (e != cudaSuccess) LOAD_FAIL(fail(KC_ERR_OOM, "tensor-parallel buffers: %s", cudaGetErrorString(e)));
+  }
   {
     cudaError_t e = cudaSuccess;
     if (e == cudaSuccess) e = cudaMalloc(&m->row_tokens, R * 4);
@@ -945,6 +967,8 @@ extern "C" int kc_envelope(kc_model_t m, int32_t* max_gamma, int32_t* max_key_le
 // ---------------------------------------------------------------------------
 // step metadata
 // ---------------------------------------------------------------------------
+
+constexpr int KC_TP_HANDLES = 3;   // per rank: tp_out[0], tp_out[1], tp_flags
 
 namespace {
 
@@ -1114,6 +1138,32 @@ int tp_allgather(kc_model* m, const bf16* local, bf16* out, int n) {
   return KC_OK;
 }
 
+// The exchange after o_proj / down_proj. With peer memory attached (kc_tp_attach) nothing is copied: the GEMM has
+// written this rank's rows to tp_out[e & 1], a one-warp kernel publishes `e` into every rank's flag array, and the
+// consumer kernel reads every rank's rows where they lie, in rank order. Buffer e & 1 is written again at exchange
+// e + 2, which this rank's GEMM reaches only after its consumer of e + 1 has seen every peer's flag e + 1, i.e. after
+// every peer has finished reading e. Otherwise: NCCL all-gather into proj_ranks.
+int tp_exchange(kc_model* m, int n, SublayerOut* so) {
+  kc_ctx* c = m->ctx;
+  const int H = m->d.hidden_size;
+  if (m->tp_p2p) {
+    const uint32_t e = m->tp_epoch;   // set by tp_out_buffer for this exchange
+    LAUNCH(c, KC_PROF_ROWWISE, 1, launch_tp_signal(m->peer_flags, m->d.tp_world, m->d.tp_rank, e, c->stream));
+    *so = SublayerOut::of_peers(m->peer_out[e & 1], m->d.tp_world, H, m->tp_flags, e, c->status);
+    return KC_OK;
+  }
+  int rc = tp_allgather(m, m->proj, m->proj_ranks, n);
+  if (rc) return rc;
+  *so = SublayerOut::of_ranks(m->proj_ranks, m->d.tp_world, (size_t)n, H);
+  return KC_OK;
+}
+// Where the GEMM of the next exchange writes this rank's rows.
+bf16* tp_out_buffer(kc_model* m) {
+  if (!m->tp_p2p) return m->proj;
+  m->tp_epoch += 1;
+  return m->tp_out[m->tp_epoch & 1];
+}
+
 // The forward proper. tokens_dev: n u32 on the device (normally the metadata arena's copy).
 int run_forward(kc_model* m, kc_kv* kv, const uint32_t* tokens_dev, const StepPlan& p, bool want_logits) {
   kc_ctx* c = m->ctx;
@@ -1138,11 +1188,8 @@ int run_forward(kc_model* m, kc_kv* kv, const uint32_t* tokens_dev, const StepPl
     AttnParams a = attn_params(m, kv, p, l, m->q_rot, m->attn, m->attn_scale, gemma ? d.attn_logit_softcapping : 0.f, window, m->Hq);
     LAUNCH(c, KC_PROF_ATTN, 2, paged_attention(kv->map, a, D, p.tokens_per_item, p.n_work, p.max_chunks, n, c->stream));
     if (stream) RC(run_stream(c, L.o, m->attn, n, m->proj, H, m->partial, &so));
-    else RC(run_qlinear(c, L.o, m->op_attn, n, m->proj, H, m->partial, d.tp_world > 1 ? nullptr : &so));
-    if (d.tp_world > 1) {
-      if ((rc = tp_allgather(m, m->proj, m->proj_ranks, n))) return rc;
-      so = SublayerOut::of_ranks(m->proj_ranks, d.tp_world, (size_t)n, H);
-    }
+    else RC(run_qlinear(c, L.o, m->op_attn, n, d.tp_world > 1 ? tp_out_buffer(m) : m->proj, H, m->partial, d.tp_world > 1 ? nullptr : &so));
+    if (d.tp_world > 1 && (rc = tp_exchange(m, n, &so))) return rc;
     if (gemma) LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, so, L.post_attn_ln, L.pre_ffw_ln, nullptr, n, H, d.rms_norm_eps, m->h, m->normed, c->stream));
     else LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, so, nullptr, L.post_attn_ln, nullptr, n, H, d.rms_norm_eps, m->h, m->normed, c->stream));
     if (stream) {
@@ -1152,12 +1199,9 @@ int run_forward(kc_model* m, kc_kv* kv, const uint32_t* tokens_dev, const StepPl
       RC(run_stream(c, L.down, m->act, n, m->proj, H, m->partial, &so));
     } else {
       RC(run_gated(c, L.gate_up, m->op_normed, n, m->gu, m->F, gemma ? 1 : 0, m->glu_interleaved, m->act, m->partial));
-      RC(run_qlinear(c, L.down, m->op_act, n, m->proj, H, m->partial, d.tp_world > 1 ? nullptr : &so));
+      RC(run_qlinear(c, L.down, m->op_act, n, d.tp_world > 1 ? tp_out_buffer(m) : m->proj, H, m->partial, d.tp_world > 1 ? nullptr : &so));
     }
-    if (d.tp_world > 1) {
-      if ((rc = tp_allgather(m, m->proj, m->proj_ranks, n))) return rc;
-      so = SublayerOut::of_ranks(m->proj_ranks, d.tp_world, (size_t)n, H);
-    }
+    if (d.tp_world > 1 && (rc = tp_exchange(m, n, &so))) return rc;
     const bf16* next_ln = l + 1 < d.num_layers ? m->layers[l + 1].input_ln : nullptr;
     LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, so, gemma ? L.post_ffw_ln : nullptr, next_ln, nullptr, n, H, d.rms_norm_eps, m->h, m->normed, c->stream));
   }
@@ -1173,6 +1217,51 @@ int run_forward(kc_model* m, kc_kv* kv, const uint32_t* tokens_dev, const StepPl
 }
 
 }  // namespace
+
+extern "C" int kc_tp_export(kc_model_t m, void* handles_out) {
+  if (!m || !handles_out) return fail(KC_ERR_INVALID, "kc_tp_export: NULL argument");
+  if (m->d.tp_world < 2) return fail(KC_ERR_INVALID, "kc_tp_export: the model is not a tensor-parallel slice");
+  CK(cudaSetDevice(m->ctx->device));
+  cudaIpcMemHandle_t* h = reinterpret_cast<cudaIpcMemHandle_t*>(handles_out);
+  CK(cudaIpcGetMemHandle(&h[0], m->tp_out[0]));
+  CK(cudaIpcGetMemHandle(&h[1], m->tp_out[1]));
+  CK(cudaIpcGetMemHandle(&h[2], m->tp_flags));
+  return KC_OK;
+}
+
+extern "C" int kc_tp_attach(kc_model_t m, const void* handles_all) {
+  if (!m || !handles_all) return fail(KC_ERR_INVALID, "kc_tp_attach: NULL argument");
+  const int W = m->d.tp_world, me = m->d.tp_rank;
+  if (W < 2 || W > KC_MAX_TP) return fail(KC_ERR_INVALID, "kc_tp_attach: world %d (2..%d)", W, KC_MAX_TP);
+  if (m->tp_p2p) return fail(KC_ERR_INVALID, "kc_tp_attach: peers are already attached");
+  CK(cudaSetDevice(m->ctx->device));
+  CK(cudaStreamSynchronize(m->ctx->stream));
+  const cudaIpcMemHandle_t* h = reinterpret_cast<const cudaIpcMemHandle_t*>(handles_all);
+  for (int r = 0; r < W; ++r) {
+    if (r == me) {
+      m->peer_out[0][r] = m->tp_out[0]; m->peer_out[1][r] = m->tp_out[1]; m->peer_flags[r] = m->tp_flags;
+      continue;
+    }
+    void* p[3] = {nullptr, nullptr, nullptr};
+    for (int k = 0; k < 3; ++k) {
+      cudaError_t e = cudaIpcOpenMemHandle(&p[k], h[r * KC_TP_HANDLES + k], cudaIpcMemLazyEnablePeerAccess);
+      if (e != cudaSuccess) {
+        for (int j = 0; j < k; ++j) cudaIpcCloseMemHandle(p[j]);
+        for (int q = 0; q < r; ++q) {
+          if (q == me) continue;
+          cudaIpcCloseMemHandle(m->peer_out[0][q]); cudaIpcCloseMemHandle(m->peer_out[1][q]); cudaIpcCloseMemHandle(m->peer_flags[q]);
+          m->peer_out[0][q] = m->peer_out[1][q] = nullptr; m->peer_flags[q] = nullptr;
+        }
+        cudaGetLastError();
+        return fail(KC_ERR_CUDA, "kc_tp_attach: cannot map rank %d's buffer %d: %s", r, k, cudaGetErrorString(e));
+      }
+    }
+    m->peer_out[0][r] = (bf16*)p[0]; m->peer_out[1][r] = (bf16*)p[1]; m->peer_flags[r] = (uint32_t*)p[2];
+  }
+  m->tp_p2p = true;
+  m->tp_epoch = 0;
+  return KC_OK;
+}
 
 extern "C" int kc_model_set_stream_lane(kc_model_t m, int32_t on) {
   if (!m) return fail(KC_ERR_INVALID, "kc_model_set_stream_lane: model is NULL");

@@ -28,6 +28,7 @@ typedef __nv_bfloat162 bf162;
 enum : uint32_t {
   KC_DEV_QLINEAR = 0x100,
   KC_DEV_ATTN = 0x200,
+  KC_DEV_TP = 0x300,
 };
 
 constexpr unsigned long long KC_SPIN_LIMIT_NS = 1500ull * 1000ull * 1000ull;  // 1.5 s

@@ -64,7 +64,38 @@ struct RowSource {
   const bf16* rank_y;   // per-rank bf16 form [ranks][rows][ld], or null
   int ranks;
   size_t rank_stride;
+  const bf16* peer_y[KC_MAX_TP];   // per-rank bf16 [rows][ld] in each rank's own memory (peer loads), peers > 0
+  int peers;
+  const uint32_t* flags;           // this rank's flag array: flags[r] >= epoch once rank r's output is complete
+  uint32_t epoch;
+  uint32_t* status;
 };
+
+// Waits until every tensor-parallel rank has published the output of exchange `epoch`. The flags live in this GPU's
+// own memory (the peers store into them), so the poll is local. Bounded: after the limit the status word gets
+// KC_DEV_TP | 1 and the kernel goes on (its result is then not valid; the host sees the status at its next
+// synchronisation). Every thread of the CTA must call it.
+__device__ __forceinline__ void tp_wait(const RowSource& s) {
+  if ((int)threadIdx.x < s.peers) {
+    const uint32_t* f = s.flags + threadIdx.x;
+    auto ready = [&]() {
+      uint32_t v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+      return (int32_t)(v - s.epoch) >= 0;
+    };
+    if (!ready()) {
+      const unsigned long long t0 = globaltimer_ns();
+      uint32_t spins = 0;
+      while (!ready()) {
+        if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > KC_SPIN_LIMIT_NS) {
+          if (s.status) atomicOr(s.status, KC_DEV_TP | 1u);
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+}
 __device__ __forceinline__ void load8(const RowSource& s, size_t row, int col, float (&v)[8]) {
   if (s.part) {
     const float* p0 = s.part + row * s.ld + col;
@@ -90,6 +121,22 @@ __device__ __forceinline__ void load8(const RowSource& s, size_t row, int col, f
     }
     v[0] = bf16_round(a.x); v[1] = bf16_round(a.y); v[2] = bf16_round(a.z); v[3] = bf16_round(a.w);
     v[4] = bf16_round(b.x); v[5] = bf16_round(b.y); v[6] = bf16_round(b.z); v[7] = bf16_round(b.w);
+  } else if (s.peers) {
+    // rank order, fp32, one rounding; the peers' rows are read where they were written (NVLink loads, not cached here)
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    uint4 u[KC_MAX_TP];
+#pragma unroll
+    for (int r = 0; r < KC_MAX_TP; ++r)
+      if (r < s.peers) u[r] = __ldcv(reinterpret_cast<const uint4*>(s.peer_y[r] + row * s.ld + col));
+#pragma unroll
+    for (int r = 0; r < KC_MAX_TP; ++r) {
+      if (r < s.peers) {
+        const float2 a = unpack_bf162(u[r].x), b = unpack_bf162(u[r].y), c = unpack_bf162(u[r].z), d = unpack_bf162(u[r].w);
+        acc[0] += a.x; acc[1] += a.y; acc[2] += b.x; acc[3] += b.y; acc[4] += c.x; acc[5] += c.y; acc[6] += d.x; acc[7] += d.y;
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v[k] = bf16_round(acc[k]);
   } else if (s.rank_y) {
     // rank order, fp32, one rounding: the same bits whatever collective moved the per-rank outputs here
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -128,14 +175,17 @@ __global__ void __launch_bounds__(256)
 add_rmsnorm_kernel(const bf16* __restrict__ x, RowSource y, const bf16* __restrict__ w_pre,
                    const bf16* __restrict__ w_out, const int32_t* __restrict__ row_map, int H, float eps,
                    bf16* __restrict__ h_out, bf16* __restrict__ normed) {
-  pdl_launch_dependents();
+  // with peer inputs the kernels after this one are released only once the peers' data is here: nothing of the next
+  // kernel sits resident, counting down its own bounded waits, while this one waits for another GPU
+  if (!y.peers) pdl_launch_dependents();
   pdl_wait();
+  if (y.peers) { tp_wait(y); pdl_launch_dependents(); }
   extern __shared__ float srow[];   // H floats
   __shared__ float red[32];
   const int row = blockIdx.x;
   const size_t src = row_map ? row_map[row] : row;
   const bf16* xr = x + src * H;
-  const bool has_y = y.y || y.part || y.rank_y;
+  const bool has_y = y.y || y.part || y.rank_y || y.peers;
   float ss = 0.f;
   if (has_y && w_pre) {
     for (int i = threadIdx.x * 8; i < H; i += blockDim.x * 8) {
@@ -198,14 +248,15 @@ __global__ void __launch_bounds__(256)
 add_rmsnorm_reg_kernel(const bf16* __restrict__ x, RowSource y, const bf16* __restrict__ w_out,
                        const int32_t* __restrict__ row_map, float eps, bf16* __restrict__ h_out,
                        bf16* __restrict__ normed) {
-  pdl_launch_dependents();
+  if (!y.peers) pdl_launch_dependents();
   pdl_wait();
+  if (y.peers) { tp_wait(y); pdl_launch_dependents(); }
   constexpr int H = 2048 * CPT;
   __shared__ float red[32];
   const int row = blockIdx.x;
   const size_t src = row_map ? row_map[row] : row;
   const bf16* xr = x + src * H;
-  const bool has_y = y.y || y.part || y.rank_y;
+  const bool has_y = y.y || y.part || y.rank_y || y.peers;
   float v[CPT][8];
   uint4 xraw[CPT];
 #pragma unroll
@@ -382,6 +433,19 @@ __global__ void __launch_bounds__(256) glu_from_kernel(const RowSource gu, int n
   }
 }
 
+// Publishes "this rank's output of exchange `epoch` is complete" to every rank (its own flag array included). The
+// kernel follows the producing GEMM on the stream; the GEMM's stores are in this GPU's L2, where the peers' loads
+// are served, once it has finished.
+struct TpFlagPtrs { uint32_t* p[KC_MAX_TP]; };
+__global__ void tp_signal_kernel(TpFlagPtrs flags, int world, int rank, uint32_t epoch) {
+  pdl_launch_dependents();
+  pdl_wait();
+  if ((int)threadIdx.x < world) {
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flags.p[threadIdx.x] + rank), "r"(epoch) : "memory");
+  }
+}
+
 // CausalLm::softcap_logits (nn.rs:1158-1169): tanh(l / cap) * cap, each op rounded to bf16.
 __global__ void softcap_kernel(bf16* __restrict__ x, long long total, float cap) {
   pdl_launch_dependents();
@@ -423,6 +487,8 @@ static RowSource row_source(const SublayerOut& y) {
   RowSource r;
   r.y = y.y; r.part = y.part; r.splits = y.splits; r.split_stride = y.split_stride; r.ld = y.ld;
   r.rank_y = y.rank_y; r.ranks = y.ranks; r.rank_stride = y.rank_stride;
+  for (int i = 0; i < KC_MAX_TP; ++i) r.peer_y[i] = y.peer_y[i];
+  r.peers = y.peers; r.flags = y.flags; r.epoch = y.epoch; r.status = y.status;
   return r;
 }
 
@@ -454,6 +520,13 @@ cudaError_t launch_glu(const bf16* gu, int n, int F, int gelu, int interleaved, 
   const long long total = (long long)n * (F / 8);
   const int blocks = (int)std::min<long long>((total + 255) / 256, 148LL * 8);
   return launch_k(glu_kernel, dim3(blocks), dim3(256), 0, s, gu, n, F, gelu, interleaved, out);
+}
+
+cudaError_t launch_tp_signal(uint32_t* const* peer_flags, int world, int rank, uint32_t epoch, cudaStream_t s) {
+  if (world < 1 || world > KC_MAX_TP) return cudaErrorInvalidValue;
+  TpFlagPtrs f{};
+  for (int r = 0; r < world; ++r) f.p[r] = peer_flags[r];
+  return launch_k(tp_signal_kernel, dim3(1), dim3(32), 0, s, f, world, rank, epoch);
 }
 
 cudaError_t launch_glu_from(const SublayerOut& gu, int n, int F, int gelu, int interleaved, bf16* out, cudaStream_t s) {

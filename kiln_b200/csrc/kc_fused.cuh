@@ -11,6 +11,8 @@ cudaError_t launch_embed(const uint32_t* w, const bf16* scales, const bf16* bias
 // A GEMM output as its consumer reads it: bf16 [rows, ld], or the GEMM's fp32 split-K partials
 // [splits][rows][ld] (summed in split order and rounded to bf16 by the consumer), or the bf16 outputs of the
 // tensor-parallel ranks [ranks][rows][ld] (summed in rank order in fp32 and rounded once by the consumer), or nothing.
+constexpr int KC_MAX_TP = 8;
+
 struct SublayerOut {
   const bf16* y = nullptr;
   const float* part = nullptr;
@@ -20,6 +22,18 @@ struct SublayerOut {
   const bf16* rank_y = nullptr;
   int ranks = 0;
   size_t rank_stride = 0;
+  // Tensor-parallel peers: every rank's bf16 [rows, ld] output where it was written (this rank's own buffer and the
+  // peers' buffers mapped into this process), read in place once flags[r] >= epoch for every rank r.
+  const bf16* peer_y[KC_MAX_TP] = {};
+  int peers = 0;
+  const uint32_t* flags = nullptr;
+  uint32_t epoch = 0;
+  uint32_t* status = nullptr;
+  static SublayerOut of_peers(const bf16* const* peer_y, int peers, int ld, const uint32_t* flags, uint32_t epoch, uint32_t* status) {
+    SublayerOut s; s.peers = peers; s.ld = ld; s.flags = flags; s.epoch = epoch; s.status = status;
+    for (int r = 0; r < peers; ++r) s.peer_y[r] = peer_y[r];
+    return s;
+  }
   static SublayerOut of_ranks(const bf16* rank_y, int ranks, size_t rows, int ld) {
     SublayerOut s; s.rank_y = rank_y; s.ranks = ranks; s.rank_stride = rows * (size_t)ld; s.ld = ld; return s;
   }
@@ -39,6 +53,10 @@ cudaError_t launch_add_rmsnorm(const bf16* x, const SublayerOut& y, const bf16* 
 cudaError_t launch_rope_kv_write(const SublayerOut& qkv, const bf16* bias, const float* inv_freq, const int32_t* token_pos,
                                  const int32_t* kv_slot, int n, int Hq, int Hkv, int D, int traditional, int layer,
                                  int NB, int BS, bf16* pool, bf16* q_out, cudaStream_t s);
+
+// After the kernels before it on the stream have finished, stores `epoch` into slot `rank` of every rank's flag array
+// (peer_flags[r] = rank r's array as mapped into this process): "this rank's output of exchange `epoch` is complete".
+cudaError_t launch_tp_signal(uint32_t* const* peer_flags, int world, int rank, uint32_t epoch, cudaStream_t s);
 
 cudaError_t launch_glu(const bf16* gu, int n, int F, int gelu, int interleaved, bf16* out, cudaStream_t s);
 // The same over a GEMM output in its consumer form (gu.ld must be 2 F).

@@ -34,6 +34,15 @@ def main():
     model = api.CudaModel(ctx, cfg, ck, max_step_tokens=256, max_step_seqs=8, tp_rank=rank, tp_world=world)
     bs, nb = 16, 32
     kv = api.PagedKv(ctx, model.kv_spec(nb, bs, tp_world=world))
+    # a second slice of the same weights whose exchange runs over peer memory instead of NCCL
+    peer_model = api.CudaModel(ctx, cfg, ck, max_step_tokens=256, max_step_seqs=8, tp_rank=rank, tp_world=world)
+    peer_kv = api.PagedKv(ctx, peer_model.kv_spec(nb, bs, tp_world=world))
+
+    def everyone(b):
+        out = [None] * world
+        dist.all_gather_object(out, b)
+        return out
+    peer_model.tp_connect(everyone)
     g = torch.Generator().manual_seed(5)
     lens = [37, 20]
     ids, seqs, at = [], [], 0
@@ -47,6 +56,13 @@ def main():
     ids2 = torch.randint(0, cfg.vocab_size, (10,), generator=g).tolist()
     batch2 = api.StepBatch(ids2, [api.SeqStep(5, n, 5, b) for n, b in seqs])
     got2 = model.forward_step(batch2, kv); ctx.sync(); got2 = got2.cpu().clone()
+    dist.barrier()
+    peer1 = peer_model.forward_step(batch, peer_kv); ctx.sync(); peer1 = peer1.cpu().clone()
+    peer2 = peer_model.forward_step(batch2, peer_kv); ctx.sync(); peer2 = peer2.cpu().clone()
+    # the same rank-ordered fp32 sum, so the same bits, whichever way the rows travelled
+    peer_same = torch.equal(peer1.view(torch.int16), got1.view(torch.int16)) and torch.equal(peer2.view(torch.int16), got2.view(torch.int16))
+    peer_all = [None] * world
+    dist.all_gather_object(peer_all, bool(peer_same) and ctx.device_status() == 0)
     gathered = [None] * world
     dist.gather_object((got1.view(torch.int16), got2.view(torch.int16)), gathered if rank == 0 else None, dst=0)
     ok = True
@@ -68,8 +84,11 @@ def main():
             same = torch.equal(gathered[r][0], gathered[0][0]) and torch.equal(gathered[r][1], gathered[0][1])
             print(f"rank {r} logits identical to rank 0: {same}")
             ok &= same
+        print("peer-memory exchange bit-identical to the NCCL exchange on every rank:", peer_all)
+        ok &= all(peer_all)
         print("TP CHECK", "PASSED" if ok else "FAILED", "device status", ctx.device_status())
     dist.barrier()
+    peer_model.close(); peer_kv.close()
     model.close(); kv.close(); ctx.close()
     dist.destroy_process_group()
     sys.exit(0 if ok else 1)
