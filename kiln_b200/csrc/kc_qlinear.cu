@@ -201,12 +201,19 @@ __device__ __forceinline__ uint4 dequant8_w4(uint32_t u, bf162 sb) {
   const bf162 s2 = __bfloat162bfloat162(sb.x);
   const bf162 b2 = __bfloat162bfloat162(sb.y);
   const bf162 c128 = __floats2bfloat162_rn(128.f, 128.f);
+  // The record's nibble order puts element 2j at bits 4j and element 2j + 1 at bits 16 + 4j. Two masks split the word
+  // into bytes (even nibbles: elements 0, 4, 1, 5; odd nibbles: 2, 6, 3, 7) and a byte permute sets each under 0x43:
+  // 0x4300 | q is the bf16 value 128 + q (exact for q < 128); subtracting 128 is exact.
+  const uint32_t lo = u & 0x0F0F0F0Fu, hi = (u >> 4) & 0x0F0F0F0Fu;
+  uint32_t t[4];
+  t[0] = __byte_perm(lo, 0x43434343u, 0x4240u);   // elements 0, 1
+  t[1] = __byte_perm(hi, 0x43434343u, 0x4240u);   // elements 2, 3
+  t[2] = __byte_perm(lo, 0x43434343u, 0x4341u);   // elements 4, 5
+  t[3] = __byte_perm(hi, 0x43434343u, 0x4341u);   // elements 6, 7
   uint32_t o[4];
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    // 0x4300 | q is the bf16 value 128 + q (exact for q < 128); subtracting 128 is exact.
-    uint32_t t = ((u >> (4 * j)) & 0x000F000Fu) | 0x43004300u;
-    bf162 q = __hsub2(*reinterpret_cast<bf162*>(&t), c128);
+    bf162 q = __hsub2(*reinterpret_cast<bf162*>(&t[j]), c128);
     bf162 wv = __hfma2(q, s2, b2);  // one rounding: bf16(q*s + b)
     o[j] = *reinterpret_cast<uint32_t*>(&wv);
   }
