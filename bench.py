@@ -80,6 +80,7 @@ class ClockSampler:
 
     def __init__(self, device: int):
         self.device, self.proc, self.lines, self.samples, self.stop_flag, self.nvml = device, None, [], [], False, None
+        self.recording = True
 
     def _physical_index(self):
         vis = os.environ.get("CUDA_VISIBLE_DEVICES")
@@ -89,7 +90,10 @@ class ClockSampler:
                 return int(ids[self.device])
         return self.device
 
-    def start(self):
+    def start(self, record: bool = True):
+        """record = False: open NVML and start polling without keeping samples (the first queries after nvmlInit can
+        take hundreds of milliseconds); arm() then starts the record at the head of the timed region."""
+        self.recording = record
         try:
             import pynvml
             pynvml.nvmlInit()
@@ -115,16 +119,23 @@ class ClockSampler:
             try:
                 if i % 8 == 0:   # the power query is the slow one
                     power = n.nvmlDeviceGetPowerUsage(self.handle) / 1000.0
-                self.samples.append((n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM),
-                                     n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle), power))
+                sample = (n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM),
+                          n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle), power)
+                if self.recording:
+                    self.samples.append(sample)
             except Exception:
                 pass
             i += 1
             time.sleep(0.002)
 
+    def arm(self):
+        self.samples, self.lines = [], []
+        self.recording = True
+
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            if self.recording:
+                self.lines.append(line.strip())
 
     def stop(self) -> dict:
         if self.nvml:
@@ -318,6 +329,8 @@ def timed_steps(w: Workload, base, n_steps: int, warmup: int, barrier=None, samp
     import torch
     eng = w.engine
     records, checked, identical = [], 0, True
+    if sampler:
+        sampler.start(record=False)   # polling warms up during the warm-up steps; the record starts with the timed region
     arrivals, outs = [], {}
     done_warm = 0
     started = False
@@ -342,7 +355,7 @@ def timed_steps(w: Workload, base, n_steps: int, warmup: int, barrier=None, samp
             if barrier:
                 barrier()
             if sampler:
-                sampler.start()
+                sampler.arm()
             torch.cuda.profiler.start()   # lets `ncu --profile-from-start off` list the timed region's launches only
             started = True
         t0 = time.perf_counter()
@@ -636,10 +649,11 @@ def draft_lane_line(args, metric, config, warmup):
     off_recs, off_outs = run(2 + warmup // 8, True)
     draft = host.DraftModel(dmodel, dkv, nb, bs)
     eng.set_drafter(draft)
+    sampler = ClockSampler(0)
+    sampler.start(record=False)
     run(1, False)                                  # warm-up with the drafter attached
     ctx.draft_stats(reset=True)
-    sampler = ClockSampler(0)
-    sampler.start()
+    sampler.arm()
     n_req = max(1, -(-args.steps * 3 // gen))      # about `steps` rounds at ~3 tokens per round
     torch.cuda.profiler.start()                     # lets `ncu --profile-from-start off` list the timed region only
     recs, outs = run(n_req, True)

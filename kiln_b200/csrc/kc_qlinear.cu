@@ -542,6 +542,9 @@ qlinear_umma_ta_kernel(const __grid_constant__ CUtensorMap map_rows, const QlKer
     const bool mine0 = warp == 2;
     const bool mine1 = NT == 1 ? warp == 2 : (warp == 3 && nt_live == 2);
     if (lane == 0 && (mine0 || mine1)) {
+      // the activation tiles this thread waits for are loaded only after the kernels before this one have finished:
+      // its bounded waits start counting from there, not from the moment the CTA became resident
+      pdl_wait();
       const uint32_t idesc = umma_idesc_bf16(QL_TILE_N, p.m_pad);
       const uint64_t proto = umma_smem_desc_sw128(0);
       const uint32_t d_hi = (uint32_t)(proto >> 32), d_lo = (uint32_t)proto;
@@ -585,7 +588,11 @@ qlinear_umma_ta_kernel(const __grid_constant__ CUtensorMap map_rows, const QlKer
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
     RingPos rp, ap;
     for (int g = 0; g < grp; ++g) { rp.advance(RS); ap.advance(SA); }
+    bool released = false;
     for (int i = grp; i < nst && ok; i += QL_DQ_GROUPS) {
+      // the first SA stages are dequantised under the tail of the previous kernel; a slot that is being reused is freed
+      // by an MMA, which needs activations, which need the previous kernel: the bounded wait for it counts from there
+      if (!released && i >= SA) { pdl_wait(); released = true; }
       ok = __all_sync(0xffffffffu, mbar_wait(&raw_full[rp.stage], rp.phase, p.status, KC_DEV_QLINEAR | 5));
       if (!ok) break;
       uint32_t v[32];
