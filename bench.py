@@ -311,6 +311,32 @@ class Workload:
                 "synchronous_tok_s": len(arrivals) / (s_ms * 1e-3) if s_ms else None,
                 "rows_per_step": len(arrivals)}
 
+    def prefill_pass(self, n_prompts: int = 3, length: int = 4097):
+        """Chunked prefill through the same kernels (engine.rs:2114-2162, canonical_prefill_len :167-179): fresh
+        prompts of `length` tokens (no prefix-cache hit), one at a time, one generated token each. With the
+        reference's schedule a 4097-token prompt is two 2048-token chunks (each a forward whose GEMMs run in equal
+        row chunks of 256). Time = wall clock of the engine steps until the request finishes."""
+        import numpy as np
+        eng = self.engine
+        rng = np.random.default_rng(4242)
+        ms, fwd0 = [], eng.forwards
+        for _ in range(n_prompts):
+            prompt = rng.integers(0, self.cfg.vocab_size, size=length, dtype=np.int64).tolist()
+            a = eng.submit(prompt, 1)
+            t0 = time.perf_counter()
+            eng.run_to_completion([a])
+            self.ctx.sync()
+            ms.append((time.perf_counter() - t0) * 1e3)
+        med = float(statistics.median(ms))
+        c = self.cfg
+        per_layer = (c.num_attention_heads * c.head_dim + 2 * c.num_key_value_heads * c.head_dim) * c.hidden_size + \
+            c.num_attention_heads * c.head_dim * c.hidden_size + 3 * c.intermediate_size * c.hidden_size
+        flops = 2.0 * c.num_hidden_layers * per_layer * (length - 1) + \
+            4.0 * c.num_hidden_layers * c.num_attention_heads * c.head_dim * (length - 1) * (length / 2.0)
+        return {"prompt_tokens": length, "prompts": n_prompts, "ms_per_prompt": med, "tok_s": (length - 1) / (med * 1e-3),
+                "forwards_per_prompt": (eng.forwards - fwd0) / n_prompts, "tflops": flops / (med * 1e-3) / 1e12,
+                "chunk": self.prefill_chunk}
+
     def submit_on(self, base, p_accept=0.7, seed=0):
         """Phase 2 submission: scripted drafter with injected acceptance; every prompt is a prefix-cache hit."""
         if not hasattr(self, "drafter"):
@@ -785,6 +811,7 @@ def main():
     base = w.run_off()
     off_s = time.time() - t0
     plain_decode = w.plain_decode_pass()
+    prefill = w.prefill_pass() if w.tp == 1 else None
 
     def barrier():
         if dist:
@@ -878,6 +905,7 @@ def main():
         "spec_on_equals_off": {"sequences_checked": checked, "identical": bool(identical)},
         "setup_s": {"build_model": round(build_s, 1), "speculation_off_run": round(off_s, 1)},
         "plain_decode": plain_decode,
+        "prefill": prefill,
     }
     if per_rank:
         line["per_rank"] = per_rank
