@@ -4,7 +4,8 @@
 //   warp 0      bulk-copies the weight records (cp.async.bulk, mbarrier tx)
 //   warp 1      TMA-loads the activation k-blocks (cp.async.bulk.tensor, 128B swizzle)
 //   warps 2-3   allocate TMEM, issue tcgen05.mma (weights = A/M side from TENSOR MEMORY, activations = B/N side
-//               from shared memory)
+//               from shared memory); the two issuing threads take alternate pipeline stages and pass the issue order
+//               to each other through an mbarrier
 //   warps 4-19  unpack the 4/8-bit words, apply scale/bias in registers and write the bf16 A operand into tensor
 //               memory with tcgen05.st; afterwards drain the accumulators (tcgen05.ld) into y, the split-K
 //               partials or the gated activation.
@@ -470,7 +471,8 @@ qlinear_umma_ta_kernel(const __grid_constant__ CUtensorMap map_rows, const QlKer
   uint64_t* a_ready = b_empty + SB;
   uint64_t* a_empty = a_ready + SA;
   uint64_t* acc_full = a_empty + SA;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  uint64_t* turn = acc_full + 1;                        // the two MMA issuers hand the issue order to each other through it
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(turn + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile0 = blockIdx.x * NT, split = blockIdx.y;
@@ -480,7 +482,7 @@ qlinear_umma_ta_kernel(const __grid_constant__ CUtensorMap map_rows, const QlKer
   const int nkb = (int)((long long)p.kblocks * (split + 1) / p.splits) - kb0;
   const int nst = (nkb + KC - 1) / KC;                  // pipeline stages of this CTA
   const int tail_kc = nkb - (nst - 1) * KC;             // k-blocks of the last stage (1 or KC)
-  const int n_issuers = (NT == 2 && nt_live == 2) ? 2 : 1;
+  const int n_issuers = 1;   // a stage's MMAs are all issued (and its slots released) by one thread
   const uint32_t col_stride = (uint32_t)(p.m_pad + 31) & ~31u;
   const uint32_t a_col0 = NT * col_stride;              // first column of the A ring
 
@@ -489,7 +491,8 @@ qlinear_umma_ta_kernel(const __grid_constant__ CUtensorMap map_rows, const QlKer
     for (int i = 0; i < RS; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_empty[i], QL_DQ_GROUP_WARPS); }
     for (int i = 0; i < SB; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], n_issuers); }
     for (int i = 0; i < SA; ++i) { mbar_init(&a_ready[i], QL_DQ_GROUP_WARPS); mbar_init(&a_empty[i], n_issuers); }
-    mbar_init(acc_full, n_issuers);
+    mbar_init(acc_full, 2);   // both issuing threads commit to it after their last stage
+    mbar_init(turn, 1);
     mbar_fence_init();
   }
   if (warp == 2) {
@@ -538,29 +541,32 @@ qlinear_umma_ta_kernel(const __grid_constant__ CUtensorMap map_rows, const QlKer
       }
     }
   } else if (warp == 2 || warp == 3) {
-    // ---- MMA issuers: warp 2 takes unit 0 (and unit 1 when both units feed one accumulator), warp 3 the second tile ----
-    const bool mine0 = warp == 2;
-    const bool mine1 = NT == 1 ? warp == 2 : (warp == 3 && nt_live == 2);
-    if (lane == 0 && (mine0 || mine1)) {
-      // the activation tiles this thread waits for are loaded only after the kernels before this one have finished:
-      // its bounded waits start counting from there, not from the moment the CTA became resident
+    // ---- MMA issuers: warp 2 takes the even stages, warp 3 the odd ones ----
+    // Two issuing threads take alternate stages (all MMAs of a stage, both tiles): while one issues, the other is
+    // already through the waits, the fence and the descriptor arithmetic of the next stage. The order in which the
+    // MMAs enter the tensor pipe is handed over through `turn`: the issuer of stage i arrives on it after its last
+    // MMA instruction, the issuer of stage i + 1 waits for that before its first.
+    if (lane == 0) {
       pdl_wait();
+      const int me = warp - 2;
       const uint32_t idesc = umma_idesc_bf16(QL_TILE_N, p.m_pad);
       const uint64_t proto = umma_smem_desc_sw128(0);
       const uint32_t d_hi = (uint32_t)(proto >> 32), d_lo = (uint32_t)proto;
       const uint32_t b_lo0 = d_lo | ((smem_u32(sB) >> 4) & 0x3FFF);
       const uint32_t b_step = b_stage >> 4;
-      uint32_t acc = 0;
       RingPos ap, bp;
       for (int i = 0; i < nst; ++i, ap.advance(SA), bp.advance(SB)) {
+        if ((i & 1) != me) continue;
         if (!mbar_wait(&a_ready[ap.stage], ap.phase, p.status, KC_DEV_QLINEAR | 3)) { ok = false; break; }
         if (!mbar_wait(&b_full[bp.stage], bp.phase, p.status, KC_DEV_QLINEAR | 4)) { ok = false; break; }
         tc_fence_after();   // the A operand was written with tcgen05.st by other threads
         const uint32_t b_lo = b_lo0 + bp.stage * b_step;
         const uint32_t a_t = tmem_base + a_col0 + ap.stage * (UNITS * 32);
+        const uint32_t acc = i > 0 ? 1u : 0u;
+        if (i > 0 && !mbar_wait(turn, (uint32_t)(i - 1) & 1u, p.status, KC_DEV_QLINEAR | 8)) { ok = false; break; }
 #pragma unroll
         for (int u = 0; u < UNITS; ++u) {
-          if ((u == 0 ? mine0 : mine1) && (NT == 2 || u == 0 || i < nst - 1 || tail_kc == KC)) {
+          if ((NT == 2 ? u < nt_live : true) && (NT == 2 || u == 0 || i < nst - 1 || tail_kc == KC)) {
             const int t = NT == 2 ? u : 0, kc = NT == 2 ? 0 : u;
             const uint32_t b_u = b_lo + kc * (bk_bytes >> 4);
 #pragma unroll
@@ -569,7 +575,7 @@ qlinear_umma_ta_kernel(const __grid_constant__ CUtensorMap map_rows, const QlKer
                            (NT == 1 && u == 1) ? 1u : (ks == 0 ? acc : 1u));
           }
         }
-        acc = 1u;
+        mbar_arrive(turn);
         umma_commit(&a_empty[ap.stage]);
         umma_commit(&b_empty[bp.stage]);
       }
@@ -676,7 +682,7 @@ static TaPlan plan_ta(int nt, int m_pad, uint32_t raw_stride) {
   if (sb < 2 || rs < 3) return t;
   // the epilogue's per-warp transpose buffers reuse the ring memory from its start
   while ((size_t)sb * b_stage + (size_t)rs * rstage < (size_t)QL_DQ_WARPS * QL_EPI_STAGE_BYTES) ++rs;
-  const size_t smem = 1024 + (size_t)sb * b_stage + (size_t)rs * rstage + (2 * rs + 2 * sb + 2 * sa + 1) * 8 + 16;
+  const size_t smem = 1024 + (size_t)sb * b_stage + (size_t)rs * rstage + (2 * rs + 2 * sb + 2 * sa + 2) * 8 + 16;
   if (smem > 227 * 1024) return t;
   t.ok = true; t.sa = sa; t.sb = sb; t.rs = rs; t.tmem_cols = cols; t.smem = smem;
   return t;
