@@ -188,3 +188,73 @@ def test_pipelining_can_be_switched_off_and_on_mid_generation():
     assert got + out[0] == reference_generation(p, 40)
     empty = H.KhDecodePipeline()
     assert H.lib().kh_engine_set_pipeline(eng._h, C.byref(empty)) != 0   # a table without its two calls is refused
+
+
+def test_reference_grouping_keeps_wide_steps_synchronous():
+    """With the reference's forward grouping (batch_verify = 0) a decode step wider than the deterministic width is
+    several forwards; the pipeline only spans steps that are one forward."""
+    ps = prompts(3, 31, lo=4, hi=9)
+    for n_seqs, expect in ((2, True), (3, False)):
+        eng, model, sm = make_engine(num_blocks=128, batch_verify=False, deterministic_decode_width=2)
+        arr = [eng.submit(p, 14) for p in ps[:n_seqs]]
+        out = eng.run_to_completion(arr)
+        for a, p in zip(arr, ps):
+            assert out[a] == (reference_generation(p, 14), "length")
+        widths = [len(e[2]) for e in sm.pipeline_log if e[0] == "launch"]
+        assert all(w <= 2 for w in widths)        # three sequences pipeline only once one of them has left
+        if expect:
+            assert max(widths) == 2
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_traffic_pipelined_equals_synchronous(seed):
+    """Staggered submissions, stop tokens, different lengths and a small pool (evictions): the pipelined engine and the
+    synchronous one emit the same tokens with the same finish kinds; cancelled requests emit a prefix of the model's
+    stream; every block comes back."""
+    import numpy as np
+    rng = np.random.default_rng(1000 + seed)
+    n = int(rng.integers(3, 7))
+    ps = prompts(n, 200 + seed, lo=3, hi=30)
+    script = []
+    for i, p in enumerate(ps):
+        gen = int(rng.integers(2, 28))
+        truth = reference_generation(p, gen)
+        stop = [truth[int(rng.integers(0, gen))]] if rng.random() < 0.4 else []
+        script.append({"prompt": p, "gen": gen, "stop": stop, "at": int(rng.integers(0, 25)),
+                       "cancel_at": int(rng.integers(5, 40)) if rng.random() < 0.25 else None, "truth": truth})
+    results = []
+    for pipelined in (True, False):
+        eng, model, sm = make_engine(num_blocks=48, pipelined=pipelined)
+        arr, outs, kinds = {}, {}, {}
+        for step in range(400):
+            for i, r in enumerate(script):
+                if r["at"] == step:
+                    arr[i] = eng.submit(r["prompt"], r["gen"], r["stop"])
+                    outs[i], kinds[i] = [], None
+                if r["cancel_at"] == step and i in arr and kinds[i] is None:
+                    eng.cancel(arr[i])
+            eng.step()
+            for i, a in arr.items():
+                if kinds[i] is None:
+                    toks, kind = eng.take_output(a)
+                    outs[i] += toks
+                    kinds[i] = kind
+            if len(arr) == len(script) and all(k is not None for k in kinds.values()):
+                break
+        assert all(k is not None for k in kinds.values()), "requests did not finish"
+        for _ in range(3):
+            eng.step()   # a dropped row may still be in flight
+        assert eng.block_manager().num_free + eng.cache_stats()["resident_blocks"] == 48
+        results.append((outs, kinds))
+        assert (eng.pipelined_steps > 0) or not pipelined or n == 0
+    for i, r in enumerate(script):
+        for outs, kinds in results:
+            assert outs[i] == r["truth"][:len(outs[i])]
+        if r["cancel_at"] is None:
+            assert results[0][0][i] == results[1][0][i] and results[0][1][i] == results[1][1][i]
+            want = r["truth"]
+            if r["stop"]:
+                cut = want.index(r["stop"][0])
+                assert results[0][0][i] == want[:cut] and results[0][1][i] == "stop"
+            else:
+                assert results[0][0][i] == want and results[0][1][i] == "length"
