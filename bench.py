@@ -862,7 +862,10 @@ def main():
     torch.cuda.empty_cache()
     if dist and main_tp == 1 and not args.no_tp_record:
         # the configuration that shards (BASELINE config 5's layer shapes, batch, k and prompt lengths), on all N GPUs
-        tp_rec = tp_record(rank, local_rank, world, dist, barrier)
+        try:
+            tp_rec = tp_record(rank, local_rank, world, dist, barrier)
+        except Exception as exc:   # the replica measurement above stands; the record says what failed
+            tp_rec = {"workload": TP_WORKLOAD, "ranks": world, "error": f"{type(exc).__name__}: {exc}"[:400]}
     if rank != 0:
         if dist:
             dist.destroy_process_group()
