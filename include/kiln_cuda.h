@@ -184,7 +184,9 @@ KC_API int kc_envelope(kc_model_t model, int32_t* max_gamma, int32_t* max_key_le
 
 /* Switches the weight-streaming lane on or off for this model: forwards of at most 8 rows (a draft model's chained
  * decode steps, crates/kiln-models/src/draft.rs:354-388) then read every weight straight from global memory into
- * registers instead of going through the tensor-core pipeline, whose set-up dominates such a step. Off by default,
+ * registers instead of going through the tensor-core pipeline, whose set-up dominates such a step. on = 1: weights of
+ * at least 24 MB (8B-class layers, every head; smaller ones are latency-bound either way and stay on the tensor-core
+ * kernel); on = 2: every weight; on = 0: off. Off by default,
  * and meant for draft models: a row's bits differ between the two lanes, so a target model whose decode steps
  * (few rows) and verify steps (more than 8 rows) must agree bit for bit keeps it off. Not available on a
  * tensor-parallel slice. */

@@ -438,9 +438,10 @@ class CudaModel:
         arr = (C.c_uint8 * len(blob)).from_buffer_copy(blob)
         check(L.lib().kc_tp_attach(self._h, arr))
 
-    def set_stream_lane(self, on: bool = True) -> None:
-        """Forwards of at most 8 rows take the weight-streaming kernels (kc_model_set_stream_lane): for draft models."""
-        check(L.lib().kc_model_set_stream_lane(self._h, int(on)))
+    def set_stream_lane(self, on: bool = True, every_weight: bool = False) -> None:
+        """Forwards of at most 8 rows take the weight-streaming kernels (kc_model_set_stream_lane): for draft models.
+        By default only weights of at least 24 MB stream; ``every_weight`` streams all of them."""
+        check(L.lib().kc_model_set_stream_lane(self._h, (2 if every_weight else 1) if on else 0))
 
     def envelope(self):
         """(max_gamma, max_key_len or 0 = unbounded, deterministic width) as the backend provides them."""

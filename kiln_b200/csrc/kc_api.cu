@@ -160,6 +160,7 @@ struct kc_model {
   int Hq = 0, Hkv = 0;                 // local (tensor-parallel) head counts
   int F = 0;                           // local intermediate size
   bool stream_lane = false;            // forwards of at most QL_STREAM_MAX_M rows take the weight-streaming kernels
+  size_t stream_min_bytes = QL_STREAM_MIN_BYTES;   // ... for weights of at least this many bytes of records
   bool glu_interleaved = false;        // gate_up rows alternate gate / up in blocks of 128 (so the GEMM can fuse the activation)
   int n_qkv = 0;
   std::vector<Layer> layers;
@@ -1175,32 +1176,36 @@ int run_forward(kc_model* m, kc_kv* kv, const uint32_t* tokens_dev, const StepPl
   int rc;
   if ((rc = ensure_attn_ws(m, p))) return rc;
   const bool stream = m->stream_lane && n <= QL_STREAM_MAX_M && d.tp_world <= 1;
+  // Per weight: the streaming kernel pays for itself from about 24 MB of records on (8B-class layers, every head); below
+  // that the launch is latency-bound either way and the consumer would only have more partial pieces to sum. A
+  // function of the weight's size alone, so a model takes the same kernels for every small step.
+  auto streams = [&](const QWeight& w) { return stream && w.bytes() >= m->stream_min_bytes; };
   LAUNCH(c, KC_PROF_ROWWISE, 1, launch_embed(m->emb_w, m->emb_s, m->emb_b, tokens_dev, n, H, d.bits, d.group_size, m->embed_scale, d.vocab_size, m->h, c->stream));
   LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, SublayerOut::none(), nullptr, m->layers[0].input_ln, nullptr, n, H, d.rms_norm_eps, nullptr, m->normed, c->stream));
   for (int l = 0; l < d.num_layers; ++l) {
     Layer& L = m->layers[l];
     SublayerOut so;
-    if (stream) RC(run_stream(c, L.qkv, m->normed, n, m->qkv, m->n_qkv, m->partial, &so));
+    if (streams(L.qkv)) RC(run_stream(c, L.qkv, m->normed, n, m->qkv, m->n_qkv, m->partial, &so));
     else RC(run_qlinear(c, L.qkv, m->op_normed, n, m->qkv, m->n_qkv, m->partial, &so));
     LAUNCH(c, KC_PROF_ROWWISE, 1, launch_rope_kv_write(so, L.qkv_bias, m->inv_freq, token_pos, kv_slot, n, m->Hq, m->Hkv, D, d.rope_traditional, l,
                             kv->num_blocks, kv->block_size, kv->pool, m->q_rot, c->stream));
     const int window = (d.sliding_window > 0 && (l % 2 == 0)) ? d.sliding_window : 0;
     AttnParams a = attn_params(m, kv, p, l, m->q_rot, m->attn, m->attn_scale, gemma ? d.attn_logit_softcapping : 0.f, window, m->Hq);
     LAUNCH(c, KC_PROF_ATTN, 2, paged_attention(kv->map, a, D, p.tokens_per_item, p.n_work, p.max_chunks, n, c->stream));
-    if (stream) RC(run_stream(c, L.o, m->attn, n, m->proj, H, m->partial, &so));
+    if (streams(L.o)) RC(run_stream(c, L.o, m->attn, n, m->proj, H, m->partial, &so));
     else RC(run_qlinear(c, L.o, m->op_attn, n, d.tp_world > 1 ? tp_out_buffer(m) : m->proj, H, m->partial, d.tp_world > 1 ? nullptr : &so));
     if (d.tp_world > 1 && (rc = tp_exchange(m, n, &so))) return rc;
     if (gemma) LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, so, L.post_attn_ln, L.pre_ffw_ln, nullptr, n, H, d.rms_norm_eps, m->h, m->normed, c->stream));
     else LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, so, nullptr, L.post_attn_ln, nullptr, n, H, d.rms_norm_eps, m->h, m->normed, c->stream));
-    if (stream) {
+    if (streams(L.gate_up)) {
       SublayerOut gu;
       RC(run_stream(c, L.gate_up, m->normed, n, m->gu, 2 * m->F, m->partial, &gu));
       LAUNCH(c, KC_PROF_ROWWISE, 1, launch_glu_from(gu, n, m->F, gemma ? 1 : 0, m->glu_interleaved ? 1 : 0, m->act, c->stream));
-      RC(run_stream(c, L.down, m->act, n, m->proj, H, m->partial, &so));
     } else {
       RC(run_gated(c, L.gate_up, m->op_normed, n, m->gu, m->F, gemma ? 1 : 0, m->glu_interleaved, m->act, m->partial));
-      RC(run_qlinear(c, L.down, m->op_act, n, d.tp_world > 1 ? tp_out_buffer(m) : m->proj, H, m->partial, d.tp_world > 1 ? nullptr : &so));
     }
+    if (streams(L.down)) RC(run_stream(c, L.down, m->act, n, m->proj, H, m->partial, &so));
+    else RC(run_qlinear(c, L.down, m->op_act, n, d.tp_world > 1 ? tp_out_buffer(m) : m->proj, H, m->partial, d.tp_world > 1 ? nullptr : &so));
     if (d.tp_world > 1 && (rc = tp_exchange(m, n, &so))) return rc;
     const bf16* next_ln = l + 1 < d.num_layers ? m->layers[l + 1].input_ln : nullptr;
     LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, so, gemma ? L.post_ffw_ln : nullptr, next_ln, nullptr, n, H, d.rms_norm_eps, m->h, m->normed, c->stream));
@@ -1208,7 +1213,7 @@ int run_forward(kc_model* m, kc_kv* kv, const uint32_t* tokens_dev, const StepPl
   if (want_logits && p.n_sampled > 0) {
     const int32_t* sampled = reinterpret_cast<const int32_t*>(m->meta_dev + p.lay.sampled);
     LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, SublayerOut::none(), nullptr, m->final_norm, sampled, p.n_sampled, H, d.rms_norm_eps, nullptr, m->hs, c->stream));
-    if (stream) RC(run_stream(c, m->head, m->hs, p.n_sampled, m->logits, d.vocab_size, m->partial, nullptr));
+    if (streams(m->head)) RC(run_stream(c, m->head, m->hs, p.n_sampled, m->logits, d.vocab_size, m->partial, nullptr));
     else RC(run_qlinear(c, m->head, m->op_hs, p.n_sampled, m->logits, d.vocab_size, m->partial));
     if (gemma && d.final_logit_softcapping > 0.f)
       LAUNCH(c, KC_PROF_ROWWISE, 1, launch_softcap(m->logits, (long long)p.n_sampled * d.vocab_size, d.final_logit_softcapping, c->stream));
@@ -1267,6 +1272,7 @@ extern "C" int kc_model_set_stream_lane(kc_model_t m, int32_t on) {
   if (!m) return fail(KC_ERR_INVALID, "kc_model_set_stream_lane: model is NULL");
   if (on && m->d.tp_world > 1) return fail(KC_ERR_UNSUPPORTED, "kc_model_set_stream_lane: not available on a tensor-parallel slice");
   m->stream_lane = on != 0;
+  m->stream_min_bytes = on == 2 ? 0 : QL_STREAM_MIN_BYTES;
   return KC_OK;
 }
 

@@ -29,6 +29,7 @@ namespace kc {
 constexpr int QL_TILE_N = 128;  // output features per tile = UMMA M
 constexpr int QL_KB = 64;       // input features per k-block = one 128-byte swizzle row of bf16
 constexpr int QL_MAX_M = 512;   // activation rows per qlinear_umma call (one slab of the split-K workspace)
+constexpr size_t QL_STREAM_MIN_BYTES = (size_t)24 << 20;  // records of a weight from which a model's small steps stream it
 constexpr int QL_STREAM_MAX_M = 8;  // activation rows the weight-streaming lane takes (the 8 columns of one mma.sync)
 constexpr int QL_TILE_GROUP = 4;  // tiles whose records are interleaved per k-block (the most one CTA owns)
 
