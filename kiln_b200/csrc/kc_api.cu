@@ -1122,6 +1122,7 @@ AttnParams attn_params(kc_model* m, kc_kv* kv, const StepPlan& p, int layer, con
   a.Hq = Hq; a.Hkv = kv->kv_heads; a.gqa = Hq / kv->kv_heads;
   a.layer = layer; a.NB = kv->num_blocks; a.BS = kv->block_size;
   a.max_chunks = p.max_chunks; a.chunk_lo_grid = 0;
+  a.single_chunk = p.max_chunks == 1 ? 1 : 0;
   a.scale = scale; a.softcap = softcap; a.window = window;
   a.pool = kv->pool;
   a.kv4d = kv->map4d ? 1 : 0;
@@ -1191,7 +1192,7 @@ int run_forward(kc_model* m, kc_kv* kv, const uint32_t* tokens_dev, const StepPl
                             kv->num_blocks, kv->block_size, kv->pool, m->q_rot, c->stream));
     const int window = (d.sliding_window > 0 && (l % 2 == 0)) ? d.sliding_window : 0;
     AttnParams a = attn_params(m, kv, p, l, m->q_rot, m->attn, m->attn_scale, gemma ? d.attn_logit_softcapping : 0.f, window, m->Hq);
-    LAUNCH(c, KC_PROF_ATTN, 2, paged_attention(kv->map, a, D, p.tokens_per_item, p.n_work, p.max_chunks, n, c->stream));
+    LAUNCH(c, KC_PROF_ATTN, a.single_chunk ? 1 : 2, paged_attention(kv->map, a, D, p.tokens_per_item, p.n_work, p.max_chunks, n, c->stream));
     if (streams(L.o)) RC(run_stream(c, L.o, m->attn, n, m->proj, H, m->partial, &so));
     else RC(run_qlinear(c, L.o, m->op_attn, n, d.tp_world > 1 ? tp_out_buffer(m) : m->proj, H, m->partial, d.tp_world > 1 ? nullptr : &so));
     if (d.tp_world > 1 && (rc = tp_exchange(m, n, &so))) return rc;
@@ -1490,7 +1491,7 @@ extern "C" int kc_paged_attention(kc_ctx_t c, kc_kv_t kv, int32_t layer, const v
   if (!rc) {
     AttnParams a = attn_params(m, kv, p, layer, (const bf16*)q_dev, (bf16*)out_dev, scale, softcap, window, num_heads);
     rc = [&]() -> int {
-      LAUNCH(c, KC_PROF_ATTN, 2, paged_attention(kv->map, a, kv->head_dim, p.tokens_per_item, p.n_work, p.max_chunks, n, c->stream));
+      LAUNCH(c, KC_PROF_ATTN, a.single_chunk ? 1 : 2, paged_attention(kv->map, a, kv->head_dim, p.tokens_per_item, p.n_work, p.max_chunks, n, c->stream));
       return KC_OK;
     }();
   }

@@ -56,6 +56,7 @@ __device__ __forceinline__ void named_bar_sync(int id, int threads) {
 // holds): the split a key tile belongs to, and so the merge order a row sees, must be the
 // same in a one-token decode launch and in a verify launch.
 template <int MT> struct KeySplit { static constexpr int value = 2; };
+static_assert(KeySplit<1>::value > 1, "the partial kernel finishes single-chunk rows in its key-split merge");
 
 // Shared memory: [stages][K tile | V tile] (1024-aligned, swizzled by TMA),
 // then the Q rows (padded), then barriers. The K/V ring is reused for the
@@ -307,6 +308,10 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap kvmap, const AttnParams 
           const int t = r / gqa, hg = r % gqa;
           const size_t prow = ((size_t)(tok0 + t) * p.Hq + kvh * gqa + hg) * p.max_chunks + chunk;
           float* po = p.part_o + prow * D;
+          // When no sequence of the step reaches past the first chunk, the chunk merge is the identity (weight
+          // exp2(m - m) = 1) followed by the division: the row is finished here, with the arithmetic the combine
+          // kernel would have applied to it, and that launch is skipped.
+          bf16* fo = p.out + prow * D;   // max_chunks == 1 and chunk == 0 then: prow is the output row
           const int d0 = (lane & 1) * (D / 2);
           for (int d = d0; d < d0 + D / 2; d += 4) {
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -314,9 +319,16 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap kvmap, const AttnParams 
               const float4 x = *reinterpret_cast<const float4*>(mg + ((size_t)(k * MT * 16) + r) * RS + d);
               acc.x += wgt[k] * x.x; acc.y += wgt[k] * x.y; acc.z += wgt[k] * x.z; acc.w += wgt[k] * x.w;
             }
-            *reinterpret_cast<float4*>(po + d) = acc;
+            if (p.single_chunk) {
+              // 0 + x: what the combine kernel's accumulation from zero yields (a -0 becomes +0 there too)
+              acc.x = 0.f + acc.x; acc.y = 0.f + acc.y; acc.z = 0.f + acc.z; acc.w = 0.f + acc.w;
+              if (lsum != 0.f) { acc.x = acc.x / lsum; acc.y = acc.y / lsum; acc.z = acc.z / lsum; acc.w = acc.w / lsum; }
+              *reinterpret_cast<uint2*>(fo + d) = make_uint2(pack_bf162(acc.x, acc.y), pack_bf162(acc.z, acc.w));
+            } else {
+              *reinterpret_cast<float4*>(po + d) = acc;
+            }
           }
-          if ((lane & 1) == 0) p.part_ml[prow] = make_float2(mmax, lsum);
+          if ((lane & 1) == 0 && !p.single_chunk) p.part_ml[prow] = make_float2(mmax, lsum);
         }
       }
     } else if (ok) {
@@ -393,7 +405,7 @@ cudaError_t launch_d(const CUtensorMap& map, const AttnParams& p, int mt, int n_
     case 3: e = launch_partial<D, 3>(map, p, n_work, grid_chunks, s); break;
     default: e = launch_partial<D, 4>(map, p, n_work, grid_chunks, s); break;
   }
-  if (e != cudaSuccess) return e;
+  if (e != cudaSuccess || p.single_chunk) return e;
   const int n_rows = n_tokens * p.Hq;
   return launch_k(attn_combine_kernel<D>, dim3((n_rows + 7) / 8), dim3(256), 0, s, p, n_rows);
 }

@@ -25,6 +25,7 @@ struct AttnParams {
   int Hq, Hkv, gqa;
   int layer, NB, BS;
   int max_chunks;
+  int single_chunk;            // 1: max_chunks == 1, the partial kernel writes `out` itself and no combine kernel follows
   int chunk_lo_grid;           // chunk index of blockIdx.x == 0
   float scale;                 // softmax scale (applied to fp32 scores)
   float softcap;               // 0 = off
