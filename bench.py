@@ -561,12 +561,16 @@ def tp_record(rank: int, local_rank: int, world: int, dist, barrier) -> dict:
            "spec_on_equals_off": chk["spec_on_equals_off"]["identical"], "sequences_checked": chk["spec_on_equals_off"]["sequences_checked"],
            "speculation_on_twice_equal": chk["speculation_on_twice_equal"], "all_ranks_ok": tot.all_identical,
            "device_status_max_over_ranks": int(st[0]),
-           "exchange": ("peer memory: every rank's bf16 [rows, hidden] sublayer output after o_proj and down_proj is read in place over "
-                        "NVLink by the consumer kernel (flag per rank and exchange, plain peer loads) and summed in rank order in fp32"
+           "exchange": (("peer memory, two phases: every rank sums its column slice of all ranks' bf16 [rows, hidden] sublayer outputs "
+                         "(peer loads over NVLink, rank order, fp32, one rounding), the consumer kernel gathers the summed slices"
+                         if world >= 4 and os.environ.get("KILN_TP_TWO_PHASE", "1") != "0" else
+                         "peer memory: every rank's bf16 [rows, hidden] sublayer output after o_proj and down_proj is read in place over "
+                         "NVLink by the consumer kernel (flag per rank and exchange, plain peer loads) and summed in rank order in fp32")
                         if w.tp_exchange == "peer" else
                         "all-gather of every rank's bf16 [rows, hidden] sublayer output after o_proj and down_proj (NCCL), summed "
                         "in rank order in fp32 by the consumer kernel"),
-           "peer_bytes_received_per_rank_per_step": int(2 * cfg.num_hidden_layers * (world - 1) * rows * cfg.hidden_size * 2),
+           "peer_bytes_received_per_rank_per_step": int(2 * cfg.num_hidden_layers * (world - 1) * rows * cfg.hidden_size * 2 *
+                                                        (2.0 / world if (w.tp_exchange == "peer" and world >= 4 and os.environ.get("KILN_TP_TWO_PHASE", "1") != "0") else 1.0)),
            "seconds": round(time.time() - t0, 1)}
     w.close()
     return rec

@@ -188,6 +188,10 @@ struct kc_model {
   bf16* peer_out[2][KC_MAX_TP] = {};
   uint32_t* peer_flags[KC_MAX_TP] = {};
   bool tp_p2p = false;
+  // Two-phase exchange (from 4 ranks on): each tp_out buffer is followed by a second region of the same size that
+  // holds this rank's summed column slice [rows][H / world]; the second half of the flag array belongs to that phase.
+  bool tp_two_phase = false;
+  size_t tp_sum_off = 0;              // elements from tp_out[b] to the slice region
   uint32_t tp_epoch = 0;
   // step metadata
   uint8_t* meta_dev = nullptr; size_t meta_cap = 0;
@@ -916,9 +920,10 @@ extern "C" int kc_model_load(kc_ctx_t c, const kc_model_desc* desc, const kc_ten
   }
   if (tp > 1) {
     cudaError_t e = cudaMalloc(&m->tp_buf, R * H * sizeof(float));
-    for (int b = 0; b < 2 && e == cudaSuccess; ++b) e = cudaMalloc(&m->tp_out[b], R * H * sizeof(bf16));
-    if (e == cudaSuccess) e = cudaMalloc(&m->tp_flags, KC_MAX_TP * sizeof(uint32_t));
-    if (e == cudaSuccess) e = cudaMemsetAsync(m->tp_flags, 0, KC_MAX_TP * sizeof(uint32_t), c->stream);
+    m->tp_sum_off = R * H;
+    for (int b = 0; b < 2 && e == cudaSuccess; ++b) e = cudaMalloc(&m->tp_out[b], 2 * R * H * sizeof(bf16));
+    if (e == cudaSuccess) e = cudaMalloc(&m->tp_flags, 2 * KC_MAX_TP * sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMemsetAsync(m->tp_flags, 0, 2 * KC_MAX_TP * sizeof(uint32_t), c->stream);
     if (e != cudaSuccess) LOAD_FAIL(fail(KC_ERR_OOM, "tensor-parallel buffers: %s", cudaGetErrorString(e)));
   }
   {
@@ -1150,8 +1155,23 @@ int tp_exchange(kc_model* m, int n, SublayerOut* so) {
   const int H = m->d.hidden_size;
   if (m->tp_p2p) {
     const uint32_t e = m->tp_epoch;   // set by tp_out_buffer for this exchange
-    LAUNCH(c, KC_PROF_ROWWISE, 1, launch_tp_signal(m->peer_flags, m->d.tp_world, m->d.tp_rank, e, c->stream));
-    *so = SublayerOut::of_peers(m->peer_out[e & 1], m->d.tp_world, H, m->tp_flags, e, c->status);
+    const int W = m->d.tp_world, me = m->d.tp_rank;
+    LAUNCH(c, KC_PROF_ROWWISE, 1, launch_tp_signal(m->peer_flags, W, me, e, c->stream));
+    if (!m->tp_two_phase) {
+      *so = SublayerOut::of_peers(m->peer_out[e & 1], W, H, m->tp_flags, e, c->status);
+      return KC_OK;
+    }
+    // Two phases, the shape of a reduce-scatter followed by an all-gather: this rank sums ITS column slice of every
+    // rank's rows (pulling (W - 1) / W of a [rows, H] buffer instead of W - 1 whole ones), publishes it, and the
+    // consumer gathers the W summed slices. Same rank-ordered fp32 sum, same single rounding: the same bits.
+    const int sw = H / W;
+    const bf16* slices[KC_MAX_TP] = {};
+    uint32_t* flags2[KC_MAX_TP] = {};
+    for (int r = 0; r < W; ++r) { slices[r] = m->peer_out[e & 1][r] + m->tp_sum_off; flags2[r] = m->peer_flags[r] + KC_MAX_TP; }
+    LAUNCH(c, KC_PROF_ROWWISE, 1, launch_tp_reduce_slice(m->peer_out[e & 1], W, me, n, H, sw, m->tp_flags, e, c->status,
+                                                        m->tp_out[e & 1] + m->tp_sum_off, c->stream));
+    LAUNCH(c, KC_PROF_ROWWISE, 1, launch_tp_signal(flags2, W, me, e, c->stream));
+    *so = SublayerOut::of_peer_slices(slices, W, H, sw, m->tp_flags + KC_MAX_TP, e, c->status);
     return KC_OK;
   }
   int rc = tp_allgather(m, m->proj, m->proj_ranks, n);
@@ -1266,6 +1286,9 @@ extern "C" int kc_tp_attach(kc_model_t m, const void* handles_all) {
   }
   m->tp_p2p = true;
   m->tp_epoch = 0;
+  // the two-phase form pays from 4 ranks on (at 2 ranks both forms move the same bytes and it only adds launches)
+  m->tp_two_phase = W >= 4 && m->d.hidden_size % (8 * W) == 0;
+  if (const char* env = getenv("KILN_TP_TWO_PHASE")) m->tp_two_phase = atoi(env) != 0 && m->d.hidden_size % (8 * W) == 0;
   return KC_OK;
 }
 

@@ -69,6 +69,7 @@ struct RowSource {
   const uint32_t* flags;           // this rank's flag array: flags[r] >= epoch once rank r's output is complete
   uint32_t epoch;
   uint32_t* status;
+  int slice_w;                     // > 0: peer_y[s] holds the summed columns s * slice_w .. as [rows][slice_w]
 };
 
 // Waits until every tensor-parallel rank has published the output of exchange `epoch`. The flags live in this GPU's
@@ -121,6 +122,12 @@ __device__ __forceinline__ void load8(const RowSource& s, size_t row, int col, f
     }
     v[0] = bf16_round(a.x); v[1] = bf16_round(a.y); v[2] = bf16_round(a.z); v[3] = bf16_round(a.w);
     v[4] = bf16_round(b.x); v[5] = bf16_round(b.y); v[6] = bf16_round(b.z); v[7] = bf16_round(b.w);
+  } else if (s.peers && s.slice_w) {
+    // already summed and rounded by the slice's owner: gather
+    const int owner = col / s.slice_w;
+    const uint4 u = __ldcv(reinterpret_cast<const uint4*>(s.peer_y[owner] + row * s.slice_w + (col - owner * s.slice_w)));
+    const float2 a = unpack_bf162(u.x), b = unpack_bf162(u.y), c = unpack_bf162(u.z), d = unpack_bf162(u.w);
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y; v[4] = c.x; v[5] = c.y; v[6] = d.x; v[7] = d.y;
   } else if (s.peers) {
     // rank order, fp32, one rounding; the peers' rows are read where they were written (NVLink loads, not cached here)
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -446,6 +453,20 @@ __global__ void tp_signal_kernel(TpFlagPtrs flags, int world, int rank, uint32_t
   }
 }
 
+// First phase of the two-phase tensor-parallel exchange (a reduce-scatter over peer memory): this rank sums its
+// column slice of every rank's partial output. One CTA per row.
+__global__ void __launch_bounds__(128) tp_reduce_slice_kernel(RowSource src, int rank, int H, int slice_w, bf16* __restrict__ out) {
+  pdl_wait();
+  tp_wait(src);
+  pdl_launch_dependents();
+  const size_t row = blockIdx.x;
+  for (int c = threadIdx.x * 8; c < slice_w; c += blockDim.x * 8) {
+    float v[8];
+    load8(src, row, rank * slice_w + c, v);   // src.slice_w == 0: the rank-ordered sum
+    store8_bf16(out + row * slice_w + c, v);
+  }
+}
+
 // CausalLm::softcap_logits (nn.rs:1158-1169): tanh(l / cap) * cap, each op rounded to bf16.
 __global__ void softcap_kernel(bf16* __restrict__ x, long long total, float cap) {
   pdl_launch_dependents();
@@ -488,7 +509,7 @@ static RowSource row_source(const SublayerOut& y) {
   r.y = y.y; r.part = y.part; r.splits = y.splits; r.split_stride = y.split_stride; r.ld = y.ld;
   r.rank_y = y.rank_y; r.ranks = y.ranks; r.rank_stride = y.rank_stride;
   for (int i = 0; i < KC_MAX_TP; ++i) r.peer_y[i] = y.peer_y[i];
-  r.peers = y.peers; r.flags = y.flags; r.epoch = y.epoch; r.status = y.status;
+  r.peers = y.peers; r.flags = y.flags; r.epoch = y.epoch; r.status = y.status; r.slice_w = y.slice_w;
   return r;
 }
 
@@ -527,6 +548,14 @@ cudaError_t launch_tp_signal(uint32_t* const* peer_flags, int world, int rank, u
   TpFlagPtrs f{};
   for (int r = 0; r < world; ++r) f.p[r] = peer_flags[r];
   return launch_k(tp_signal_kernel, dim3(1), dim3(32), 0, s, f, world, rank, epoch);
+}
+
+cudaError_t launch_tp_reduce_slice(const bf16* const* peer_y, int world, int rank, int rows, int H, int slice_w, const uint32_t* flags,
+                                   uint32_t epoch, uint32_t* status, bf16* out, cudaStream_t s) {
+  if (rows <= 0) return cudaSuccess;
+  if (world < 2 || world > KC_MAX_TP || slice_w % 8 || slice_w * world != H) return cudaErrorInvalidValue;
+  return launch_k(tp_reduce_slice_kernel, dim3(rows), dim3(128), 0, s,
+                  row_source(SublayerOut::of_peers(peer_y, world, H, flags, epoch, status)), rank, H, slice_w, out);
 }
 
 cudaError_t launch_glu_from(const SublayerOut& gu, int n, int F, int gelu, int interleaved, bf16* out, cudaStream_t s) {

@@ -29,6 +29,15 @@ struct SublayerOut {
   const uint32_t* flags = nullptr;
   uint32_t epoch = 0;
   uint32_t* status = nullptr;
+  // slice_w > 0: the peers' buffers hold ALREADY SUMMED column slices, [rows][slice_w] each, rank s owning columns
+  // s * slice_w .. (the second phase of the two-phase exchange): the row is gathered, nothing is added.
+  int slice_w = 0;
+  static SublayerOut of_peer_slices(const bf16* const* peer_y, int peers, int ld, int slice_w, const uint32_t* flags, uint32_t epoch,
+                                    uint32_t* status) {
+    SublayerOut s = of_peers(peer_y, peers, ld, flags, epoch, status);
+    s.slice_w = slice_w;
+    return s;
+  }
   static SublayerOut of_peers(const bf16* const* peer_y, int peers, int ld, const uint32_t* flags, uint32_t epoch, uint32_t* status) {
     SublayerOut s; s.peers = peers; s.ld = ld; s.flags = flags; s.epoch = epoch; s.status = status;
     for (int r = 0; r < peers; ++r) s.peer_y[r] = peer_y[r];
@@ -57,6 +66,11 @@ cudaError_t launch_rope_kv_write(const SublayerOut& qkv, const bf16* bias, const
 // After the kernels before it on the stream have finished, stores `epoch` into slot `rank` of every rank's flag array
 // (peer_flags[r] = rank r's array as mapped into this process): "this rank's output of exchange `epoch` is complete".
 cudaError_t launch_tp_signal(uint32_t* const* peer_flags, int world, int rank, uint32_t epoch, cudaStream_t s);
+// First phase of the two-phase exchange: once flags[r] >= epoch for every rank, sums column slice `rank` (slice_w
+// columns from rank * slice_w) of every rank's bf16 [rows, H] output in rank order in fp32, rounds once and writes
+// out[rows][slice_w].
+cudaError_t launch_tp_reduce_slice(const bf16* const* peer_y, int world, int rank, int rows, int H, int slice_w, const uint32_t* flags,
+                                   uint32_t epoch, uint32_t* status, bf16* out, cudaStream_t s);
 
 cudaError_t launch_glu(const bf16* gu, int n, int F, int gelu, int interleaved, bf16* out, cudaStream_t s);
 // The same over a GEMM output in its consumer form (gu.ld must be 2 F).

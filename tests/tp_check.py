@@ -43,6 +43,13 @@ def main():
         dist.all_gather_object(out, b)
         return out
     peer_model.tp_connect(everyone)
+    # and a third one on the two-phase form of the peer exchange (each rank sums its column slice, then the slices are
+    # gathered), which models of four or more ranks take by themselves
+    os.environ["KILN_TP_TWO_PHASE"] = "1"
+    two_model = api.CudaModel(ctx, cfg, ck, max_step_tokens=256, max_step_seqs=8, tp_rank=rank, tp_world=world)
+    two_kv = api.PagedKv(ctx, two_model.kv_spec(nb, bs, tp_world=world))
+    two_model.tp_connect(everyone)
+    del os.environ["KILN_TP_TWO_PHASE"]
     g = torch.Generator().manual_seed(5)
     lens = [37, 20]
     ids, seqs, at = [], [], 0
@@ -61,6 +68,10 @@ def main():
     peer2 = peer_model.forward_step(batch2, peer_kv); ctx.sync(); peer2 = peer2.cpu().clone()
     # the same rank-ordered fp32 sum, so the same bits, whichever way the rows travelled
     peer_same = torch.equal(peer1.view(torch.int16), got1.view(torch.int16)) and torch.equal(peer2.view(torch.int16), got2.view(torch.int16))
+    dist.barrier()
+    two1 = two_model.forward_step(batch, two_kv); ctx.sync(); two1 = two1.cpu().clone()
+    two2 = two_model.forward_step(batch2, two_kv); ctx.sync(); two2 = two2.cpu().clone()
+    peer_same = peer_same and torch.equal(two1.view(torch.int16), got1.view(torch.int16)) and torch.equal(two2.view(torch.int16), got2.view(torch.int16))
     peer_all = [None] * world
     dist.all_gather_object(peer_all, bool(peer_same) and ctx.device_status() == 0)
     gathered = [None] * world
@@ -84,10 +95,11 @@ def main():
             same = torch.equal(gathered[r][0], gathered[0][0]) and torch.equal(gathered[r][1], gathered[0][1])
             print(f"rank {r} logits identical to rank 0: {same}")
             ok &= same
-        print("peer-memory exchange bit-identical to the NCCL exchange on every rank:", peer_all)
+        print("peer-memory exchange (one-phase and two-phase) bit-identical to the NCCL exchange on every rank:", peer_all)
         ok &= all(peer_all)
         print("TP CHECK", "PASSED" if ok else "FAILED", "device status", ctx.device_status())
     dist.barrier()
+    two_model.close(); two_kv.close()
     peer_model.close(); peer_kv.close()
     model.close(); kv.close(); ctx.close()
     dist.destroy_process_group()
