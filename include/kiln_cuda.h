@@ -384,8 +384,11 @@ KC_API int kc_tp_init(kc_ctx_t ctx, const void* unique_id, int32_t rank, int32_t
  * outputs are not copied at all: a one-warp kernel publishes "exchange e done" into every rank's flag array and the
  * consumer kernel (residual add + RMSNorm) reads every rank's rows where they were written, in rank order — plain
  * peer loads over NVLink, no multicast. The consumer's wait for the flags is bounded like every wait of the library
- * (KC_ERR_TIMEOUT at the next synchronisation if a rank never publishes). Without these two calls the exchange is an
- * NCCL all-gather. All ranks must run the same sequence of forwards. */
+ * (KC_ERR_TIMEOUT at the next synchronisation if a rank never publishes). From 4 ranks on the exchange takes two
+ * phases (each rank first sums its column slice of all ranks' rows, the consumer then gathers the summed slices:
+ * fewer bytes over NVLink, the same bits); the environment variable KILN_TP_TWO_PHASE = 0 / 1, read by kc_tp_attach,
+ * forces one form. Without these two calls the exchange is an NCCL all-gather. All ranks must run the same sequence
+ * of forwards. */
 #define KC_TP_EXPORT_BYTES 192
 KC_API int kc_tp_export(kc_model_t model, void* handles_out);
 KC_API int kc_tp_attach(kc_model_t model, const void* handles_all);
