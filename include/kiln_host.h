@@ -182,6 +182,46 @@ KH_API void kh_engine_spec_stats(kh_engine_t e, kh_spec_stats* out);
 KH_API kh_bm_t kh_engine_block_manager(kh_engine_t e);        /* borrowed; do not free */
 KH_API void kh_engine_cache_stats(kh_engine_t e, uint64_t* hits, uint64_t* tokens_reused, uint64_t* resident_blocks);
 
+/* ---- SSD cold tier (crates/kiln-engine/src/ssd.rs; engine hooks engine.rs:601-690, 1412-1426, 1868-2033, 2559-2704) ---- */
+
+typedef struct { uint32_t layers, kv_heads, head_dim, block_size; } kh_slab_geometry;   /* SlabGeometry (ssd.rs:61-66) */
+/* Block IO of the pool: read has the signature of kc_kv_read_block, write of kc_kv_write_block (payload per layer: K
+ * rows then V rows, paged.rs:280-304). dtype_tag is the stable on-disk tag (engine.rs:2707-2718: 7 = bfloat16). */
+typedef struct {
+  int (*read)(void* kv, uint32_t block, void* dst, size_t n);
+  int (*write)(void* kv, uint32_t block, const void* src, size_t n);
+  uint32_t dtype_tag, dtype_size;
+} kh_block_io;
+typedef struct {  /* SsdCounters (ssd.rs:94-99) + the store's totals + the engine's flush queue and SSD-served prefix hits */
+  uint64_t blocks_stored, bytes_stored, reads_total, writes_total, writes_failed_total, fingerprint_rejects_total, flush_queue_depth,
+      ssd_hits_total;
+} kh_ssd_stats;
+typedef struct { uint64_t node, generation; uint8_t hash[32]; int32_t ok; } kh_flush_ack;   /* FlushAck (ssd.rs:135-140) */
+
+/* Attaches the tier to an engine with a prefix cache: blocks donated at finish are written behind the steps
+ * (FLUSH_BATCH captures per synchronous or idle step, none during a pipelined turn), evicted blocks stay discoverable,
+ * and a new engine over the same directory finds them hash-first on its prefix walks. fingerprint: 32 bytes binding
+ * weights, architecture, dtype and block geometry; slabs that fail it are skipped with a counter. */
+KH_API int kh_engine_set_ssd(kh_engine_t e, const char* dir, const uint8_t* fingerprint, const kh_slab_geometry* g, uint64_t max_bytes,
+                             const kh_block_io* io);
+KH_API void kh_engine_ssd_sync(kh_engine_t e);                 /* Engine::sync_ssd (engine.rs:1220-1235): shutdown and tests */
+KH_API void kh_engine_ssd_stats(kh_engine_t e, kh_ssd_stats* out);
+
+/* The slab store on its own (SsdStore, ssd.rs:159-586). */
+typedef struct kh_ssd* kh_ssd_t;
+KH_API int kh_ssd_open(const char* dir, const uint8_t* fingerprint, const kh_slab_geometry* g, uint64_t max_bytes, kh_ssd_t* out);
+KH_API void kh_ssd_close(kh_ssd_t s);                          /* joins the writer thread: queued writes land first */
+KH_API int kh_ssd_contains(kh_ssd_t s, const uint8_t* hash);
+KH_API int kh_ssd_enqueue_write(kh_ssd_t s, uint64_t node, uint64_t generation, const uint8_t* hash, const uint32_t* tokens,
+                                uint64_t n_tokens, const uint8_t* payload, uint64_t n_payload, uint32_t dtype_tag, uint32_t dtype_size);
+KH_API uint64_t kh_ssd_drain_acks(kh_ssd_t s, kh_flush_ack* out, uint64_t cap);
+KH_API uint64_t kh_ssd_sync(kh_ssd_t s, kh_flush_ack* out, uint64_t cap);
+/* Returns the payload size, -1 when the slot is missing or fails verification (the index entry is then dropped),
+ * -2 when `cap` is too small. pool_dtype_tag < 0 accepts the slab's dtype. */
+KH_API int64_t kh_ssd_read(kh_ssd_t s, const uint8_t* hash, const uint32_t* expected_tokens, uint64_t n_tokens, int64_t pool_dtype_tag,
+                           uint8_t* out, uint64_t cap, uint32_t* dtype_tag);
+KH_API void kh_ssd_get_stats(kh_ssd_t s, kh_ssd_stats* out);
+
 /* ---- drafters ---- */
 
 /* Scripted drafter with seeded acceptance injection: proposal position j equals the registered continuation

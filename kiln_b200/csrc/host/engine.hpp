@@ -38,6 +38,7 @@
 
 #include "block.hpp"
 #include "radix.hpp"
+#include "ssd.hpp"
 
 namespace kh {
 
@@ -65,6 +66,14 @@ struct DecodePipelineVT {
   int (*launch)(void* model, void* kv, const uint32_t* ids, const int32_t* feed, const SeqStepC* seqs, int32_t n_seqs,
                 uint64_t* ticket);
   int (*collect)(void* model, uint64_t ticket, uint32_t* row_tokens, int32_t n);
+};
+
+// Block IO for the SSD tier: read has the signature of kc_kv_read_block, write of kc_kv_write_block (the payload order
+// of PagedKv::read_block_bytes, paged.rs:280-304); kv is the step model's pool.
+struct BlockIoVT {
+  int (*read)(void* kv, uint32_t block, void* dst, size_t n);
+  int (*write)(void* kv, uint32_t block, const void* src, size_t n);
+  uint32_t dtype_tag = 7, dtype_size = 2;   // stable on-disk tags (engine.rs:2707-2718): 7 = bfloat16
 };
 
 // Drafter seam (drafter.rs:125-147). propose writes at most `gamma` ids; a non-zero return is a DraftError.
@@ -154,7 +163,9 @@ struct Seq {  // engine.rs:470-527 (the fields this path uses)
   }
 };
 
-struct PrefixCacheStats { uint64_t hits_total = 0, tokens_reused_total = 0, resident_blocks = 0; };
+struct PrefixCacheStats { uint64_t hits_total = 0, tokens_reused_total = 0, resident_blocks = 0, ssd_hits_total = 0; };
+
+constexpr size_t FLUSH_BATCH = 8;   // blocks captured for the SSD writer per synchronous step (engine.rs:225-228)
 
 class Engine {
  public:
@@ -163,6 +174,23 @@ class Engine {
     if (cfg.prefix_cache) radix_.reset(new RadixCache(cfg.block_size, ChainHash{}));
   }
   void set_drafter(const DrafterVT& d) { drafter_ = d; has_drafter_ = true; }
+  // Attaches the SSD tier (engine.rs:1053-1076): donated blocks are written behind the steps, evicted ones stay
+  // discoverable, and a fresh engine over the same directory finds them again hash-first. Needs the prefix cache.
+  bool set_ssd(const std::string& dir, const ChainHash& fingerprint, const SlabGeometry& g, uint64_t max_bytes, const BlockIoVT& io) {
+    if (!radix_) return false;
+    store_ = SsdStore::open(dir, fingerprint, g, max_bytes);
+    io_ = io;
+    slab_geometry_ = g;
+    return store_ != nullptr;
+  }
+  SsdStore* ssd() { return store_.get(); }
+  size_t flush_queue_depth() const { return store_ ? flush_queue_.size() : 0; }
+  // Blocks until every queued write has landed and applies the acks (shutdown and tests; engine.rs:1220-1235).
+  void ssd_sync() {
+    if (!store_) return;
+    while (!flush_queue_.empty()) flush_entries(flush_queue_.size());
+    for (const FlushAck& a : store_->sync()) apply_ack(a);
+  }
   void set_pipeline(const DecodePipelineVT& p) { pipe_ = p; has_pipe_ = true; }
   void clear_pipeline() { has_pipe_ = false; }  // a step already in flight is still read back at the next turn
   uint64_t pipelined_steps() const { return pipelined_total_; }  // engine.rs:1160-1163
@@ -224,13 +252,17 @@ class Engine {
       bool still = false;
       int rc = pipelined_turn(prev, &still);
       if (rc != 0) { fail_all(err_); return rc; }
-      if (still) return 0;  // a new step is in flight (or its rows were all dropped): the turn is complete
+      if (still) { cache_io_tick(0); return 0; }  // a new step is in flight: only the (cheap) write acks are applied
     }
     sweep_cancelled();
     admit();
-    if (running_.empty()) return 0;
+    if (running_.empty()) {
+      cache_io_tick(FLUSH_BATCH);   // idle: write-behind progress never depends on new traffic
+      return 0;
+    }
     int rc = run_iteration();
     if (rc != 0) fail_all(err_);
+    else if (!has_inflight_) cache_io_tick(FLUSH_BATCH);
     return rc;
   }
 
@@ -300,10 +332,11 @@ class Engine {
     const size_t limit = seq.prompt.size() - 1;  // the last prompt token is always computed
     size_t cur = RADIX_ROOT;
     std::vector<uint32_t> walked;
+    bool from_ssd = false;
     while ((walked.size() + 1) * bs <= limit) {
       const size_t at = walked.size() * bs;
       std::vector<uint32_t> chunk(seq.prompt.begin() + at, seq.prompt.begin() + at + bs);
-      const int64_t node = radix_->child(cur, chunk);
+      const int64_t node = resolve_chunk(cur, chunk, &from_ssd);
       if (node < 0) break;
       const int64_t block = radix_->node_block((size_t)node);
       if (block < 0) break;
@@ -322,6 +355,19 @@ class Engine {
       for (size_t node : radix_->full_children(cur)) if (starts_with(radix_->node_tokens(node))) { cand = (int64_t)node; break; }
       if (cand < 0)
         for (size_t node : radix_->partial_children(cur)) if (starts_with(radix_->node_tokens(node))) { cand = (int64_t)node; break; }
+      if (cand < 0 && store_ && seq.prompt.size() >= d_full + bs) {
+        // hash-first discovery needs a full chunk's tokens, which the request has when exactly one position is left
+        const std::vector<uint32_t> chunk(seq.prompt.begin() + d_full, seq.prompt.begin() + d_full + bs);
+        if (store_->contains(radix_->chain_hash_of(cur, chunk.data(), chunk.size()))) {
+          cand = (int64_t)radix_->insert_child(cur, chunk);
+          radix_->set_on_ssd((size_t)cand);
+        }
+      }
+      if (cand >= 0 && radix_->node_block((size_t)cand) < 0 && !radix_->node_is_partial((size_t)cand) && radix_->node_on_ssd((size_t)cand) && store_) {
+        const std::vector<uint32_t> toks = radix_->node_tokens((size_t)cand);
+        if (load_from_ssd((size_t)cand, toks)) from_ssd = true;
+        else cand = -1;   // the node was pruned
+      }
       if (cand >= 0 && radix_->node_block((size_t)cand) >= 0) {
         radix_->touch((size_t)cand);
         tail = (uint32_t)radix_->node_block((size_t)cand);
@@ -358,6 +404,72 @@ class Engine {
     seq.cached_tokens = std::max<uint32_t>(seq.cached_tokens, (uint32_t)served);
     cache_stats_.hits_total++;
     cache_stats_.tokens_reused_total += served;
+    if (from_ssd) cache_stats_.ssd_hits_total++;
+  }
+
+  // engine.rs:1412-1426: apply writer acks, capture up to `captures` queued blocks.
+  void cache_io_tick(size_t captures) {
+    if (!store_) return;
+    for (const FlushAck& a : store_->drain_acks()) apply_ack(a);
+    if (captures > 0) flush_entries(captures);
+  }
+  void apply_ack(const FlushAck& ack) {  // engine.rs:2693-2704
+    if (!radix_->is_live(ack.node, ack.generation) || radix_->node_hash(ack.node) != ack.hash) return;
+    if (ack.ok) radix_->set_on_ssd(ack.node);
+    else radix_->clear_flush_pending(ack.node);   // a later donation may retry
+  }
+  size_t flush_entries(size_t max) {  // engine.rs:2645-2690
+    size_t flushed = 0;
+    while (flushed < max && !flush_queue_.empty()) {
+      const auto [node, generation] = flush_queue_.front();
+      flush_queue_.pop_front();
+      if (!radix_->is_live(node, generation) || radix_->node_on_ssd(node) || radix_->flush_pending(node)) continue;
+      const int64_t block = radix_->node_block(node);
+      if (block < 0) continue;
+      std::vector<uint8_t> payload(slab_geometry_.payload_bytes(io_.dtype_size));
+      if (!io_.read || io_.read(model_.kv, (uint32_t)block, payload.data(), payload.size()) != 0) continue;   // silent skip
+      const auto& toks = radix_->node_tokens(node);
+      store_->enqueue_write(FlushTicket{node, generation, radix_->node_hash(node)}, toks.data(), toks.size(), std::move(payload), io_.dtype_tag,
+                            io_.dtype_size);
+      radix_->set_flush_pending(node);
+      flushed++;
+    }
+    return flushed;
+  }
+  // engine.rs:2596-2640: pulls one persisted block into the pool for a non-resident node; failures are silent.
+  bool load_from_ssd(size_t node, const std::vector<uint32_t>& chunk) {
+    std::vector<uint8_t> payload;
+    uint32_t tag = 0;
+    if (!store_->read(radix_->node_hash(node), chunk.data(), chunk.size(), (int64_t)io_.dtype_tag, &payload, &tag)) {
+      radix_->prune_subtree(mgr_, node);   // the store dropped its entry: drop the dead subtree too
+      return false;
+    }
+    uint32_t block = 0;
+    if (!mgr_.allocate(&block).ok()) {
+      if (!evict_one() || !mgr_.allocate(&block).ok()) return false;   // the pool is full of live requests: a miss
+    }
+    if (!io_.write || io_.write(model_.kv, block, payload.data(), payload.size()) != 0) {
+      mgr_.release(block);
+      return false;
+    }
+    radix_->set_resident(node, block);
+    return true;
+  }
+  // engine.rs:2559-2594: the child of `cur` keyed by `chunk` for a match walk — an existing node, or hash-first discovery
+  // from the SSD index — made resident; -1 stops the walk.
+  int64_t resolve_chunk(size_t cur, const std::vector<uint32_t>& chunk, bool* from_ssd) {
+    int64_t node = radix_->child(cur, chunk);
+    if (node < 0) {
+      if (!store_ || !store_->contains(radix_->chain_hash_of(cur, chunk.data(), chunk.size()))) return -1;
+      node = (int64_t)radix_->insert_child(cur, chunk);
+      radix_->set_on_ssd((size_t)node);
+    }
+    if (radix_->node_block((size_t)node) < 0) {
+      if (!radix_->node_on_ssd((size_t)node) || !store_) { radix_->prune_subtree(mgr_, (size_t)node); return -1; }
+      if (!load_from_ssd((size_t)node, chunk)) return -1;
+      *from_ssd = true;
+    }
+    return node;
   }
 
   int find_running(uint64_t arrival) const {
@@ -600,6 +712,7 @@ class Engine {
       } else {
         const size_t node = radix_->insert_child(cur, chunk);
         radix_->set_resident(node, block);
+        if (store_ && store_->contains(radix_->node_hash(node))) radix_->set_on_ssd(node);   // a previous run persisted it
         std::vector<size_t> covered;
         for (size_t partial : radix_->partial_children(cur)) {
           const auto& t = radix_->node_tokens(partial);
@@ -608,6 +721,7 @@ class Engine {
         for (size_t partial : covered) radix_->prune_subtree(mgr_, partial);
         cur = node;
       }
+      if (store_ && !radix_->node_on_ssd(cur) && !radix_->flush_pending(cur)) flush_queue_.push_back({cur, radix_->node_generation(cur)});
     }
   }
   void donate_partial(size_t parent, uint32_t block, const std::vector<uint32_t>& tokens) {  // engine.rs:694-731
@@ -835,6 +949,7 @@ class Engine {
     running_.clear();
     waiting_.clear();
     has_inflight_ = false;  // engine.rs:2521
+    flush_queue_.clear();
     mgr_ = BlockManager(cfg_.num_blocks, cfg_.block_size);
     if (radix_) radix_->reset();
   }
@@ -843,6 +958,10 @@ class Engine {
   StepModelVT model_;
   DrafterVT drafter_{};
   bool has_drafter_ = false;
+  std::unique_ptr<SsdStore> store_;
+  BlockIoVT io_{};
+  SlabGeometry slab_geometry_{};
+  std::deque<std::pair<size_t, uint64_t>> flush_queue_;   // (node, generation) awaiting capture
   DecodePipelineVT pipe_{};
   bool has_pipe_ = false, has_inflight_ = false;
   InFlight inflight_;

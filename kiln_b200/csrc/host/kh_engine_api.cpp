@@ -1,6 +1,8 @@
 // C ABI of the engine and the drafters (declared in include/kiln_host.h).
 #include "../../../include/kiln_host.h"
 
+#include <cstring>
+#include <memory>
 #include <string>
 
 #include "engine.hpp"
@@ -72,6 +74,81 @@ int kh_engine_set_pipeline(kh_engine_t e, const kh_decode_pipeline* p) {
   return KH_OK;
 }
 uint64_t kh_engine_pipelined_steps(kh_engine_t e) { return e->e->pipelined_steps(); }
+
+static ChainHash hash_of(const uint8_t* p) {
+  ChainHash h;
+  memcpy(h.data(), p, 32);
+  return h;
+}
+int kh_engine_set_ssd(kh_engine_t e, const char* dir, const uint8_t* fingerprint, const kh_slab_geometry* g, uint64_t max_bytes,
+                      const kh_block_io* io) {
+  if (!e || !dir || !fingerprint || !g || !io || !io->read || !io->write || io->dtype_size == 0 || io->dtype_size > 8) return KH_ERR_ARG;
+  SlabGeometry sg;
+  sg.layers = g->layers; sg.kv_heads = g->kv_heads; sg.head_dim = g->head_dim; sg.block_size = g->block_size;
+  BlockIoVT vt;
+  vt.read = io->read; vt.write = io->write; vt.dtype_tag = io->dtype_tag; vt.dtype_size = io->dtype_size;
+  return e->e->set_ssd(dir, hash_of(fingerprint), sg, max_bytes, vt) ? KH_OK : KH_ERR_ARG;
+}
+void kh_engine_ssd_sync(kh_engine_t e) { e->e->ssd_sync(); }
+void kh_engine_ssd_stats(kh_engine_t e, kh_ssd_stats* out) {
+  memset(out, 0, sizeof *out);
+  SsdStore* s = e->e->ssd();
+  if (!s) return;
+  out->blocks_stored = s->blocks_stored(); out->bytes_stored = s->bytes_stored();
+  out->reads_total = s->counters().reads_total; out->writes_total = s->counters().writes_total;
+  out->writes_failed_total = s->counters().writes_failed_total; out->fingerprint_rejects_total = s->counters().fingerprint_rejects_total;
+  out->flush_queue_depth = e->e->flush_queue_depth();
+  out->ssd_hits_total = e->e->cache_stats().ssd_hits_total;
+}
+
+// ---- the slab store on its own (ssd.rs unit tests drive it like this) ----
+struct kh_ssd { std::unique_ptr<SsdStore> s; };
+int kh_ssd_open(const char* dir, const uint8_t* fingerprint, const kh_slab_geometry* g, uint64_t max_bytes, kh_ssd_t* out) {
+  if (!dir || !fingerprint || !g || !out) return KH_ERR_ARG;
+  SlabGeometry sg;
+  sg.layers = g->layers; sg.kv_heads = g->kv_heads; sg.head_dim = g->head_dim; sg.block_size = g->block_size;
+  std::unique_ptr<SsdStore> s = SsdStore::open(dir, hash_of(fingerprint), sg, max_bytes);
+  if (!s) return KH_ERR_ARG;
+  *out = new kh_ssd{std::move(s)};
+  return KH_OK;
+}
+void kh_ssd_close(kh_ssd_t s) { delete s; }
+int kh_ssd_contains(kh_ssd_t s, const uint8_t* hash) { return s->s->contains(hash_of(hash)) ? 1 : 0; }
+int kh_ssd_enqueue_write(kh_ssd_t s, uint64_t node, uint64_t generation, const uint8_t* hash, const uint32_t* tokens, uint64_t n_tokens,
+                         const uint8_t* payload, uint64_t n_payload, uint32_t dtype_tag, uint32_t dtype_size) {
+  if (!s || !hash || !payload || dtype_size == 0) return KH_ERR_ARG;
+  s->s->enqueue_write(FlushTicket{(size_t)node, generation, hash_of(hash)}, tokens, n_tokens, std::vector<uint8_t>(payload, payload + n_payload),
+                      dtype_tag, dtype_size);
+  return KH_OK;
+}
+static uint64_t copy_acks(const std::vector<FlushAck>& acks, kh_flush_ack* out, uint64_t cap) {
+  uint64_t n = 0;
+  for (const FlushAck& a : acks) {
+    if (n >= cap) break;
+    out[n].node = a.node; out[n].generation = a.generation; out[n].ok = a.ok ? 1 : 0;
+    memcpy(out[n].hash, a.hash.data(), 32);
+    ++n;
+  }
+  return n;
+}
+uint64_t kh_ssd_drain_acks(kh_ssd_t s, kh_flush_ack* out, uint64_t cap) { return copy_acks(s->s->drain_acks(), out, cap); }
+uint64_t kh_ssd_sync(kh_ssd_t s, kh_flush_ack* out, uint64_t cap) { return copy_acks(s->s->sync(), out, cap); }
+int64_t kh_ssd_read(kh_ssd_t s, const uint8_t* hash, const uint32_t* expected_tokens, uint64_t n_tokens, int64_t pool_dtype_tag, uint8_t* out,
+                    uint64_t cap, uint32_t* dtype_tag) {
+  std::vector<uint8_t> payload;
+  uint32_t tag = 0;
+  if (!s->s->read(hash_of(hash), expected_tokens, n_tokens, pool_dtype_tag, &payload, &tag)) return -1;
+  if (payload.size() > cap) return -2;
+  memcpy(out, payload.data(), payload.size());
+  if (dtype_tag) *dtype_tag = tag;
+  return (int64_t)payload.size();
+}
+void kh_ssd_get_stats(kh_ssd_t s, kh_ssd_stats* out) {
+  memset(out, 0, sizeof *out);
+  out->blocks_stored = s->s->blocks_stored(); out->bytes_stored = s->s->bytes_stored();
+  out->reads_total = s->s->counters().reads_total; out->writes_total = s->s->counters().writes_total;
+  out->writes_failed_total = s->s->counters().writes_failed_total; out->fingerprint_rejects_total = s->s->counters().fingerprint_rejects_total;
+}
 int kh_engine_submit(kh_engine_t e, const uint32_t* prompt, uint64_t n, uint64_t max_tokens, const uint32_t* stop_tokens,
                      uint64_t n_stop, uint64_t* arrival_out) {
   if (!e || (!prompt && n)) return KH_ERR_ARG;

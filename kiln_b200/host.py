@@ -60,6 +60,27 @@ class KhDraftBackend(C.Structure):
     _fields_ = [("model", _P), ("kv", _P), ("forward", VERIFY_FN), ("chain", CHAIN_FN), ("max_chunk", C.c_int32)]
 
 
+class KhSlabGeometry(C.Structure):
+    _fields_ = [("layers", C.c_uint32), ("kv_heads", C.c_uint32), ("head_dim", C.c_uint32), ("block_size", C.c_uint32)]
+
+
+BLOCK_READ_FN = C.CFUNCTYPE(C.c_int, _P, C.c_uint32, _P, C.c_size_t)
+BLOCK_WRITE_FN = C.CFUNCTYPE(C.c_int, _P, C.c_uint32, _P, C.c_size_t)
+
+
+class KhBlockIo(C.Structure):
+    _fields_ = [("read", BLOCK_READ_FN), ("write", BLOCK_WRITE_FN), ("dtype_tag", C.c_uint32), ("dtype_size", C.c_uint32)]
+
+
+class KhSsdStats(C.Structure):
+    _fields_ = [(n, C.c_uint64) for n in ("blocks_stored", "bytes_stored", "reads_total", "writes_total", "writes_failed_total",
+                                          "fingerprint_rejects_total", "flush_queue_depth", "ssd_hits_total")]
+
+
+class KhFlushAck(C.Structure):
+    _fields_ = [("node", C.c_uint64), ("generation", C.c_uint64), ("hash", C.c_uint8 * 32), ("ok", C.c_int32)]
+
+
 class KhEngineConfig(C.Structure):
     _fields_ = [("block_size", C.c_int32), ("num_blocks", C.c_int32), ("max_batch_tokens", C.c_int32),
                 ("prefill_chunk", C.c_int32), ("prefill_fine_chunk", C.c_int32), ("prefix_cache", C.c_int32),
@@ -117,6 +138,14 @@ _SIGNATURES = {
                                       _U32P, _U32P, C.POINTER(_I32), _U32P]),
     "kh_engine_spec_stats": (None, [_P, C.POINTER(KhSpecStats)]), "kh_engine_block_manager": (_P, [_P]),
     "kh_engine_cache_stats": (None, [_P, C.POINTER(_U64), C.POINTER(_U64), C.POINTER(_U64)]),
+    "kh_engine_set_ssd": (C.c_int, [_P, C.c_char_p, C.c_char_p, C.POINTER(KhSlabGeometry), _U64, C.POINTER(KhBlockIo)]),
+    "kh_engine_ssd_sync": (None, [_P]), "kh_engine_ssd_stats": (None, [_P, C.POINTER(KhSsdStats)]),
+    "kh_ssd_open": (C.c_int, [C.c_char_p, C.c_char_p, C.POINTER(KhSlabGeometry), _U64, C.POINTER(_P)]), "kh_ssd_close": (None, [_P]),
+    "kh_ssd_contains": (C.c_int, [_P, C.c_char_p]),
+    "kh_ssd_enqueue_write": (C.c_int, [_P, _U64, _U64, C.c_char_p, _U32P, _U64, C.c_char_p, _U64, C.c_uint32, C.c_uint32]),
+    "kh_ssd_drain_acks": (_U64, [_P, C.POINTER(KhFlushAck), _U64]), "kh_ssd_sync": (_U64, [_P, C.POINTER(KhFlushAck), _U64]),
+    "kh_ssd_read": (_I64, [_P, C.c_char_p, _U32P, _U64, _I64, C.c_char_p, _U64, C.POINTER(C.c_uint32)]),
+    "kh_ssd_get_stats": (None, [_P, C.POINTER(KhSsdStats)]),
     "kh_scripted_create": (C.c_int, [C.c_double, _U64, C.c_uint32, C.POINTER(_P)]), "kh_scripted_free": (None, [_P]),
     "kh_scripted_set_continuation": (C.c_int, [_P, _U64, _U32P, _U64]), "kh_scripted_vtable": (None, [_P, C.POINTER(KhDrafter)]),
     "kh_draft_model_create": (C.c_int, [C.POINTER(KhDraftBackend), _U64, _U64, C.POINTER(_P)]),
@@ -584,6 +613,66 @@ class DraftModel(Drafter):
             pass
 
 
+class SsdStore:
+    """SsdStore (ssd.rs:159-586) on its own: slab files under `directory`, index rebuilt from their headers on open."""
+
+    def __init__(self, directory: str, fingerprint: bytes, layers: int, kv_heads: int, head_dim: int, block_size: int,
+                 max_bytes: int = 1 << 40):
+        assert len(fingerprint) == 32
+        self.geometry = KhSlabGeometry(layers, kv_heads, head_dim, block_size)
+        self._h = _P()
+        _check(lib().kh_ssd_open(str(directory).encode(), bytes(fingerprint), C.byref(self.geometry), max_bytes, C.byref(self._h)))
+
+    def payload_bytes(self, dtype_size: int) -> int:
+        g = self.geometry
+        return g.layers * 2 * g.kv_heads * g.block_size * g.head_dim * dtype_size
+
+    def contains(self, chain_hash: bytes) -> bool:
+        return bool(lib().kh_ssd_contains(self._h, bytes(chain_hash)))
+
+    def enqueue_write(self, node: int, generation: int, chain_hash: bytes, tokens: Sequence[int], payload: bytes, dtype_tag: int = 7,
+                      dtype_size: int = 2) -> None:
+        a, p = _u32(tokens)
+        _check(lib().kh_ssd_enqueue_write(self._h, node, generation, bytes(chain_hash), p, len(a), bytes(payload), len(payload),
+                                          dtype_tag, dtype_size))
+
+    def _acks(self, fn):
+        buf = (KhFlushAck * 256)()
+        n = fn(self._h, buf, 256)
+        return [(int(buf[i].node), int(buf[i].generation), bytes(buf[i].hash), bool(buf[i].ok)) for i in range(n)]
+
+    def drain_acks(self):
+        return self._acks(lib().kh_ssd_drain_acks)
+
+    def sync(self):
+        return self._acks(lib().kh_ssd_sync)
+
+    def read(self, chain_hash: bytes, expected_tokens: Sequence[int], pool_dtype_tag: int = -1, dtype_size: int = 2):
+        """(payload, dtype tag) or None when the slot is missing or fails verification."""
+        a, p = _u32(expected_tokens)
+        cap = self.payload_bytes(8)
+        buf = C.create_string_buffer(cap)
+        tag = C.c_uint32(0)
+        n = lib().kh_ssd_read(self._h, bytes(chain_hash), p, len(a), pool_dtype_tag, buf, cap, C.byref(tag))
+        return None if n < 0 else (buf.raw[:n], int(tag.value))
+
+    def stats(self) -> dict:
+        s = KhSsdStats()
+        lib().kh_ssd_get_stats(self._h, C.byref(s))
+        return {n: int(getattr(s, n)) for n, _ in KhSsdStats._fields_}
+
+    def close(self) -> None:
+        if self._h:
+            lib().kh_ssd_close(self._h)
+            self._h = _P()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 FINISH_KINDS = {0: None, 1: "stop", 2: "length", 3: "error", 4: "cancelled"}
 
 
@@ -614,6 +703,48 @@ class Engine:
     def set_drafter(self, drafter: Drafter) -> None:
         self._drafter = drafter
         _check(lib().kh_engine_set_drafter(self._h, C.byref(drafter.c)))
+
+    def set_ssd(self, directory: str, fingerprint: bytes, layers: int, kv_heads: int, head_dim: int, max_bytes: int = 1 << 40,
+                read_block=None, write_block=None, kv=None, dtype_tag: int = 7, dtype_size: int = 2) -> None:
+        """Attaches the SSD tier (kh_engine_set_ssd). With ``kv`` (an api.PagedKv) the block IO is kc_kv_read_block /
+        kc_kv_write_block on the model's pool; otherwise read_block(block) -> bytes and write_block(block, bytes) are
+        Python callables (fake models)."""
+        g = KhSlabGeometry(layers, kv_heads, head_dim, self.config.block_size)
+        io = KhBlockIo()
+        if kv is not None:
+            from . import _lib as L
+            cl = L.lib()
+            io.read, io.write = C.cast(cl.kc_kv_read_block, BLOCK_READ_FN), C.cast(cl.kc_kv_write_block, BLOCK_WRITE_FN)
+            self._ssd_keep = (kv,)
+        else:
+            def _r(_kv, block, dst, n):
+                try:
+                    data = read_block(int(block))
+                    if len(data) != n:
+                        return 2
+                    C.memmove(dst, data, n)
+                    return 0
+                except Exception:
+                    return 2
+
+            def _w(_kv, block, src, n):
+                try:
+                    write_block(int(block), C.string_at(src, n))
+                    return 0
+                except Exception:
+                    return 2
+            io.read, io.write = BLOCK_READ_FN(_r), BLOCK_WRITE_FN(_w)
+            self._ssd_keep = (io.read, io.write, read_block, write_block)
+        io.dtype_tag, io.dtype_size = dtype_tag, dtype_size
+        _check(lib().kh_engine_set_ssd(self._h, str(directory).encode(), bytes(fingerprint), C.byref(g), max_bytes, C.byref(io)))
+
+    def ssd_sync(self) -> None:
+        lib().kh_engine_ssd_sync(self._h)
+
+    def ssd_stats(self) -> dict:
+        s = KhSsdStats()
+        lib().kh_engine_ssd_stats(self._h, C.byref(s))
+        return {n: int(getattr(s, n)) for n, _ in KhSsdStats._fields_}
 
     def set_pipelined(self, on: bool) -> None:
         """Turns pipelined plain decode on (the model must offer launch/collect) or off."""

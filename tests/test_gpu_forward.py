@@ -315,6 +315,40 @@ def test_stream_lane_decode_logits_match_oracle(ctx, name):
     model.set_stream_lane(False)
 
 
+def test_ssd_tier_warm_restart_on_the_device(ctx, tmp_path):
+    """Blocks donated at finish are captured with kc_kv_read_block, written behind the steps, and a second engine over
+    a zeroed pool and the same slab directory reloads them with kc_kv_write_block: the same tokens as a cold run, the
+    prompt served from the slabs (engine.rs:2559-2704; payload order of paged.rs:280-304)."""
+    from kiln_b200 import host
+    cfg, model, kv, _, _ = load(ctx, "tiny-llama")
+    p = prompts(cfg, [50], 12)[0]
+
+    def engine(directory):
+        ec = host.EngineConfig(block_size=BS, num_blocks=64, max_batch_tokens=256, prefill_chunk=64, prefill_fine_chunk=16,
+                               prefix_cache=True, deterministic_decode_width=32, gamma=0, spec_max_batch=4,
+                               spec_min_acceptance=0.0, max_key_len=0, batch_verify=True)
+        eng = host.Engine(ec, host.StepModel.from_cuda(model, kv))
+        eng.set_ssd(str(directory), b"\x11" * 32, cfg.num_hidden_layers, cfg.num_key_value_heads, cfg.head_dim, kv=kv)
+        return eng
+
+    kv.reset()
+    eng = engine(tmp_path / "slabs")
+    a = eng.submit(p, 12)
+    cold = eng.run_to_completion([a])[a]
+    eng.ssd_sync()
+    settled = len(p) - 1 + 12
+    assert eng.ssd_stats()["blocks_stored"] == settled // BS
+    del eng
+    kv.reset()                                   # the pools are zero again: nothing survives but the slab files
+    eng = engine(tmp_path / "slabs")
+    a = eng.submit(p, 12)
+    warm = eng.run_to_completion([a])[a]
+    assert warm == cold
+    assert eng.seq_state(a).cached_tokens == (len(p) - 1) // BS * BS
+    assert eng.ssd_stats()["reads_total"] == (len(p) - 1) // BS and eng.ssd_stats()["ssd_hits_total"] == 1
+    assert ctx.device_status() == 0
+
+
 def test_invalid_batches_are_rejected(ctx):
     """Validation mirrors nn.rs:1309-1337; errors come back as status + message, never an abort."""
     cfg, model, kv, _, _ = load(ctx, "tiny-llama")
