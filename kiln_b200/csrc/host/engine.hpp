@@ -7,7 +7,9 @@
 //                                      match_head_prefix (1294-1363, 1367-1407, 1508-1634,
 //                                      1802-2033, 2035-2417, 2736-2796, 601-778, 907-963),
 //                                      pipelined_turn, pipeline_ok, build_pipelined,
-//                                      apply_inflight (1428-1475, 1656-1766)
+//                                      apply_inflight (1428-1475, 1656-1766); cache_io_tick,
+//                                      resolve_chunk, load_from_ssd, flush_entries, apply_ack
+//                                      (1412-1426, 2559-2704) over the slab store of ssd.hpp
 //   crates/kiln-engine/src/drafter.rs  spec_gamma_at_width, trait Drafter (62-70, 125-147)
 //   crates/kiln-models/src/draft.rs    DraftModel::{begin, propose, release} (268-411)
 // The model and the drafter sit behind C function tables (the StepModel / Drafter
@@ -23,7 +25,7 @@
 // dispatch (VERIFY_MAX_KEY_LEN, deterministic width, per-model gamma) are inputs here.
 //
 // Out of scope (not on the verify path): preemption under pool exhaustion, priorities,
-// cancellation tokens, penalties, grammars, stochastic samplers, the SSD tier. A step
+// cancellation tokens, penalties, grammars, stochastic samplers. A step
 // that cannot get blocks for a plain decode slot returns a capacity error.
 #pragma once
 
