@@ -180,3 +180,47 @@ def test_donated_blocks_are_written_behind_and_survive_eviction_and_restart(tmp_
     assert eng3.ssd_stats()["blocks_stored"] == 0 and eng3.ssd_stats()["fingerprint_rejects_total"] >= 1
     a, toks = run(eng3, p, 8)
     assert toks == truth and eng3.seq_state(a).cached_tokens == 0
+
+
+def test_store_against_a_shadow_dictionary(tmp_path):
+    """Random interleavings of writes, acknowledgement drains, reads and restarts against a dictionary: a block is
+    readable exactly from the moment its acknowledgement has been applied, survives a restart, and rewriting a hash makes
+    the later slot win."""
+    from hypothesis import given, settings, strategies as st
+
+    ops = st.lists(st.tuples(st.sampled_from(["write", "sync", "read", "reopen"]), st.integers(0, 11), st.integers(0, 255)),
+                   min_size=1, max_size=40)
+    counter = [0]
+
+    @settings(max_examples=25, deadline=None)
+    @given(ops)
+    def run(seq):
+        counter[0] += 1
+        d = tmp_path / f"case{counter[0]}"
+        store = open_store(d)
+        committed, pending = {}, {}
+        hash_of = lambda i: struct.pack("<I", i) + b"\x33" * 28
+        for op, i, seed in seq:
+            if op == "write":
+                store.enqueue_write(i, 1, hash_of(i), [i, i + 1, i + 2, i + 3], payload(seed), 3, 2)
+                pending[i] = seed
+            elif op == "sync":
+                acks = store.sync()
+                assert all(a[3] for a in acks)
+                committed.update(pending)
+                pending.clear()
+            elif op == "read":
+                got = store.read(hash_of(i), [i, i + 1, i + 2, i + 3], 3)
+                if i in committed and i not in pending:
+                    assert got == (payload(committed[i]), 3)
+                elif i not in committed and i not in pending:
+                    assert got is None
+            else:
+                store.close()                       # joins the writer: queued writes land, and the scan finds them
+                committed.update(pending)
+                pending.clear()
+                store = open_store(d)
+                assert store.stats()["blocks_stored"] == len(committed)
+        store.close()
+
+    run()
