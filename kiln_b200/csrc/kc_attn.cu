@@ -114,10 +114,12 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap kvmap, const AttnParams 
     for (int i = 0; i < ATT_STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], MT); }
     mbar_fence_init();
   }
-  // Stage Q: row r = token (r / gqa), head-in-group (r % gqa); dead rows are zero.
-  {
+  __syncthreads();
+  // The producer starts on the K/V tiles at once; the consumer warps stage Q meanwhile (its load latency then hides
+  // under that of the first tiles). Row r = token (r / gqa), head-in-group (r % gqa); dead rows are zero.
+  if (warp < CW) {
     const int chunks_per_row = D / 8;
-    for (int i = threadIdx.x; i < MT * 16 * chunks_per_row; i += blockDim.x) {
+    for (int i = threadIdx.x; i < MT * 16 * chunks_per_row; i += CW * 32) {
       const int r = i / chunks_per_row, ch = i % chunks_per_row;
       uint4 v = make_uint4(0, 0, 0, 0);
       if (r < rows) {
@@ -126,8 +128,8 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap kvmap, const AttnParams 
       }
       *reinterpret_cast<uint4*>(sQ + r * S::Q_LD + ch * 16) = v;
     }
+    named_bar_sync(1, CW * 32);
   }
-  __syncthreads();
 
   if (warp == CW) {
     // ---- producer: one TMA per K+V tile pair (4-D map), or one per 64-feature slab of a K or V tile (2-D map). The chunk's block-table entries (at most
@@ -208,6 +210,21 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap kvmap, const AttnParams 
       const int key0 = key_base + t * 16;
       float tmax_lo = -INFINITY, tmax_hi = -INFINITY;
       bool v[2][4];
+      // Every key of the tile is visible to every live row (the rows' positions start at pos0), no window, no softcap:
+      // the same arithmetic without the per-element predicates. Dead rows then carry finite garbage nobody stores.
+      if (p.window == 0 && p.softcap == 0.f && key0 + 15 <= pos0) {
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float x = s[nt][j] * p.scale;
+            x *= 1.4426950408889634f;
+            v[nt][j] = true;
+            s[nt][j] = x;
+            if (j >= 2) tmax_hi = fmaxf(tmax_hi, x); else tmax_lo = fmaxf(tmax_lo, x);
+          }
+        }
+      } else
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
