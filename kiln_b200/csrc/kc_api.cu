@@ -151,7 +151,7 @@ struct Layer {
 
 // Per-step metadata, packed on the host and copied to the device in one transfer.
 struct MetaLayout {
-  size_t tokens, token_pos, kv_slot, sampled, tables, work, units, units_win, v_row_off, v_draft_off, v_draft_len, v_draft, feed, total;
+  size_t tokens, token_pos, kv_slot, sampled, tables, work, v_row_off, v_draft_off, v_draft_len, v_draft, feed, total;
 };
 
 struct kc_model {
@@ -980,7 +980,6 @@ namespace {
 
 struct StepPlan {
   int n = 0, n_seqs = 0, n_sampled = 0, max_blocks = 0, n_work = 0, tokens_per_item = 1, max_chunks = 1;
-  int n_units = 0, n_units_win = 0;   // attention CTAs per kv head: (work item, key chunk) pairs, all layers / windowed layers
   int max_len = 1;
   MetaLayout lay{};
 };
@@ -1022,14 +1021,7 @@ int validate_step(kc_model* m, kc_kv* kv, const uint32_t* token_ids, int32_t n, 
   if (p.n_sampled > m->logit_rows) return fail(KC_ERR_INVALID, "step samples %d rows; at most %d", p.n_sampled, m->logit_rows);
   const int gqa = m->d.num_heads / m->d.num_kv_heads;
   p.tokens_per_item = attn_tokens_per_item(gqa, p.max_len);
-  for (int i = 0; i < n_seqs; ++i) {
-    p.n_work += (seqs[i].len + p.tokens_per_item - 1) / p.tokens_per_item;
-    for (int t = 0; t < seqs[i].len; t += p.tokens_per_item) {
-      const int pos0 = seqs[i].offset + t, pos_max = pos0 + std::min(p.tokens_per_item, seqs[i].len - t) - 1;
-      p.n_units += pos_max / ATT_CHUNK + 1;
-      if (m->d.sliding_window > 0) p.n_units_win += pos_max / ATT_CHUNK + 1 - std::max(0, pos0 - m->d.sliding_window + 1) / ATT_CHUNK;
-    }
-  }
+  for (int i = 0; i < n_seqs; ++i) p.n_work += (seqs[i].len + p.tokens_per_item - 1) / p.tokens_per_item;
   p.max_chunks = (max_ctx + ATT_CHUNK - 1) / ATT_CHUNK;
   MetaLayout& L = p.lay;
   size_t at = 0;
@@ -1038,8 +1030,6 @@ int validate_step(kc_model* m, kc_kv* kv, const uint32_t* token_ids, int32_t n, 
   L.sampled = put((size_t)std::max(1, p.n_sampled) * 4);
   L.tables = put((size_t)n_seqs * p.max_blocks * 4);
   L.work = put((size_t)p.n_work * 16);
-  L.units = put((size_t)p.n_units * 16);
-  L.units_win = put((size_t)std::max(1, p.n_units_win) * 16);
   L.v_row_off = put((size_t)n_seqs * 4); L.v_draft_off = put((size_t)n_seqs * 4); L.v_draft_len = put((size_t)n_seqs * 4);
   L.v_draft = put((size_t)n * 4);
   L.feed = put((size_t)n * 4);
@@ -1102,30 +1092,6 @@ int upload_meta(kc_model* m, kc_kv* kv, const uint32_t* token_ids, const kc_seq_
     for (int t = s.len - s.sample_rows + 1; t < s.len; ++t) v_draft[dat++] = token_ids[row + t];
     row += s.len;
   }
-  // Attention units: one CTA per (work item, key chunk, kv head). The grid walks the list in order, so the units are
-  // sorted by the keys they hold, longest first: the CTAs that start last are the short ones, and the kernel's tail
-  // is a fraction of a full chunk instead of a whole one. Which CTA computes what does not change a bit of any row.
-  {
-    struct Unit { int keys, item, chunk; };
-    auto build = [&](int window, size_t off, int expect) {
-      std::vector<Unit> u;
-      u.reserve((size_t)expect);
-      for (int it = 0; it < p.n_work; ++it) {
-        const int qlen = work[4 * it + 2], pos0 = work[4 * it + 3], pos_max = pos0 + qlen - 1;
-        const int c_lo = window > 0 ? std::max(0, pos0 - window + 1) / ATT_CHUNK : 0;
-        for (int ch = c_lo; ch <= pos_max / ATT_CHUNK; ++ch) u.push_back(Unit{std::min(ATT_CHUNK, pos_max + 1 - ch * ATT_CHUNK), it, ch});
-      }
-      std::stable_sort(u.begin(), u.end(), [](const Unit& a, const Unit& b) { return a.keys > b.keys; });
-      int32_t* dst = reinterpret_cast<int32_t*>(hbuf + off);
-      for (size_t k = 0; k < u.size() && (int)k < expect; ++k) {
-        const int it = u[k].item;
-        dst[4 * k + 0] = work[4 * it + 0] | (u[k].chunk << 16);   // sequence (its block table row) and chunk
-        dst[4 * k + 1] = work[4 * it + 1]; dst[4 * k + 2] = work[4 * it + 2]; dst[4 * k + 3] = work[4 * it + 3];
-      }
-    };
-    build(0, L.units, p.n_units);
-    if (p.n_units_win > 0) build(m->d.sliding_window, L.units_win, p.n_units_win);
-  }
   if (before_copy) CK(cudaEventRecord(before_copy, c->stream));
   CK(cudaMemcpyAsync(m->meta_dev, hbuf, L.total, cudaMemcpyHostToDevice, c->stream));
   CK(cudaEventRecord(m->meta_ev[slot], c->stream));
@@ -1154,14 +1120,13 @@ AttnParams attn_params(kc_model* m, kc_kv* kv, const StepPlan& p, int layer, con
   a.part_o = m->attn_ws;
   a.part_ml = reinterpret_cast<float2*>(reinterpret_cast<uint8_t*>(m->attn_ws) + align_up(rows * m->d.head_dim * 4, 256));
   a.block_tables = reinterpret_cast<const int32_t*>(m->meta_dev + p.lay.tables);
-  a.work = reinterpret_cast<const int4*>(m->meta_dev + (window > 0 ? p.lay.units_win : p.lay.units));
-  a.n_units = window > 0 ? p.n_units_win : p.n_units;
+  a.work = reinterpret_cast<const int4*>(m->meta_dev + p.lay.work);
   a.token_pos = reinterpret_cast<const int32_t*>(m->meta_dev + p.lay.token_pos);
   a.status = m->ctx->status;
   a.max_blocks = p.max_blocks;
   a.Hq = Hq; a.Hkv = kv->kv_heads; a.gqa = Hq / kv->kv_heads;
   a.layer = layer; a.NB = kv->num_blocks; a.BS = kv->block_size;
-  a.max_chunks = p.max_chunks;
+  a.max_chunks = p.max_chunks; a.chunk_lo_grid = 0;
   a.single_chunk = p.max_chunks == 1 ? 1 : 0;
   a.scale = scale; a.softcap = softcap; a.window = window;
   a.pool = kv->pool;
@@ -1247,7 +1212,7 @@ int run_forward(kc_model* m, kc_kv* kv, const uint32_t* tokens_dev, const StepPl
                             kv->num_blocks, kv->block_size, kv->pool, m->q_rot, c->stream));
     const int window = (d.sliding_window > 0 && (l % 2 == 0)) ? d.sliding_window : 0;
     AttnParams a = attn_params(m, kv, p, l, m->q_rot, m->attn, m->attn_scale, gemma ? d.attn_logit_softcapping : 0.f, window, m->Hq);
-    LAUNCH(c, KC_PROF_ATTN, a.single_chunk ? 1 : 2, paged_attention(kv->map, a, D, p.tokens_per_item, n, c->stream));
+    LAUNCH(c, KC_PROF_ATTN, a.single_chunk ? 1 : 2, paged_attention(kv->map, a, D, p.tokens_per_item, p.n_work, p.max_chunks, n, c->stream));
     if (streams(L.o)) RC(run_stream(c, L.o, m->attn, n, m->proj, H, m->partial, &so));
     else RC(run_qlinear(c, L.o, m->op_attn, n, d.tp_world > 1 ? tp_out_buffer(m) : m->proj, H, m->partial, d.tp_world > 1 ? nullptr : &so));
     if (d.tp_world > 1 && (rc = tp_exchange(m, n, &so))) return rc;
@@ -1543,14 +1508,13 @@ extern "C" int kc_paged_attention(kc_ctx_t c, kc_kv_t kv, int32_t layer, const v
   if (rc) return rc;
   std::vector<uint32_t> ids(std::max(n, 1), 0);
   StepPlan p;
-  m->d.sliding_window = window > 0 ? window : 0;   // the windowed unit list is built for this window
   rc = validate_step(m, kv, ids.data(), n, seqs, n_seqs, 0, &p);
   if (!rc) rc = upload_meta(m, kv, ids.data(), seqs, p);
   if (!rc) rc = ensure_attn_ws(m, p);
   if (!rc) {
     AttnParams a = attn_params(m, kv, p, layer, (const bf16*)q_dev, (bf16*)out_dev, scale, softcap, window, num_heads);
     rc = [&]() -> int {
-      LAUNCH(c, KC_PROF_ATTN, a.single_chunk ? 1 : 2, paged_attention(kv->map, a, kv->head_dim, p.tokens_per_item, n, c->stream));
+      LAUNCH(c, KC_PROF_ATTN, a.single_chunk ? 1 : 2, paged_attention(kv->map, a, kv->head_dim, p.tokens_per_item, p.n_work, p.max_chunks, n, c->stream));
       return KC_OK;
     }();
   }

@@ -16,8 +16,7 @@
 // row's result therefore does not depend on how many other rows (of its own
 // sequence or of others) share the launch.
 //
-// The grid is a host-built list of units (work item, key chunk), longest first, times the kv heads: the CTAs that start
-// last are the short ones, so the tail of the launch is a fraction of a chunk. One CTA = (unit, kv head); a work item is up to MT*16/gqa
+// One CTA = (chunk, kv head, work item); a work item is up to MT*16/gqa
 // consecutive tokens of one sequence, so the CTA's MT*16 query rows (token x
 // head-in-group) all read the same K/V tiles: K/V bytes cross HBM once per
 // (sequence, kv head). K/V tiles arrive by TMA (cp.async.bulk.tensor, 128-byte
@@ -87,9 +86,10 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap kvmap, const AttnParams 
 
   pdl_launch_dependents();
   pdl_wait();   // everything below reads step data (work items, q, block tables, this layer's K/V rows)
-  const int kvh = blockIdx.x;
-  const int4 wk = p.work[blockIdx.y];   // {seq | chunk << 16, first token row in the step, tokens, position of first token}
-  const int seq = wk.x & 0xffff, chunk = wk.x >> 16, tok0 = wk.y, qlen = wk.z, pos0 = wk.w;
+  const int chunk = p.chunk_lo_grid + blockIdx.x;
+  const int kvh = blockIdx.y;
+  const int4 wk = p.work[blockIdx.z];   // {seq, first token row in the step, tokens, position of first token}
+  const int seq = wk.x, tok0 = wk.y, qlen = wk.z, pos0 = wk.w;
   const int pos_max = pos0 + qlen - 1;
   const int c_hi = pos_max / ATT_CHUNK;
   int c_lo = 0;
@@ -401,26 +401,26 @@ __global__ void attn_combine_kernel(const AttnParams p, int n_rows) {
 }
 
 template <int D, int MT>
-cudaError_t launch_partial(const CUtensorMap& map, const AttnParams& p, cudaStream_t s) {
+cudaError_t launch_partial(const CUtensorMap& map, const AttnParams& p, int n_work, int grid_chunks, cudaStream_t s) {
   using S = AttnSmem<D, MT>;
   static DeviceOnce configured;   // the attribute belongs to the device's copy of the kernel
   if (configured.first_on_current_device()) {
     cudaError_t e = cudaFuncSetAttribute(attn_partial_kernel<D, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
     if (e != cudaSuccess) { configured.forget_current_device(); return e; }
   }
-  dim3 grid(p.Hkv, p.n_units, 1);
+  dim3 grid(grid_chunks, p.Hkv, n_work);
   return launch_k(attn_partial_kernel<D, MT>, grid, dim3((S::CW + 1) * 32), S::TOTAL, s, map, p);
 }
 
 template <int D>
-cudaError_t launch_d(const CUtensorMap& map, const AttnParams& p, int mt, int n_tokens,
+cudaError_t launch_d(const CUtensorMap& map, const AttnParams& p, int mt, int n_work, int grid_chunks, int n_tokens,
                      cudaStream_t s) {
   cudaError_t e;
   switch (mt) {
-    case 1: e = launch_partial<D, 1>(map, p, s); break;
-    case 2: e = launch_partial<D, 2>(map, p, s); break;
-    case 3: e = launch_partial<D, 3>(map, p, s); break;
-    default: e = launch_partial<D, 4>(map, p, s); break;
+    case 1: e = launch_partial<D, 1>(map, p, n_work, grid_chunks, s); break;
+    case 2: e = launch_partial<D, 2>(map, p, n_work, grid_chunks, s); break;
+    case 3: e = launch_partial<D, 3>(map, p, n_work, grid_chunks, s); break;
+    default: e = launch_partial<D, 4>(map, p, n_work, grid_chunks, s); break;
   }
   if (e != cudaSuccess || p.single_chunk) return e;
   const int n_rows = n_tokens * p.Hq;
@@ -436,14 +436,14 @@ int attn_tokens_per_item(int gqa, int max_len) {
 }
 
 cudaError_t paged_attention(const CUtensorMap& kvmap, const AttnParams& p, int head_dim, int tokens_per_item,
-                            int n_tokens, cudaStream_t s) {
+                            int n_work, int grid_chunks, int n_tokens, cudaStream_t s) {
   const int rows = tokens_per_item * p.gqa;
   const int mt = (rows + 15) / 16;
   if (mt < 1 || mt > 4) return cudaErrorInvalidValue;
   switch (head_dim) {
-    case 64: return launch_d<64>(kvmap, p, mt, n_tokens, s);
-    case 128: return launch_d<128>(kvmap, p, mt, n_tokens, s);
-    case 256: return launch_d<256>(kvmap, p, mt, n_tokens, s);
+    case 64: return launch_d<64>(kvmap, p, mt, n_work, grid_chunks, n_tokens, s);
+    case 128: return launch_d<128>(kvmap, p, mt, n_work, grid_chunks, n_tokens, s);
+    case 256: return launch_d<256>(kvmap, p, mt, n_work, grid_chunks, n_tokens, s);
     default: return cudaErrorInvalidValue;
   }
 }
