@@ -49,6 +49,9 @@ GRID = [
     (256, 4, 2, 16, [(4, 70), (4, 600)], 50.0, 0),            # gemma-2 geometry with softcap
     (256, 4, 2, 16, [(4, 70), (4, 600)], 50.0, 48),           # + sliding window
     (128, 8, 2, 16, [(40, 0), (23, 100)], 0.0, 0),            # prefill-shaped segments (several work items each)
+    (128, 8, 2, 64, [(6, 700), (1, 130)], 0.0, 0),            # 64-token blocks (four tiles per block)
+    (128, 8, 2, 128, [(6, 1100)], 0.0, 0),                    # 128-token blocks, three chunks
+    (128, 8, 2, 16, [(6, 1500), (6, 300)], 0.0, 600),         # a window that ends inside an earlier chunk, head_dim 128
 ]
 
 
