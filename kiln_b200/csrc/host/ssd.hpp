@@ -156,20 +156,24 @@ class SsdStore {
     bytes_ += stride;
     files_[file].pending_slots++;
     files_[file].pending_bytes += stride;
-    inflight_[ticket.hash] = SlotRef{file, slot, dtype_tag, dtype_size};
+    inflight_[{file, slot}] = ticket.hash;
     Job j; j.kind = Job::Write; j.file = file; j.offset = g.slot_offset(dtype_size, slot); j.bytes = std::move(bytes);
     j.ack = FlushAck{ticket.node, ticket.generation, ticket.hash, true};
+    j.slot = SlotRef{file, slot, dtype_tag, dtype_size};
+    j.close_after = slot + 1 == SLOTS_PER_FILE;   // the file is full: the writer gives its descriptor back
     push(std::move(j));
   }
 
   // Applies completed writes and returns their acks (ssd.rs:411-446).
   std::vector<FlushAck> drain_acks() {
-    std::vector<FlushAck> acks;
+    std::vector<Done> done;
     {
       std::lock_guard<std::mutex> lk(mu_);
-      acks.swap(acks_);
+      done.swap(acks_);
     }
-    for (const FlushAck& a : acks) commit(a);
+    std::vector<FlushAck> acks;
+    acks.reserve(done.size());
+    for (const Done& d : done) { commit(d.ack, d.slot); acks.push_back(d.ack); }
     return acks;
   }
 
@@ -191,7 +195,10 @@ class SsdStore {
     uint64_t offset = 0;
     std::vector<uint8_t> bytes;
     FlushAck ack{};
+    SlotRef slot{};
+    bool close_after = false;
   };
+  struct Done { FlushAck ack; SlotRef slot; };
 
   SsdStore(const std::string& dir, const ChainHash& fp, const SlabGeometry& g, uint64_t max_bytes)
       : dir_(dir), fingerprint_(fp), geometry_(g), max_bytes_(max_bytes) {}
@@ -251,10 +258,11 @@ class SsdStore {
     return ok;
   }
 
-  void commit(const FlushAck& ack) {  // ssd.rs:420-446
-    auto it = inflight_.find(ack.hash);
+  // Writes in flight are keyed by their slot, not by their hash: a block that is queued twice before the first
+  // acknowledgement arrives owns two slots, and each acknowledgement must settle its own.
+  void commit(const FlushAck& ack, const SlotRef& slot) {  // ssd.rs:420-446
+    auto it = inflight_.find({slot.file, slot.slot});
     if (it == inflight_.end()) return;   // the slab was evicted while the write was queued
-    const SlotRef slot = it->second;
     inflight_.erase(it);
     const uint64_t stride = geometry_.slot_stride(slot.dtype_size);
     auto f = files_.find(slot.file);
@@ -283,7 +291,7 @@ class SsdStore {
       files_.erase(f);
     }
     for (auto it = index_.begin(); it != index_.end();) it = it->second.file == file ? index_.erase(it) : std::next(it);
-    for (auto it = inflight_.begin(); it != inflight_.end();) it = it->second.file == file ? inflight_.erase(it) : std::next(it);
+    for (auto it = inflight_.begin(); it != inflight_.end();) it = it->first.first == file ? inflight_.erase(it) : std::next(it);
     Job j; j.kind = Job::Delete; j.file = file;
     push(std::move(j));
   }
@@ -369,8 +377,9 @@ class SsdStore {
       } else if (j.kind == Job::Write) {
         auto h = handles_.find(j.file);
         j.ack.ok = h != handles_.end() && ::pwrite(h->second, j.bytes.data(), j.bytes.size(), (off_t)j.offset) == (ssize_t)j.bytes.size();
+        if (j.close_after && h != handles_.end()) { ::close(h->second); handles_.erase(h); }
         std::lock_guard<std::mutex> lk(mu_);
-        acks_.push_back(j.ack);
+        acks_.push_back(Done{j.ack, j.slot});
       } else {
         auto h = handles_.find(j.file);
         if (h != handles_.end()) { ::close(h->second); handles_.erase(h); }
@@ -388,7 +397,8 @@ class SsdStore {
   ChainHash fingerprint_;
   SlabGeometry geometry_;
   uint64_t max_bytes_;
-  std::map<ChainHash, SlotRef> index_, inflight_;
+  std::map<ChainHash, SlotRef> index_;
+  std::map<std::pair<uint32_t, uint32_t>, ChainHash> inflight_;   // (file, slot) of every write not yet acknowledged
   std::map<uint32_t, FileMeta> files_;
   uint64_t bytes_ = 0, clock_ = 0;
   uint32_t next_file_ = 0, open_file_ = 0, open_used_ = 0;
@@ -398,7 +408,7 @@ class SsdStore {
   std::mutex mu_;
   std::condition_variable cv_, done_cv_;
   std::deque<Job> jobs_;
-  std::vector<FlushAck> acks_;
+  std::vector<Done> acks_;
   uint64_t pushed_ = 0, done_ = 0;
   bool closing_ = false;
   std::map<uint32_t, int> handles_;   // writer thread only (and the destructor after the join)

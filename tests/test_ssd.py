@@ -95,6 +95,24 @@ def test_corrupt_header_and_wrong_fingerprint_are_skipped(tmp_path):
     store.close()
 
 
+def test_a_block_queued_twice_settles_both_slots(tmp_path):
+    """Two writes of one hash before the first acknowledgement: each acknowledgement settles its own slot and the later
+    payload is the one served, also after a restart (later slots win the header scan)."""
+    tokens, h = [5, 6, 7, 8], b"\x0a" * 32
+    store = open_store(tmp_path)
+    store.enqueue_write(1, 1, h, tokens, payload(0x11), 3, 2)
+    store.enqueue_write(1, 2, h, tokens, payload(0x22), 3, 2)
+    acks = store.sync()
+    assert [a[3] for a in acks] == [True, True]
+    assert store.stats()["blocks_stored"] == 1 and store.stats()["writes_total"] == 2
+    assert store.read(h, tokens, 3) == (payload(0x22), 3)
+    assert store.stats()["bytes_stored"] == HEADER_BYTES + 2 * slot_stride()
+    store.close()
+    store = open_store(tmp_path)
+    assert store.read(h, tokens, 3) == (payload(0x22), 3)
+    store.close()
+
+
 def test_byte_cap_drops_lru_slabs(tmp_path):
     cap = HEADER_BYTES + slot_stride() * SLOTS_PER_FILE + slot_stride()
     store = open_store(tmp_path, cap=cap)
