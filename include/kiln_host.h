@@ -127,13 +127,18 @@ typedef struct {
   int (*collect)(void* model, uint64_t ticket, uint32_t* row_tokens, int32_t n);
 } kh_decode_pipeline;
 
-/* trait Drafter (drafter.rs:125-147). A non-zero return from begin/propose is a DraftError: never fatal to the request. */
+/* DrafterMemory (drafter.rs:88-102): summed into the worker's memory report. */
+typedef struct { uint64_t weights_bytes, kv_allocated_bytes, kv_used_bytes; } kh_drafter_memory;
+
+/* trait Drafter (drafter.rs:125-147). A non-zero return from begin/propose is a DraftError: never fatal to the request.
+ * memory may be NULL (a drafter with no footprint of its own: all zeros). */
 typedef struct {
   void* user;
   int (*begin)(void* user, uint64_t seq, const uint32_t* prompt, int32_t n);
   int (*propose)(void* user, uint64_t seq, const uint32_t* committed, int32_t n_committed, int32_t gamma, uint32_t* out,
                  int32_t* n_out);
   void (*release)(void* user, uint64_t seq);
+  void (*memory)(void* user, kh_drafter_memory* out);
 } kh_drafter;
 
 /* EngineConfig (engine.rs:239-306) plus the envelope the backend provides (kc_envelope). */
@@ -156,6 +161,9 @@ KH_API void kh_engine_default_config(kh_engine_config* out);   /* EngineConfig::
 KH_API int kh_engine_create(const kh_engine_config* cfg, const kh_step_model* model, kh_engine_t* out);
 KH_API void kh_engine_free(kh_engine_t e);
 KH_API int kh_engine_set_drafter(kh_engine_t e, const kh_drafter* d);
+/* Engine::drafter_memory (engine.rs:1128-1132): 1 and the attached drafter's footprint, or 0 (and zeros) when
+ * speculation is not configured. */
+KH_API int kh_engine_drafter_memory(kh_engine_t e, kh_drafter_memory* out);
 /* Without this call the engine never pipelines (every step is read back before the next is built). p = NULL turns
  * pipelining off again; a step already in flight is read back at the next kh_engine_step. */
 KH_API int kh_engine_set_pipeline(kh_engine_t e, const kh_decode_pipeline* p);
@@ -242,6 +250,9 @@ typedef struct {
   int (*chain)(void* model, void* kv, uint32_t first_token, int32_t offset, const uint32_t* blocks, int32_t n_blocks,
                int32_t gamma, uint32_t* proposal);
   int32_t max_chunk;
+  /* For Drafter::memory (draft.rs:259-266): kc_model_weight_bytes, kc_kv_allocated_bytes and kc_kv_block_bytes of the
+   * draft model and its pool; kv_used_bytes is live blocks x kv_block_bytes. Zeros where unknown. */
+  uint64_t weights_bytes, kv_allocated_bytes, kv_block_bytes;
 } kh_draft_backend;
 typedef struct kh_draft_model* kh_draft_model_t;
 KH_API int kh_draft_model_create(const kh_draft_backend* b, uint64_t num_blocks, uint64_t block_size, kh_draft_model_t* out);

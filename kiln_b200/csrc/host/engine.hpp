@@ -79,12 +79,16 @@ struct BlockIoVT {
 };
 
 // Drafter seam (drafter.rs:125-147). propose writes at most `gamma` ids; a non-zero return is a DraftError.
+// DrafterMemory (drafter.rs:88-102): what a drafter adds to the worker's memory report.
+struct DrafterMemory { uint64_t weights_bytes = 0, kv_allocated_bytes = 0, kv_used_bytes = 0; };
+
 struct DrafterVT {
   void* user;
   int (*begin)(void* user, uint64_t seq, const uint32_t* prompt, int32_t n);
   int (*propose)(void* user, uint64_t seq, const uint32_t* committed, int32_t n_committed, int32_t gamma, uint32_t* out,
                  int32_t* n_out);
   void (*release)(void* user, uint64_t seq);
+  void (*memory)(void* user, DrafterMemory* out) = nullptr;   // Drafter::memory (drafter.rs:127); null = all zeros
 };
 
 // drafter.rs:26-50 and engine.rs:133-213 defaults.
@@ -176,6 +180,13 @@ class Engine {
     if (cfg.prefix_cache) radix_.reset(new RadixCache(cfg.block_size, ChainHash{}));
   }
   void set_drafter(const DrafterVT& d) { drafter_ = d; has_drafter_ = true; }
+  // Engine::drafter_memory (engine.rs:1128-1132): false when speculation is not configured.
+  bool drafter_memory(DrafterMemory* out) const {
+    *out = DrafterMemory{};
+    if (!has_drafter_) return false;
+    if (drafter_.memory) drafter_.memory(drafter_.user, out);
+    return true;
+  }
   // Attaches the SSD tier (engine.rs:1053-1076): donated blocks are written behind the steps, evicted ones stay
   // discoverable, and a fresh engine over the same directory finds them again hash-first. Needs the prefix cache.
   bool set_ssd(const std::string& dir, const ChainHash& fingerprint, const SlabGeometry& g, uint64_t max_bytes, const BlockIoVT& io) {
@@ -1039,6 +1050,7 @@ class ScriptedDrafter {
 struct DraftModelVT {
   void* model;
   void* kv;
+  uint64_t weights_bytes = 0, kv_allocated_bytes = 0, kv_block_bytes = 0;   // for Drafter::memory (draft.rs:259-266)
   int (*forward)(void* model, void* kv, const uint32_t* ids, int32_t n, const SeqStepC* seqs, int32_t n_seqs, uint32_t* row_tokens,
                  int32_t* n_committed, int32_t* n_accepted);
   int (*chain)(void* model, void* kv, uint32_t first_token, int32_t offset, const uint32_t* blocks, int32_t n_blocks, int32_t gamma,
@@ -1052,6 +1064,13 @@ class DraftModel {
   DraftModel(const DraftModelVT& vt, size_t num_blocks, size_t block_size) : vt_(vt), mgr_(num_blocks, block_size) {}
   BlockManager& block_manager() { return mgr_; }
   size_t live_sequences() const { return seqs_.size(); }
+  DrafterMemory memory() const {  // draft.rs:259-266
+    DrafterMemory m;
+    m.weights_bytes = vt_.weights_bytes;
+    m.kv_allocated_bytes = vt_.kv_allocated_bytes;
+    m.kv_used_bytes = (uint64_t)(mgr_.capacity() - mgr_.num_free()) * vt_.kv_block_bytes;
+    return m;
+  }
 
   int begin(uint64_t seq, const uint32_t* prompt, int32_t n) {  // draft.rs:268-284
     auto it = seqs_.find(seq);
@@ -1114,7 +1133,8 @@ class DraftModel {
                      [](void* u, uint64_t s, const uint32_t* c, int32_t nc, int32_t g, uint32_t* o, int32_t* no) {
                        return ((DraftModel*)u)->propose(s, c, nc, g, o, no);
                      },
-                     [](void* u, uint64_t s) { ((DraftModel*)u)->release(s); }};
+                     [](void* u, uint64_t s) { ((DraftModel*)u)->release(s); },
+                     [](void* u, DrafterMemory* o) { *o = ((DraftModel*)u)->memory(); }};
   }
 
  private:

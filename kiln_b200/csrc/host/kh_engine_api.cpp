@@ -25,6 +25,7 @@ struct kh_draft_model {
 };
 
 static_assert(sizeof(kh_seq_step) == sizeof(SeqStepC), "seq step layout");
+static_assert(sizeof(kh_drafter_memory) == sizeof(DrafterMemory), "drafter memory layout");
 
 extern "C" {
 
@@ -60,8 +61,17 @@ void kh_engine_free(kh_engine_t e) { if (e) { delete e->e; delete e; } }
 
 int kh_engine_set_drafter(kh_engine_t e, const kh_drafter* d) {
   if (!e || !d || !d->begin || !d->propose || !d->release) return KH_ERR_ARG;
-  e->e->set_drafter(DrafterVT{d->user, d->begin, d->propose, d->release});
+  DrafterVT vt{d->user, d->begin, d->propose, d->release};
+  vt.memory = reinterpret_cast<decltype(vt.memory)>(d->memory);
+  e->e->set_drafter(vt);
   return KH_OK;
+}
+int kh_engine_drafter_memory(kh_engine_t e, kh_drafter_memory* out) {
+  if (!e || !out) return 0;
+  DrafterMemory m;
+  const bool has = e->e->drafter_memory(&m);
+  out->weights_bytes = m.weights_bytes; out->kv_allocated_bytes = m.kv_allocated_bytes; out->kv_used_bytes = m.kv_used_bytes;
+  return has ? 1 : 0;
 }
 int kh_engine_set_pipeline(kh_engine_t e, const kh_decode_pipeline* p) {
   if (!e) return KH_ERR_ARG;
@@ -224,6 +234,7 @@ int kh_scripted_set_continuation(kh_scripted_t d, uint64_t seq, const uint32_t* 
 void kh_scripted_vtable(kh_scripted_t d, kh_drafter* out) {
   DrafterVT v = d->d->vtable();
   out->user = v.user; out->begin = v.begin; out->propose = v.propose; out->release = v.release;
+  out->memory = nullptr;   // a scripted drafter holds no weights and no pool
 }
 
 int kh_draft_model_create(const kh_draft_backend* b, uint64_t num_blocks, uint64_t block_size, kh_draft_model_t* out) {
@@ -232,6 +243,7 @@ int kh_draft_model_create(const kh_draft_backend* b, uint64_t num_blocks, uint64
   if (!st.ok()) return (int)st.err;
   DraftModelVT vt;
   vt.model = b->model; vt.kv = b->kv; vt.max_chunk = b->max_chunk > 0 ? b->max_chunk : 2048;
+  vt.weights_bytes = b->weights_bytes; vt.kv_allocated_bytes = b->kv_allocated_bytes; vt.kv_block_bytes = b->kv_block_bytes;
   vt.forward = reinterpret_cast<decltype(vt.forward)>(b->forward);
   vt.chain = b->chain;
   kh_draft_model* h = new kh_draft_model;
@@ -244,6 +256,7 @@ void kh_draft_model_free(kh_draft_model_t d) { if (d) { delete d->d; delete d; }
 void kh_draft_model_vtable(kh_draft_model_t d, kh_drafter* out) {
   DrafterVT v = d->d->vtable();
   out->user = v.user; out->begin = v.begin; out->propose = v.propose; out->release = v.release;
+  out->memory = reinterpret_cast<decltype(out->memory)>(v.memory);
 }
 kh_bm_t kh_draft_model_block_manager(kh_draft_model_t d) { return &d->bm_view; }
 uint64_t kh_draft_model_live_sequences(kh_draft_model_t d) { return d->d->live_sequences(); }

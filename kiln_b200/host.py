@@ -37,6 +37,13 @@ COPY_FN = C.CFUNCTYPE(C.c_int, _P, C.c_uint32, C.c_uint32)
 BEGIN_FN = C.CFUNCTYPE(C.c_int, _P, C.c_uint64, _U32P, C.c_int32)
 PROPOSE_FN = C.CFUNCTYPE(C.c_int, _P, C.c_uint64, _U32P, C.c_int32, C.c_int32, _U32P, C.POINTER(C.c_int32))
 RELEASE_FN = C.CFUNCTYPE(None, _P, C.c_uint64)
+
+
+class KhDrafterMemory(C.Structure):
+    _fields_ = [("weights_bytes", C.c_uint64), ("kv_allocated_bytes", C.c_uint64), ("kv_used_bytes", C.c_uint64)]
+
+
+MEMORY_FN = C.CFUNCTYPE(None, _P, C.POINTER(KhDrafterMemory))
 CHAIN_FN = C.CFUNCTYPE(C.c_int, _P, _P, C.c_uint32, C.c_int32, _U32P, C.c_int32, C.c_int32, _U32P)
 
 
@@ -53,11 +60,12 @@ class KhStepModel(C.Structure):
 
 
 class KhDrafter(C.Structure):
-    _fields_ = [("user", _P), ("begin", BEGIN_FN), ("propose", PROPOSE_FN), ("release", RELEASE_FN)]
+    _fields_ = [("user", _P), ("begin", BEGIN_FN), ("propose", PROPOSE_FN), ("release", RELEASE_FN), ("memory", MEMORY_FN)]
 
 
 class KhDraftBackend(C.Structure):
-    _fields_ = [("model", _P), ("kv", _P), ("forward", VERIFY_FN), ("chain", CHAIN_FN), ("max_chunk", C.c_int32)]
+    _fields_ = [("model", _P), ("kv", _P), ("forward", VERIFY_FN), ("chain", CHAIN_FN), ("max_chunk", C.c_int32),
+                ("weights_bytes", C.c_uint64), ("kv_allocated_bytes", C.c_uint64), ("kv_block_bytes", C.c_uint64)]
 
 
 class KhSlabGeometry(C.Structure):
@@ -129,6 +137,7 @@ _SIGNATURES = {
     "kh_engine_set_pipeline": (C.c_int, [_P, C.POINTER(KhDecodePipeline)]),
     "kh_engine_pipelined_steps": (C.c_uint64, [_P]),
     "kh_engine_free": (None, [_P]), "kh_engine_set_drafter": (C.c_int, [_P, C.POINTER(KhDrafter)]),
+    "kh_engine_drafter_memory": (C.c_int, [_P, C.POINTER(KhDrafterMemory)]),
     "kh_engine_submit": (C.c_int, [_P, _U32P, _U64, _U64, _U32P, _U64, C.POINTER(_U64)]),
     "kh_engine_cancel": (C.c_int, [_P, _U64]), "kh_engine_step": (C.c_int, [_P]),
     "kh_engine_num_running": (_U64, [_P]), "kh_engine_num_waiting": (_U64, [_P]), "kh_engine_iterations": (_U64, [_P]),
@@ -529,8 +538,9 @@ class Drafter:
         self.c, self._keep = c_struct, keep
 
     @classmethod
-    def from_python(cls, begin, propose, release) -> "Drafter":
-        """begin(seq, prompt) ; propose(seq, committed, gamma) -> list[int] (raise = DraftError) ; release(seq)."""
+    def from_python(cls, begin, propose, release, memory=None) -> "Drafter":
+        """begin(seq, prompt) ; propose(seq, committed, gamma) -> list[int] (raise = DraftError) ; release(seq) ;
+        memory() -> (weights_bytes, kv_allocated_bytes, kv_used_bytes), optional (Drafter::memory)."""
         def _b(_u, seq, p, n):
             try:
                 begin(seq, [p[i] for i in range(n)])
@@ -552,10 +562,14 @@ class Drafter:
         def _r(_u, seq):
             release(seq)
 
+        def _m(_u, out):
+            out[0].weights_bytes, out[0].kv_allocated_bytes, out[0].kv_used_bytes = (int(v) for v in memory())
+
         b, p, r = BEGIN_FN(_b), PROPOSE_FN(_p), RELEASE_FN(_r)
+        m = MEMORY_FN(_m) if memory is not None else MEMORY_FN()
         d = KhDrafter()
-        d.user, d.begin, d.propose, d.release = None, b, p, r
-        return cls(d, (b, p, r, begin, propose, release))
+        d.user, d.begin, d.propose, d.release, d.memory = None, b, p, r, m
+        return cls(d, (b, p, r, m, begin, propose, release, memory))
 
 
 class ScriptedDrafter(Drafter):
@@ -592,6 +606,9 @@ class DraftModel(Drafter):
         b.forward = C.cast(cl.kc_verify_step, VERIFY_FN)
         b.chain = C.cast(cl.kc_draft_chain, CHAIN_FN)
         b.max_chunk = max_chunk
+        b.weights_bytes = int(cl.kc_model_weight_bytes(model._h))
+        b.kv_allocated_bytes = int(cl.kc_kv_allocated_bytes(kv._h))
+        b.kv_block_bytes = int(cl.kc_kv_block_bytes(kv._h))
         self._h = _P()
         _check(lib().kh_draft_model_create(C.byref(b), num_blocks, block_size, C.byref(self._h)))
         d = KhDrafter()
@@ -703,6 +720,14 @@ class Engine:
     def set_drafter(self, drafter: Drafter) -> None:
         self._drafter = drafter
         _check(lib().kh_engine_set_drafter(self._h, C.byref(drafter.c)))
+
+    def drafter_memory(self):
+        """Engine::drafter_memory (engine.rs:1128-1132): dict of the attached drafter's footprint, or None."""
+        m = KhDrafterMemory()
+        if not lib().kh_engine_drafter_memory(self._h, C.byref(m)):
+            return None
+        return {"weights_bytes": int(m.weights_bytes), "kv_allocated_bytes": int(m.kv_allocated_bytes),
+                "kv_used_bytes": int(m.kv_used_bytes)}
 
     def set_ssd(self, directory: str, fingerprint: bytes, layers: int, kv_heads: int, head_dim: int, max_bytes: int = 1 << 40,
                 read_block=None, write_block=None, kv=None, dtype_tag: int = 7, dtype_size: int = 2) -> None:

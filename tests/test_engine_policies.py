@@ -144,6 +144,7 @@ class FakeDraftBackend:
         self._f, self._c = H.VERIFY_FN(_forward), H.CHAIN_FN(_chain)
         b = H.KhDraftBackend()
         b.model, b.kv, b.forward, b.chain, b.max_chunk = None, None, self._f, self._c, 8
+        b.weights_bytes, b.kv_allocated_bytes, b.kv_block_bytes = 1000, num_blocks * 64, 64
         self.handle = H._P()
         H._check(H.lib().kh_draft_model_create(C.byref(b), num_blocks, BS, C.byref(self.handle)))
         d = H.KhDrafter()
@@ -172,3 +173,26 @@ def test_draft_model_self_draft_accepts_everything_and_releases_its_pool():
     assert st["proposed_total"] > 0 and st["accepted_total"] == st["proposed_total"]
     assert any(n == 8 for n, _ in fb.forward_calls)              # catch-up chunks capped at max_chunk
     assert fb.live() == 0 and fb.pool().num_free == 128          # released at finish
+
+
+def test_drafter_memory_report():
+    """Drafter::memory through Engine::drafter_memory (drafter.rs:88-127, engine.rs:1128-1132; draft.rs:259-266): None
+    without a drafter, zeros for a drafter with no footprint, and for a DraftModel its weights, its pool and the blocks
+    its live sequences hold (live blocks x bytes per block)."""
+    eng, _ = make_engine()
+    assert eng.drafter_memory() is None
+    eng.set_drafter(H.ScriptedDrafter(1.0, 1, VOCAB))
+    assert eng.drafter_memory() == {"weights_bytes": 0, "kv_allocated_bytes": 0, "kv_used_bytes": 0}
+    eng.set_drafter(H.Drafter.from_python(lambda s, p: None, lambda s, c, g: [], lambda s: None, memory=lambda: (7, 8, 9)))
+    assert eng.drafter_memory() == {"weights_bytes": 7, "kv_allocated_bytes": 8, "kv_used_bytes": 9}
+    fb = FakeDraftBackend(128)
+    eng.set_drafter(fb.drafter)
+    assert eng.drafter_memory() == {"weights_bytes": 1000, "kv_allocated_bytes": 128 * 64, "kv_used_bytes": 0}
+    a = eng.submit(prompts(1, 13, 20, 21)[0], 24)
+    used = 0
+    for _ in range(6):
+        eng.step()
+        used = max(used, eng.drafter_memory()["kv_used_bytes"])
+    assert used > 0 and used % 64 == 0
+    eng.run_to_completion([a])
+    assert eng.drafter_memory()["kv_used_bytes"] == 0
