@@ -185,8 +185,8 @@ KC_API int kc_envelope(kc_model_t model, int32_t* max_gamma, int32_t* max_key_le
 /* Switches the weight-streaming lane on or off for this model: forwards of at most 8 rows (a draft model's chained
  * decode steps, crates/kiln-models/src/draft.rs:354-388) then read every weight straight from global memory into
  * registers instead of going through the tensor-core pipeline, whose set-up dominates such a step. on = 1: weights of
- * at least 24 MB (8B-class layers, every head; smaller ones are latency-bound either way and stay on the tensor-core
- * kernel); on = 2: every weight; on = 0: off. Off by default,
+ * at least 24 MB (8B-class layers, every head) stream, smaller ones take the small-weight kernel of the same arithmetic
+ * (kc_quantized_matmul_gemv) where their shape fits it; on = 2: every weight streams; on = 0: off. Off by default,
  * and meant for draft models: a row's bits differ between the two lanes, so a target model whose decode steps
  * (few rows) and verify steps (more than 8 rows) must agree bit for bit keeps it off. Not available on a
  * tensor-parallel slice. */
@@ -323,6 +323,14 @@ KC_API int kc_quantized_matmul(kc_ctx_t ctx, kc_qweight_t w, const void* x_dev, 
  * lanes agree to rounding, not bit for bit. */
 KC_API int kc_quantized_matmul_stream(kc_ctx_t ctx, kc_qweight_t w, const void* x_dev, int32_t m,
                                       void* y_dev);
+
+/* The same arithmetic for weights of a few MB (the layers of a 1B-class draft model), where a launch is a chain of
+ * latencies rather than a stream: one CTA per (128-row tile, run of k-blocks) asks for all of its records at once,
+ * before it waits for the kernel ahead of it, and works through them resident; a tile's k-blocks are cut into at most
+ * 8 runs whose fp32 partials are summed in order. A model with the weight-streaming lane on takes this kernel for the
+ * weights below the streaming threshold. KC_ERR_UNSUPPORTED when the weight's shape does not fit the lane. */
+KC_API int kc_quantized_matmul_gemv(kc_ctx_t ctx, kc_qweight_t w, const void* x_dev, int32_t m,
+                                    void* y_dev);
 
 /* kc_quantized_matmul without any allocation behind it. No counterpart in the
  * reference (MLX owns every buffer there); added for callers that cannot let a

@@ -85,6 +85,7 @@ _SIGNATURES = {
     "kc_qweight_free": (None, [_P]),
     "kc_quantized_matmul": (C.c_int, [_P, _P, _P, C.c_int32, _P]),
     "kc_quantized_matmul_stream": (C.c_int, [_P, _P, _P, C.c_int32, _P]),
+    "kc_quantized_matmul_gemv": (C.c_int, [_P, _P, _P, C.c_int32, _P]),
     "kc_tp_export": (C.c_int, [_P, _P]),
     "kc_tp_attach": (C.c_int, [_P, _P]),
     "kc_model_set_stream_lane": (C.c_int, [_P, C.c_int32]),

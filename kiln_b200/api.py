@@ -536,6 +536,16 @@ class QuantizedWeight:
         self.ctx.sync()
         return y
 
+    def matmul_gemv(self, x: torch.Tensor) -> torch.Tensor:
+        """The same product for at most 8 rows through the small-weight lane (kc_quantized_matmul_gemv)."""
+        assert x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[1] == self.in_features
+        x = x.contiguous()
+        y = torch.empty(x.shape[0], self.out_features, dtype=torch.bfloat16, device=x.device)
+        torch.cuda.current_stream().synchronize()
+        check(L.lib().kc_quantized_matmul_gemv(self.ctx._h, self._h, x.data_ptr(), x.shape[0], y.data_ptr()))
+        self.ctx.sync()
+        return y
+
     def matmul_static(self, xp: torch.Tensor, m: int, y: torch.Tensor) -> None:
         """kc_quantized_matmul_static on caller-owned buffers: xp bf16 [round_up(m, 16), in], y bf16 [m, out], both
         on the device. This wrapper allocates nothing either; the caller synchronises (Context.sync)."""

@@ -178,6 +178,7 @@ struct kc_model {
        *gu = nullptr, *act = nullptr, *hs = nullptr, *logits = nullptr;
   ActOperand op_normed, op_attn, op_act, op_hs;
   float* partial = nullptr; size_t partial_bytes = 0;
+  float* partial_gu = nullptr;         // gate_up's fp32 partials while a gated down projection reads them (stream lane on)
   float* attn_ws = nullptr; size_t attn_ws_bytes = 0;
   float* tp_buf = nullptr;             // fp32 staging for the tensor-parallel all-reduce
   // Tensor-parallel exchange over peer memory (kc_tp_export / kc_tp_attach): the o_proj / down_proj output of exchange e
@@ -496,6 +497,15 @@ static int run_stream(kc_ctx* c, const QWeight& w, const bf16* x, int M, bf16* y
   return KC_OK;
 }
 
+// The small-weight lane (qlinear_gemv): same contract as run_stream.
+static int run_gemv(kc_ctx* c, const QWeight& w, const bf16* x, int M, bf16* y, int ldy, float* partial, SublayerOut* out) {
+  const int pieces = qlinear_gemv_pieces(w);
+  LAUNCH(c, KC_PROF_GEMM, 1, qlinear_gemv(w, x, w.K, M, partial, c->status, c->stream));
+  if (!out) LAUNCH(c, KC_PROF_GEMM_REDUCE, 1, qlinear_reduce_splits(partial, pieces, M, w.N, y, ldy, c->stream));
+  else *out = SublayerOut::partials(partial, pieces, (size_t)M, w.N);
+  return KC_OK;
+}
+
 // ---------------------------------------------------------------------------
 // stand-alone quantised weight (parity tests / composed graphs)
 // ---------------------------------------------------------------------------
@@ -535,8 +545,9 @@ extern "C" int kc_qweight_create(kc_ctx_t c, const uint32_t* w, const void* scal
   cudaError_t e = qweight_build(&q->w, (const uint32_t*)dw, (const bf16*)ds, (const bf16*)db, out_features,
                                 in_features, bits, group_size, c->sm_count, c->stream);
   if (e == cudaSuccess) {
-    const size_t need = std::max((size_t)(q->w.splits > 1 ? q->w.splits : 0) * QL_MAX_M * q->w.N,
-                                 (size_t)qlinear_stream_pieces(q->w) * QL_STREAM_MAX_M * q->w.N);
+    const size_t need = std::max({(size_t)(q->w.splits > 1 ? q->w.splits : 0) * QL_MAX_M * q->w.N,
+                                  (size_t)qlinear_stream_pieces(q->w) * QL_STREAM_MAX_M * q->w.N,
+                                  (size_t)qlinear_gemv_pieces(q->w) * QL_STREAM_MAX_M * q->w.N});
     if (need) e = cudaMalloc(&q->partial, need * sizeof(float));
   }
   cudaStreamSynchronize(c->stream);
@@ -584,6 +595,18 @@ extern "C" int kc_quantized_matmul_stream(kc_ctx_t c, kc_qweight_t q, const void
   CK(cudaSetDevice(c->device));
   LAUNCH(c, KC_PROF_GEMM, 1, qlinear_stream(q->w, (const bf16*)x_dev, q->w.K, m, q->partial, c->status, c->stream));
   LAUNCH(c, KC_PROF_GEMM_REDUCE, 1, qlinear_reduce_splits(q->partial, qlinear_stream_pieces(q->w), m, q->w.N, (bf16*)y_dev, q->w.N, c->stream));
+  return KC_OK;
+}
+
+extern "C" int kc_quantized_matmul_gemv(kc_ctx_t c, kc_qweight_t q, const void* x_dev, int32_t m, void* y_dev) {
+  if (!c || !q || !x_dev || !y_dev) return fail(KC_ERR_INVALID, "kc_quantized_matmul_gemv: NULL argument");
+  if (m < 1 || m > QL_STREAM_MAX_M) return fail(KC_ERR_INVALID, "kc_quantized_matmul_gemv: m = %d (1..%d)", m, QL_STREAM_MAX_M);
+  if ((uintptr_t)x_dev % 16) return fail(KC_ERR_INVALID, "kc_quantized_matmul_gemv: x must be 16-byte aligned");
+  if (q->ctx != c) return fail(KC_ERR_INVALID, "kc_quantized_matmul_gemv: the weight was created on another context");
+  if (qlinear_gemv_pieces(q->w) == 0)
+    return fail(KC_ERR_UNSUPPORTED, "kc_quantized_matmul_gemv: a weight of %d x %d does not fit the small-weight lane", q->w.N, q->w.K);
+  CK(cudaSetDevice(c->device));
+  RC(run_gemv(c, q->w, (const bf16*)x_dev, m, (bf16*)y_dev, q->w.N, q->partial, nullptr));
   return KC_OK;
 }
 
@@ -740,6 +763,7 @@ std::vector<float> rope_inv_freq(const kc_model_desc& d) {
 }
 
 void free_model(kc_model* m) {
+  cudaFree(m->partial_gu);
   for (auto& L : m->layers) {
     qweight_free(&L.qkv); qweight_free(&L.o); qweight_free(&L.gate_up); qweight_free(&L.down);
     cudaFree(L.qkv_bias); cudaFree(L.input_ln); cudaFree(L.post_attn_ln); cudaFree(L.pre_ffw_ln); cudaFree(L.post_ffw_ln);
@@ -912,6 +936,7 @@ extern "C" int kc_model_load(kc_ctx_t c, const kc_model_desc* desc, const kc_ten
       if (w.splits > 1) need = std::max(need, (size_t)w.splits * QL_MAX_M * w.N * sizeof(float));
       // the weight-streaming lane's partials, at most 8 rows
       need = std::max(need, (size_t)qlinear_stream_pieces(w) * QL_STREAM_MAX_M * w.N * sizeof(float));
+      need = std::max(need, (size_t)qlinear_gemv_pieces(w) * QL_STREAM_MAX_M * w.N * sizeof(float));
     };
     for (auto& L : m->layers) { acc(L.qkv); acc(L.o); acc(L.gate_up); acc(L.down); }
     acc(m->head);
@@ -1201,12 +1226,16 @@ int run_forward(kc_model* m, kc_kv* kv, const uint32_t* tokens_dev, const StepPl
   // that the launch is latency-bound either way and the consumer would only have more partial pieces to sum. A
   // function of the weight's size alone, so a model takes the same kernels for every small step.
   auto streams = [&](const QWeight& w) { return stream && w.bytes() >= m->stream_min_bytes; };
+  // ... and the smaller ones the small-weight lane of the same arithmetic (one CTA per tile and run of k-blocks, all
+  // records requested at once), where their shape fits it
+  auto small = [&](const QWeight& w) { return stream && !streams(w) && qlinear_gemv_pieces(w) > 0; };
   LAUNCH(c, KC_PROF_ROWWISE, 1, launch_embed(m->emb_w, m->emb_s, m->emb_b, tokens_dev, n, H, d.bits, d.group_size, m->embed_scale, d.vocab_size, m->h, c->stream));
   LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, SublayerOut::none(), nullptr, m->layers[0].input_ln, nullptr, n, H, d.rms_norm_eps, nullptr, m->normed, c->stream));
   for (int l = 0; l < d.num_layers; ++l) {
     Layer& L = m->layers[l];
     SublayerOut so;
     if (streams(L.qkv)) RC(run_stream(c, L.qkv, m->normed, n, m->qkv, m->n_qkv, m->partial, &so));
+    else if (small(L.qkv)) RC(run_gemv(c, L.qkv, m->normed, n, m->qkv, m->n_qkv, m->partial, &so));
     else RC(run_qlinear(c, L.qkv, m->op_normed, n, m->qkv, m->n_qkv, m->partial, &so));
     LAUNCH(c, KC_PROF_ROWWISE, 1, launch_rope_kv_write(so, L.qkv_bias, m->inv_freq, token_pos, kv_slot, n, m->Hq, m->Hkv, D, d.rope_traditional, l,
                             kv->num_blocks, kv->block_size, kv->pool, m->q_rot, c->stream));
@@ -1214,18 +1243,31 @@ int run_forward(kc_model* m, kc_kv* kv, const uint32_t* tokens_dev, const StepPl
     AttnParams a = attn_params(m, kv, p, l, m->q_rot, m->attn, m->attn_scale, gemma ? d.attn_logit_softcapping : 0.f, window, m->Hq);
     LAUNCH(c, KC_PROF_ATTN, a.single_chunk ? 1 : 2, paged_attention(kv->map, a, D, p.tokens_per_item, p.n_work, p.max_chunks, n, c->stream));
     if (streams(L.o)) RC(run_stream(c, L.o, m->attn, n, m->proj, H, m->partial, &so));
+    else if (small(L.o)) RC(run_gemv(c, L.o, m->attn, n, m->proj, H, m->partial, &so));
     else RC(run_qlinear(c, L.o, m->op_attn, n, d.tp_world > 1 ? tp_out_buffer(m) : m->proj, H, m->partial, d.tp_world > 1 ? nullptr : &so));
     if (d.tp_world > 1 && (rc = tp_exchange(m, n, &so))) return rc;
     if (gemma) LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, so, L.post_attn_ln, L.pre_ffw_ln, nullptr, n, H, d.rms_norm_eps, m->h, m->normed, c->stream));
     else LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, so, nullptr, L.post_attn_ln, nullptr, n, H, d.rms_norm_eps, m->h, m->normed, c->stream));
-    if (streams(L.gate_up)) {
-      SublayerOut gu;
-      RC(run_stream(c, L.gate_up, m->normed, n, m->gu, 2 * m->F, m->partial, &gu));
-      LAUNCH(c, KC_PROF_ROWWISE, 1, launch_glu_from(gu, n, m->F, gemma ? 1 : 0, m->glu_interleaved ? 1 : 0, m->act, c->stream));
+    // a down projection on the small-weight lane applies the activation itself while it stages its input, straight
+    // from gate_up's fp32 partials (kept in a workspace of their own: down writes its partials meanwhile)
+    bool gated_down = false;
+    SublayerOut gu;
+    if (streams(L.gate_up) || small(L.gate_up)) {
+      gated_down = small(L.down) && m->partial_gu && (m->F % 128) == 0;
+      float* ws = gated_down ? m->partial_gu : m->partial;
+      if (streams(L.gate_up)) RC(run_stream(c, L.gate_up, m->normed, n, m->gu, 2 * m->F, ws, &gu));
+      else RC(run_gemv(c, L.gate_up, m->normed, n, m->gu, 2 * m->F, ws, &gu));
+      if (!gated_down) LAUNCH(c, KC_PROF_ROWWISE, 1, launch_glu_from(gu, n, m->F, gemma ? 1 : 0, m->glu_interleaved ? 1 : 0, m->act, c->stream));
     } else {
       RC(run_gated(c, L.gate_up, m->op_normed, n, m->gu, m->F, gemma ? 1 : 0, m->glu_interleaved, m->act, m->partial));
     }
     if (streams(L.down)) RC(run_stream(c, L.down, m->act, n, m->proj, H, m->partial, &so));
+    else if (gated_down) {
+      const QvGatedInput in{gu.part, gu.splits, gemma, m->glu_interleaved};
+      LAUNCH(c, KC_PROF_GEMM, 1, qlinear_gemv(L.down, nullptr, 0, n, m->partial, c->status, c->stream, &in));
+      so = SublayerOut::partials(m->partial, qlinear_gemv_pieces(L.down), (size_t)n, H);
+    }
+    else if (small(L.down)) RC(run_gemv(c, L.down, m->act, n, m->proj, H, m->partial, &so));
     else RC(run_qlinear(c, L.down, m->op_act, n, d.tp_world > 1 ? tp_out_buffer(m) : m->proj, H, m->partial, d.tp_world > 1 ? nullptr : &so));
     if (d.tp_world > 1 && (rc = tp_exchange(m, n, &so))) return rc;
     const bf16* next_ln = l + 1 < d.num_layers ? m->layers[l + 1].input_ln : nullptr;
@@ -1235,6 +1277,7 @@ int run_forward(kc_model* m, kc_kv* kv, const uint32_t* tokens_dev, const StepPl
     const int32_t* sampled = reinterpret_cast<const int32_t*>(m->meta_dev + p.lay.sampled);
     LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, SublayerOut::none(), nullptr, m->final_norm, sampled, p.n_sampled, H, d.rms_norm_eps, nullptr, m->hs, c->stream));
     if (streams(m->head)) RC(run_stream(c, m->head, m->hs, p.n_sampled, m->logits, d.vocab_size, m->partial, nullptr));
+    else if (small(m->head) && p.n_sampled <= QL_STREAM_MAX_M) RC(run_gemv(c, m->head, m->hs, p.n_sampled, m->logits, d.vocab_size, m->partial, nullptr));
     else RC(run_qlinear(c, m->head, m->op_hs, p.n_sampled, m->logits, d.vocab_size, m->partial));
     if (gemma && d.final_logit_softcapping > 0.f)
       LAUNCH(c, KC_PROF_ROWWISE, 1, launch_softcap(m->logits, (long long)p.n_sampled * d.vocab_size, d.final_logit_softcapping, c->stream));
@@ -1297,6 +1340,12 @@ extern "C" int kc_model_set_stream_lane(kc_model_t m, int32_t on) {
   if (on && m->d.tp_world > 1) return fail(KC_ERR_UNSUPPORTED, "kc_model_set_stream_lane: not available on a tensor-parallel slice");
   m->stream_lane = on != 0;
   m->stream_min_bytes = on == 2 ? 0 : QL_STREAM_MIN_BYTES;
+  if (on && !m->partial_gu && !m->layers.empty()) {
+    const QWeight& gu = m->layers[0].gate_up;
+    const size_t pieces = (size_t)std::max(qlinear_stream_pieces(gu), qlinear_gemv_pieces(gu));
+    CK(cudaSetDevice(m->ctx->device));
+    CK(cudaMalloc(&m->partial_gu, pieces * QL_STREAM_MAX_M * gu.N * sizeof(float)));
+  }
   return KC_OK;
 }
 

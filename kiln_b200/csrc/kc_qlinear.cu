@@ -1079,6 +1079,254 @@ cudaError_t qlinear_stream(const QWeight& w, const bf16* x, int ldx, int M, floa
 }
 
 // ---------------------------------------------------------------------------
+// The small-weight lane of the same arithmetic: at most 8 rows against a weight of a few MB (the layers of a 1B-class
+// draft model), where a launch is a chain of latencies and not a stream. One CTA = (tile, run of k-blocks); thread 0
+// asks for ALL of the CTA's records with bulk copies onto one barrier before the kernel waits for its predecessor
+// (weights depend on nothing), the activation slice of the run is staged once, and the eight warps (16 weight rows
+// of the tile each) then work through records that are all resident, four at a time, with no ring and no hand-over.
+// The k-blocks of a tile are cut into at most QV_MAX_PIECES runs — a function of the weight's shape and the SM count
+// only — and leave fp32 partials [pieces][M][N] like the streaming kernel's, for the consumer kernel to sum in order.
+// ---------------------------------------------------------------------------
+constexpr int QV_WARPS = 8;
+constexpr int QV_THREADS = QV_WARPS * 32;
+constexpr int QV_MAX_PIECES = 8;
+constexpr size_t QV_SMEM_BUDGET = 96 * 1024;   // two CTAs per SM
+
+struct QvParams {
+  const uint8_t* records;
+  uint32_t record_bytes;
+  int N, n_tiles, kblocks, c_used, kbper;
+  const bf16* x;   // [M, ldx]
+  int ldx, M;
+  float* partial;  // [c_used][M][N]
+  uint32_t* status;
+  // Optional gated-activation operand: x is then not read; the activations are silu(gate) * up (gelu_approx for
+  // glu == 2) of a gate_up output still in its fp32 partial form [gu_pieces][M][2 K] (K = this weight's input width).
+  const float* gu;
+  int gu_pieces, glu, gu_interleaved;
+};
+
+template <int BITS, int GPK>
+__global__ void __launch_bounds__(QV_THREADS) qlinear_gemv_kernel(const QvParams p) {
+  constexpr int ROW_BYTES = QL_KB * BITS / 8;
+  constexpr int PACKED = QL_TILE_N * ROW_BYTES;
+  constexpr int HALF_BYTES = ROW_BYTES / 2;
+  constexpr int LANE_WORDS = BITS / 4;
+  constexpr int RB = BITS == 4 ? 4 : 2;               // records whose loads and MMA chains overlap
+  extern __shared__ __align__(128) uint8_t smem[];
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x / p.c_used, part = blockIdx.x - tile * p.c_used;
+  const int kb0 = part * p.kbper, kb1 = min(p.kblocks, kb0 + p.kbper), nkb = kb1 - kb0;
+  uint8_t* recs = smem;                                                     // [nkb][record_bytes]
+  bf16* xs = reinterpret_cast<bf16*>(recs + (size_t)p.kbper * p.record_bytes);      // [8][kbper * 64]
+  float* xsum = reinterpret_cast<float*>(xs + (size_t)8 * p.kbper * QL_KB);         // [kbper][GPK][8]
+  uint64_t* bar = reinterpret_cast<uint64_t*>(xsum + (size_t)p.kbper * GPK * 8);   // one per batch of RB records
+  const int n_batches = (nkb + RB - 1) / RB;
+  if (threadIdx.x == 0) {
+    for (int b = 0; b < n_batches; ++b) mbar_init(&bar[b], 1);
+    mbar_fence_init();
+    const uint8_t* src = p.records + ((size_t)(tile >> 2) * p.kblocks + kb0) * QL_TILE_GROUP * p.record_bytes + (size_t)(tile & 3) * p.record_bytes;
+    for (int b = 0; b < n_batches; ++b) {
+      const int in_batch = min(RB, nkb - b * RB);
+      mbar_arrive_expect_tx(&bar[b], (uint32_t)in_batch * p.record_bytes);
+      for (int i = b * RB; i < b * RB + in_batch; ++i, src += (size_t)QL_TILE_GROUP * p.record_bytes)
+        bulk_g2s(recs + (size_t)i * p.record_bytes, src, p.record_bytes, &bar[b]);
+    }
+  }
+  __syncthreads();
+  pdl_wait();   // x comes from the kernel before; the partials below may still be read by it
+  // the activation slice of this run, rows past M as zeros
+  const int row_elems = p.kbper * QL_KB;
+  for (int i = threadIdx.x; i < 8 * nkb * 8; i += QV_THREADS) {
+    const int m = i / (nkb * 8), c8 = i - m * (nkb * 8);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (m < p.M) {
+      if (!p.gu) {
+        v = *reinterpret_cast<const uint4*>(p.x + (size_t)m * p.ldx + (size_t)kb0 * QL_KB + c8 * 8);
+      } else {
+        // Mlp::forward's activation (nn.rs:284-294) on the way in: the arithmetic of glu_from_kernel
+        const int F = p.kblocks * QL_KB, col = kb0 * QL_KB + c8 * 8;
+        const int gcol = p.gu_interleaved ? (col >> 7) * 256 + (col & 127) : col;
+        const int ucol = p.gu_interleaved ? gcol + 128 : F + col;
+        const float* base = p.gu + (size_t)m * 2 * F;
+        float4 g0 = *reinterpret_cast<const float4*>(base + gcol), g1 = *reinterpret_cast<const float4*>(base + gcol + 4);
+        float4 u0 = *reinterpret_cast<const float4*>(base + ucol), u1 = *reinterpret_cast<const float4*>(base + ucol + 4);
+        for (int k = 1; k < p.gu_pieces; ++k) {
+          const float* pk = base + (size_t)k * p.M * 2 * F;
+          const float4 a = *reinterpret_cast<const float4*>(pk + gcol), b = *reinterpret_cast<const float4*>(pk + gcol + 4);
+          const float4 c = *reinterpret_cast<const float4*>(pk + ucol), d = *reinterpret_cast<const float4*>(pk + ucol + 4);
+          g0.x += a.x; g0.y += a.y; g0.z += a.z; g0.w += a.w; g1.x += b.x; g1.y += b.y; g1.z += b.z; g1.w += b.w;
+          u0.x += c.x; u0.y += c.y; u0.z += c.z; u0.w += c.w; u1.x += d.x; u1.y += d.y; u1.z += d.z; u1.w += d.w;
+        }
+        const float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w}, uv[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+        float a[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          a[k] = p.glu == 2 ? act_gelu_mul(bf16_round(gv[k]), bf16_round(uv[k])) : act_silu_mul(bf16_round(gv[k]), bf16_round(uv[k]));
+        v = make_uint4(pack_bf162(a[0], a[1]), pack_bf162(a[2], a[3]), pack_bf162(a[4], a[5]), pack_bf162(a[6], a[7]));
+      }
+    }
+    *reinterpret_cast<uint4*>(xs + (size_t)m * row_elems + c8 * 8) = v;
+  }
+  __syncthreads();
+  // sums of x per (k-block, scale group, row)
+  for (int i = threadIdx.x; i < nkb * GPK * 8; i += QV_THREADS) {
+    const int m = i & 7, q = (i >> 3) % GPK, kbl = i / (8 * GPK);
+    constexpr int SPAN = QL_KB / GPK;
+    const bf16* src = xs + (size_t)m * row_elems + kbl * QL_KB + q * SPAN;
+    float s0 = 0.f;
+#pragma unroll
+    for (int e = 0; e < SPAN; e += 8) {
+      const uint4 v = *reinterpret_cast<const uint4*>(src + e);
+      const float2 a = unpack_bf162(v.x), b = unpack_bf162(v.y), c = unpack_bf162(v.z), d = unpack_bf162(v.w);
+      s0 += ((a.x + a.y) + (b.x + b.y)) + ((c.x + c.y) + (d.x + d.y));
+    }
+    xsum[(size_t)(kbl * GPK + q) * 8 + m] = s0;
+  }
+  __syncthreads();
+
+  const int g = lane >> 2, t = lane & 3;
+  const int r0 = warp * 16 + g;
+  const uint32_t lane_off = (uint32_t)r0 * ROW_BYTES + t * (4 * LANE_WORDS);
+  const uint32_t sb_off = PACKED + (uint32_t)r0 * GPK * 4;
+  const bf16* xrow = xs + (size_t)g * row_elems + 8 * t;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int kbl = 0; kbl < nkb; kbl += RB) {
+    const int nb = nkb - kbl < RB ? nkb - kbl : RB;
+    // the batch's records have landed (the later batches are still on their way: copy and arithmetic overlap)
+    if (!__all_sync(0xffffffffu, mbar_wait(&bar[kbl / RB], 0, p.status, KC_DEV_QLINEAR | 0x21))) {
+      // gave up: the copies may still land in this CTA's shared memory; one more bounded wait for each of them
+      for (int b = kbl / RB; b < n_batches; ++b) mbar_wait(&bar[b], 0, nullptr, 0);
+      return;
+    }
+    uint4 xa[RB][2];
+    float2 xsv[RB][GPK];
+    uint32_t u[RB][2][2][LANE_WORDS];
+    uint32_t sbw[RB][2][GPK];
+#pragma unroll
+    for (int i = 0; i < RB; ++i) {
+      const int kk = kbl + (i < nb ? i : 0);
+      const uint8_t* rc = recs + (size_t)kk * p.record_bytes;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) xa[i][h] = *reinterpret_cast<const uint4*>(xrow + kk * QL_KB + 32 * h);
+#pragma unroll
+      for (int q = 0; q < GPK; ++q) xsv[i][q] = *reinterpret_cast<const float2*>(xsum + (size_t)(kk * GPK + q) * 8 + 2 * t);
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          const uint8_t* src = rc + lane_off + r * 8 * ROW_BYTES + h * HALF_BYTES;
+          if (LANE_WORDS == 1) u[i][h][r][0] = *reinterpret_cast<const uint32_t*>(src);
+          else { const uint2 v = *reinterpret_cast<const uint2*>(src); u[i][h][r][0] = v.x; u[i][h][r][LANE_WORDS - 1] = v.y; }
+        }
+#pragma unroll
+      for (int r = 0; r < 2; ++r)
+#pragma unroll
+        for (int q = 0; q < GPK; ++q) sbw[i][r][q] = *reinterpret_cast<const uint32_t*>(rc + sb_off + r * 8 * GPK * 4 + q * 4);
+    }
+    float raw[RB][2][4];
+#pragma unroll
+    for (int i = 0; i < RB; ++i) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        raw[i][h][0] = raw[i][h][1] = raw[i][h][2] = raw[i][h][3] = 0.f;
+        uint32_t e0[4], e1[4];
+        qg_raw_pairs<BITS>(u[i][h][0], e0);
+        qg_raw_pairs<BITS>(u[i][h][1], e1);
+        mma_bf16_16816(raw[i][h], e0[0], e1[0], e0[2], e1[2], xa[i][h].x, xa[i][h].z);
+        mma_bf16_16816(raw[i][h], e0[1], e1[1], e0[3], e1[3], xa[i][h].y, xa[i][h].w);
+      }
+    }
+    // the sums join the accumulator in k-block order: the result does not depend on RB
+#pragma unroll
+    for (int i = 0; i < RB; ++i) {
+      if (i < nb) {
+        if (GPK == 1) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) raw[i][0][k] += raw[i][1][k];
+        }
+#pragma unroll
+        for (int q = 0; q < GPK; ++q) {
+#pragma unroll
+          for (int r = 0; r < 2; ++r) {
+            const float sc = __uint_as_float(sbw[i][r][q] << 16), bi = __uint_as_float(sbw[i][r][q] & 0xFFFF0000u);
+            const float bc = BITS == 4 ? fmaf(-128.f, sc, bi) : bi;   // the 128 every 4-bit q carries
+            acc[2 * r + 0] = fmaf(sc, raw[i][q][2 * r + 0], fmaf(bc, xsv[i][q].x, acc[2 * r + 0]));
+            acc[2 * r + 1] = fmaf(sc, raw[i][q][2 * r + 1], fmaf(bc, xsv[i][q].y, acc[2 * r + 1]));
+          }
+        }
+      }
+    }
+  }
+  // acc[0], [1] = weight row r0 against activation rows 2t, 2t + 1; [2], [3] = row r0 + 8
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int n = tile * QL_TILE_N + r0 + 8 * r;
+    if (n < p.N) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int m = 2 * t + e;
+        if (m < p.M) p.partial[((size_t)part * p.M + m) * p.N + n] = acc[2 * r + e];
+      }
+    }
+  }
+}
+
+// The cut of a weight for the small-weight lane: runs of kbper k-blocks, c_used of them per tile.
+struct QvPlan { bool ok; int c_used, kbper; size_t smem; };
+static QvPlan qv_plan(const QWeight& w) {
+  QvPlan q{false, 0, 0, 0};
+  if (w.n_tiles < 1 || w.kblocks < 1) return q;
+  const size_t per_kb = (size_t)w.record_bytes + 8 * QL_KB * sizeof(bf16) + (size_t)w.gpk * 8 * sizeof(float) + 8;   // + a barrier
+  const int cap_kb = (int)((QV_SMEM_BUDGET - 64) / per_kb);
+  if (cap_kb < 1) return q;
+  // runs of about 8 k-blocks (a few microseconds of copy and arithmetic), fewer runs where the tiles alone fill the
+  // SMs: every run is one more fp32 partial for the consumer kernel to read
+  int c = std::max(1, std::min(QV_MAX_PIECES, w.kblocks / 8));
+  c = std::min(c, std::max(1, 2 * w.sm_count / w.n_tiles));
+  int kbper = std::min((w.kblocks + c - 1) / c, cap_kb);
+  q.kbper = kbper;
+  q.c_used = (w.kblocks + kbper - 1) / kbper;
+  q.smem = (size_t)kbper * per_kb + 64;
+  q.ok = q.c_used <= QV_MAX_PIECES;
+  return q;
+}
+
+int qlinear_gemv_pieces(const QWeight& w) {
+  const QvPlan q = qv_plan(w);
+  return q.ok ? q.c_used : 0;
+}
+
+template <int BITS, int GPK>
+static cudaError_t launch_gemv(const QvParams& p, int ctas, size_t smem, cudaStream_t s) {
+  static DeviceOnce configured;
+  if (configured.first_on_current_device()) {
+    cudaError_t e = cudaFuncSetAttribute(qlinear_gemv_kernel<BITS, GPK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)QV_SMEM_BUDGET);
+    if (e != cudaSuccess) { configured.forget_current_device(); return e; }
+  }
+  return launch_k(qlinear_gemv_kernel<BITS, GPK>, dim3(ctas), dim3(QV_THREADS), smem, s, p);
+}
+
+cudaError_t qlinear_gemv(const QWeight& w, const bf16* x, int ldx, int M, float* partial, uint32_t* status, cudaStream_t s,
+                         const QvGatedInput* gated) {
+  const QvPlan q = qv_plan(w);
+  if (!q.ok || M < 1 || M > QL_STREAM_MAX_M || !partial) return cudaErrorInvalidValue;
+  if (!gated && ((ldx & 7) || (reinterpret_cast<uintptr_t>(x) & 15))) return cudaErrorInvalidValue;   // 16-byte activation loads
+  if (gated && (!gated->partial || gated->pieces < 1 || (reinterpret_cast<uintptr_t>(gated->partial) & 15) || (w.K & 127)))
+    return cudaErrorInvalidValue;
+  QvParams p;
+  p.gu = gated ? gated->partial : nullptr; p.gu_pieces = gated ? gated->pieces : 0;
+  p.glu = gated ? (gated->gelu ? 2 : 1) : 0; p.gu_interleaved = gated && gated->interleaved ? 1 : 0;
+  p.records = w.records; p.record_bytes = w.record_bytes;
+  p.N = w.N; p.n_tiles = w.n_tiles; p.kblocks = w.kblocks; p.c_used = q.c_used; p.kbper = q.kbper;
+  p.x = x; p.ldx = ldx; p.M = M; p.partial = partial; p.status = status;
+  const int ctas = w.n_tiles * q.c_used;
+  if (w.bits == 4) return w.gpk == 2 ? launch_gemv<4, 2>(p, ctas, q.smem, s) : launch_gemv<4, 1>(p, ctas, q.smem, s);
+  return w.gpk == 2 ? launch_gemv<8, 2>(p, ctas, q.smem, s) : launch_gemv<8, 1>(p, ctas, q.smem, s);
+}
+
+// ---------------------------------------------------------------------------
 // Split-K reduction
 // ---------------------------------------------------------------------------
 

@@ -103,6 +103,17 @@ int qlinear_launches(const QWeight& w, int M);
 int qlinear_stream_pieces(const QWeight& w);
 cudaError_t qlinear_stream(const QWeight& w, const bf16* x, int ldx, int M, float* partial, uint32_t* status, cudaStream_t s);
 
+// The same arithmetic for a weight of a few MB (a draft model's layers): one CTA per (tile, run of k-blocks), all of
+// its records requested at once. Partials [qlinear_gemv_pieces(w)][M][N]; 0 pieces = the weight's shape does not fit
+// the lane (the caller keeps another one).
+int qlinear_gemv_pieces(const QWeight& w);
+// gated (optional): the activations are not read from x but computed on the way in as silu(gate) * up (gelu_approx
+// with gelu) from a gate_up output in its fp32 partial form [pieces][M][2 K] — the down projection of an MLP whose
+// gate_up went through one of the fp32-partial lanes, without a separate activation kernel.
+struct QvGatedInput { const float* partial; int pieces; bool gelu, interleaved; };
+cudaError_t qlinear_gemv(const QWeight& w, const bf16* x, int ldx, int M, float* partial, uint32_t* status, cudaStream_t s,
+                         const QvGatedInput* gated = nullptr);
+
 // out[m, n] = bf16(sum over splits of partial[s][m][n]) in split order.
 cudaError_t qlinear_reduce_splits(const float* partial, int splits, int M, int N, bf16* y, int ldy,
                                   cudaStream_t s);

@@ -119,6 +119,52 @@ def test_stream_lane_matches_oracle(ctx, n, k, bits, group, m):
     assert ctx.device_status() == 0
 
 
+GEMV_CASES = [
+    # (N, K, bits, group, M): the small-weight lane of the same arithmetic
+    (256, 256, 4, 64, 1),
+    (200, 512, 4, 64, 5),          # N not a multiple of the 128-row tile
+    (384, 1024, 4, 32, 8),         # two groups per k-block
+    (256, 1024, 4, 128, 3),        # a group spans two k-blocks
+    (256, 512, 8, 32, 8),          # 8-bit
+    (256, 448, 8, 64, 7),          # K = 7 k-blocks: uneven runs
+    (3072, 2048, 4, 64, 1),        # the 1B qkv shape
+    (2048, 2048, 4, 64, 4),        # the 1B attention-output shape
+    (16384, 2048, 4, 64, 1),       # the 1B gate_up shape: two runs per tile
+    (2048, 8192, 4, 64, 8),        # the 1B down-projection depth: eight runs of 16 k-blocks
+    (4099, 2048, 4, 64, 2),        # a ragged last tile
+]
+
+
+@pytest.mark.parametrize("n,k,bits,group,m", GEMV_CASES)
+def test_small_weight_lane_matches_oracle_and_the_streaming_lane(ctx, n, k, bits, group, m):
+    """kc_quantized_matmul_gemv against the oracle's row-vector class, and against the streaming kernel of the same
+    class (they differ only in where a tile's k-blocks are cut, i.e. in fp32 summation order)."""
+    p, s, b = make(n, k, bits, group, 15)
+    x = acts(m, k, 16)
+    O.set_weight_class(0)
+    want = O.quantized_matmul(x, p, s, b, bits, group)
+    qw = api.QuantizedWeight(ctx, p.cuda(), s.cuda(), b.cuda(), bits, group)
+    got = qw.matmul_gemv(x.cuda()).cpu()
+    assert parity(f"small-weight lane {n}x{k} w{bits}g{group} rows {m}", got, want, MAX_ABS, MIN_COS)
+    stream = qw.matmul_stream(x.cuda()).cpu()
+    spacing = 2.0 ** (torch.floor(torch.log2(want.float().abs().max())) - 7)
+    assert float((got.float() - stream.float()).abs().max()) <= 2 * float(spacing)
+    # a row's bits do not depend on how many rows ride the call
+    if m > 1:
+        one = qw.matmul_gemv(x[:1].cuda()).cpu()
+        assert torch.equal(one.view(torch.int16), got[:1].view(torch.int16))
+    assert ctx.device_status() == 0
+
+
+def test_small_weight_lane_refuses_a_shape_it_cannot_hold(ctx):
+    """224 k-blocks would need more than eight runs of what shared memory holds: the entry point says so."""
+    p, s, b = make(640, 14336, 4, 64, 3)
+    qw = api.QuantizedWeight(ctx, p.cuda(), s.cuda(), b.cuda(), 4, 64)
+    with pytest.raises(api.KcError) as e:
+        qw.matmul_gemv(acts(2, 14336, 4).cuda())
+    assert "does not fit" in str(e.value)
+
+
 def test_stream_lane_rows_do_not_depend_on_row_count(ctx):
     """Within the lane a row's bits do not depend on how many rows ride the call (1..8)."""
     p, s, b = make(1024, 4096, 4, 64, 7)
