@@ -178,6 +178,7 @@ struct kc_model {
        *gu = nullptr, *act = nullptr, *hs = nullptr, *logits = nullptr;
   ActOperand op_normed, op_attn, op_act, op_hs;
   float* partial = nullptr; size_t partial_bytes = 0;
+  float* argmax_scratch = nullptr;     // per-CTA bests + counter of the fused reduction / arg-max of a streamed head
   float* partial_gu = nullptr;         // gate_up's fp32 partials while a gated down projection reads them (stream lane on)
   float* attn_ws = nullptr; size_t attn_ws_bytes = 0;
   float* tp_buf = nullptr;             // fp32 staging for the tensor-parallel all-reduce
@@ -763,7 +764,7 @@ std::vector<float> rope_inv_freq(const kc_model_desc& d) {
 }
 
 void free_model(kc_model* m) {
-  cudaFree(m->partial_gu);
+  cudaFree(m->partial_gu); cudaFree(m->argmax_scratch);
   for (auto& L : m->layers) {
     qweight_free(&L.qkv); qweight_free(&L.o); qweight_free(&L.gate_up); qweight_free(&L.down);
     cudaFree(L.qkv_bias); cudaFree(L.input_ln); cudaFree(L.post_attn_ln); cudaFree(L.pre_ffw_ln); cudaFree(L.post_ffw_ln);
@@ -1212,7 +1213,10 @@ bf16* tp_out_buffer(kc_model* m) {
 }
 
 // The forward proper. tokens_dev: n u32 on the device (normally the metadata arena's copy).
-int run_forward(kc_model* m, kc_kv* kv, const uint32_t* tokens_dev, const StepPlan& p, bool want_logits) {
+// greedy_out (optional, device): where a single sampled row's raw arg-max goes when the head's reduction can produce
+// it itself (*greedy_done = true then; otherwise the caller samples from the logits as usual).
+int run_forward(kc_model* m, kc_kv* kv, const uint32_t* tokens_dev, const StepPlan& p, bool want_logits, uint32_t* greedy_out = nullptr,
+                bool* greedy_done = nullptr) {
   kc_ctx* c = m->ctx;
   const kc_model_desc& d = m->d;
   const int n = p.n, H = d.hidden_size, D = d.head_dim;
@@ -1276,7 +1280,13 @@ int run_forward(kc_model* m, kc_kv* kv, const uint32_t* tokens_dev, const StepPl
   if (want_logits && p.n_sampled > 0) {
     const int32_t* sampled = reinterpret_cast<const int32_t*>(m->meta_dev + p.lay.sampled);
     LAUNCH(c, KC_PROF_ROWWISE, 1, launch_add_rmsnorm(m->h, SublayerOut::none(), nullptr, m->final_norm, sampled, p.n_sampled, H, d.rms_norm_eps, nullptr, m->hs, c->stream));
-    if (streams(m->head)) RC(run_stream(c, m->head, m->hs, p.n_sampled, m->logits, d.vocab_size, m->partial, nullptr));
+    if (streams(m->head) && greedy_out && p.n_sampled == 1 && m->argmax_scratch && !(gemma && d.final_logit_softcapping > 0.f)) {
+      LAUNCH(c, KC_PROF_GEMM, 1, qlinear_stream(m->head, m->hs, m->head.K, 1, m->partial, c->status, c->stream));
+      LAUNCH(c, KC_PROF_SAMPLE, 1, qlinear_reduce_argmax(m->partial, qlinear_stream_pieces(m->head), d.vocab_size, m->logits, m->argmax_scratch,
+                                                         greedy_out, c->stream));
+      if (greedy_done) *greedy_done = true;
+    }
+    else if (streams(m->head)) RC(run_stream(c, m->head, m->hs, p.n_sampled, m->logits, d.vocab_size, m->partial, nullptr));
     else if (small(m->head) && p.n_sampled <= QL_STREAM_MAX_M) RC(run_gemv(c, m->head, m->hs, p.n_sampled, m->logits, d.vocab_size, m->partial, nullptr));
     else RC(run_qlinear(c, m->head, m->op_hs, p.n_sampled, m->logits, d.vocab_size, m->partial));
     if (gemma && d.final_logit_softcapping > 0.f)
@@ -1340,6 +1350,12 @@ extern "C" int kc_model_set_stream_lane(kc_model_t m, int32_t on) {
   if (on && m->d.tp_world > 1) return fail(KC_ERR_UNSUPPORTED, "kc_model_set_stream_lane: not available on a tensor-parallel slice");
   m->stream_lane = on != 0;
   m->stream_min_bytes = on == 2 ? 0 : QL_STREAM_MIN_BYTES;
+  if (on && !m->argmax_scratch) {
+    const size_t bytes = (size_t)(2 * qlinear_reduce_argmax_ctas(m->d.vocab_size) + 4) * sizeof(float);
+    CK(cudaSetDevice(m->ctx->device));
+    CK(cudaMalloc(&m->argmax_scratch, bytes));
+    CK(cudaMemsetAsync(m->argmax_scratch, 0, bytes, m->ctx->stream));
+  }
   if (on && !m->partial_gu && !m->layers.empty()) {
     const QWeight& gu = m->layers[0].gate_up;
     const size_t pieces = (size_t)std::max(qlinear_stream_pieces(gu), qlinear_gemv_pieces(gu));
@@ -1444,8 +1460,9 @@ extern "C" int kc_draft_chain(kc_model_t m, kc_kv_t kv, uint32_t first_token, in
     if (rc) return rc;
     if ((rc = upload_meta(m, kv, &tok, &s, p))) return rc;
     const uint32_t* tokens_dev = j == 0 ? reinterpret_cast<const uint32_t*>(m->meta_dev + p.lay.tokens) : m->row_tokens + (j - 1);
-    if ((rc = run_forward(m, kv, tokens_dev, p, true))) return rc;
-    LAUNCH(c, KC_PROF_SAMPLE, 1, launch_greedy_rows(m->logits, 1, m->d.vocab_size, 0, m->row_tokens + j, c->stream));
+    bool sampled = false;
+    if ((rc = run_forward(m, kv, tokens_dev, p, true, m->row_tokens + j, &sampled))) return rc;
+    if (!sampled) LAUNCH(c, KC_PROF_SAMPLE, 1, launch_greedy_rows(m->logits, 1, m->d.vocab_size, 0, m->row_tokens + j, c->stream));
   }
   CK(cudaMemcpyAsync(m->result_host, m->row_tokens, (size_t)gamma * 4, cudaMemcpyDeviceToHost, c->stream));
   CK(status_fetch(c));

@@ -1363,6 +1363,77 @@ __global__ void qlinear_reduce_kernel(const float* __restrict__ partial, int spl
   }
 }
 
+// The reduction of ONE row fused with its raw arg-max (the head of a draft model's chained step, draft.rs:379-381:
+// argmax of the logits row, lowest index on ties): every CTA sums its slice of the pieces in index order, rounds to
+// bf16 (the head's output, also stored to y), keeps the best of its slice, and the CTA that finishes last — counted
+// with one atomic per CTA, nobody waits — takes the best over the CTAs and stores the token. scratch: 2 floats per
+// CTA followed by one counter word that is zero between launches (the last CTA resets it).
+__global__ void __launch_bounds__(256) qlinear_reduce_argmax_kernel(const float* __restrict__ partial, int splits, int N,
+                                                                    bf16* __restrict__ y, float* __restrict__ scratch,
+                                                                    uint32_t* __restrict__ token) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float s_v[8];
+  __shared__ int s_i[8];
+  __shared__ bool s_last;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  auto better = [](float av, int ai, float bv, int bi) { return bv > av || (bv == av && bi < ai); };
+  float best_v = -INFINITY;
+  int best_i = 0x7fffffff;
+  for (int n = blockIdx.x * blockDim.x + threadIdx.x; n < N; n += gridDim.x * blockDim.x) {
+    float acc = partial[n];
+    for (int k = 1; k < splits; ++k) acc += partial[(size_t)k * N + n];
+    const bf16 r = __float2bfloat16_rn(acc);
+    y[n] = r;
+    const float v = __bfloat162float(r);
+    if (better(best_v, best_i, v, n)) { best_v = v; best_i = n; }
+  }
+  auto reduce_block = [&]() {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best_v, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+      if (better(best_v, best_i, ov, oi)) { best_v = ov; best_i = oi; }
+    }
+    if (lane == 0) { s_v[warp] = best_v; s_i[warp] = best_i; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+        if (better(best_v, best_i, s_v[w], s_i[w])) { best_v = s_v[w]; best_i = s_i[w]; }
+    }
+  };
+  reduce_block();
+  uint32_t* counter = reinterpret_cast<uint32_t*>(scratch + 2 * gridDim.x);
+  if (threadIdx.x == 0) {
+    scratch[2 * blockIdx.x] = best_v;
+    scratch[2 * blockIdx.x + 1] = __int_as_float(best_i);
+    __threadfence();
+    s_last = atomicAdd(counter, 1u) == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  best_v = -INFINITY; best_i = 0x7fffffff;
+  for (int b = threadIdx.x; b < (int)gridDim.x; b += blockDim.x) {
+    const float v = __ldcg(scratch + 2 * b);
+    const int i = __float_as_int(__ldcg(scratch + 2 * b + 1));
+    if (better(best_v, best_i, v, i)) { best_v = v; best_i = i; }
+  }
+  __syncthreads();   // s_v / s_i are reused
+  reduce_block();
+  if (threadIdx.x == 0) {
+    *token = (uint32_t)best_i < (uint32_t)N ? (uint32_t)best_i : 0u;   // a row of NaNs has no maximum
+    *counter = 0u;
+  }
+}
+
+int qlinear_reduce_argmax_ctas(int N) { return std::max(1, std::min((N + 511) / 512, 296)); }
+
+cudaError_t qlinear_reduce_argmax(const float* partial, int splits, int N, bf16* y, float* scratch, uint32_t* token, cudaStream_t s) {
+  if (!partial || !y || !scratch || !token || splits < 1 || N < 1) return cudaErrorInvalidValue;
+  return launch_k(qlinear_reduce_argmax_kernel, dim3(qlinear_reduce_argmax_ctas(N)), dim3(256), 0, s, partial, splits, N, y, scratch, token);
+}
+
 cudaError_t qlinear_reduce_splits(const float* partial, int splits, int M, int N, bf16* y, int ldy,
                                   cudaStream_t s) {
   const int vec = (N % 2 == 0 && ldy % 2 == 0 && (reinterpret_cast<uintptr_t>(partial) & 7) == 0 &&

@@ -114,6 +114,11 @@ struct QvGatedInput { const float* partial; int pieces; bool gelu, interleaved; 
 cudaError_t qlinear_gemv(const QWeight& w, const bf16* x, int ldx, int M, float* partial, uint32_t* status, cudaStream_t s,
                          const QvGatedInput* gated = nullptr);
 
+// One row: y[n] = bf16(sum over pieces of partial[k][n]) and *token = arg-max of that row (lowest index on ties), in
+// one launch. scratch: 2 * qlinear_reduce_argmax_ctas(N) floats followed by one zeroed 32-bit counter (left zero).
+int qlinear_reduce_argmax_ctas(int N);
+cudaError_t qlinear_reduce_argmax(const float* partial, int splits, int N, bf16* y, float* scratch, uint32_t* token, cudaStream_t s);
+
 // out[m, n] = bf16(sum over splits of partial[s][m][n]) in split order.
 cudaError_t qlinear_reduce_splits(const float* partial, int splits, int M, int N, bf16* y, int ldy,
                                   cudaStream_t s);
