@@ -18,6 +18,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <map>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -118,6 +119,7 @@ struct kc_ctx {
 
 struct kc_kv {
   kc_ctx* ctx = nullptr;
+  int device = 0;
   int layers = 0, kv_heads = 0, head_dim = 0, num_blocks = 0, block_size = 0;
   bf16* pool = nullptr;        // [layers][2][num_blocks][kv_heads][block_size][head_dim]
   size_t block_elems = 0;      // kv_heads * block_size * head_dim
@@ -128,6 +130,7 @@ struct kc_kv {
 
 struct kc_qweight {
   kc_ctx* ctx = nullptr;
+  int device = 0;
   QWeight w;
   float* partial = nullptr;
   ActOperand op;               // bound lazily to the caller's x buffer
@@ -156,6 +159,7 @@ struct MetaLayout {
 
 struct kc_model {
   kc_ctx* ctx = nullptr;
+  int device = 0;
   kc_model_desc d{};
   int Hq = 0, Hkv = 0;                 // local (tensor-parallel) head counts
   int F = 0;                           // local intermediate size
@@ -214,6 +218,22 @@ struct kc_model {
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// Live contexts. A handle that outlives its context (the convention is the other order, but a garbage-collected host
+// language does not promise one) must not touch the context's stream when it is freed: it then synchronises the
+// device instead.
+static std::mutex g_ctx_mu;
+static std::vector<kc_ctx*> g_ctxs;
+static void quiesce(kc_ctx* c, int device) {
+  cudaSetDevice(device);
+  bool alive;
+  {
+    std::lock_guard<std::mutex> lk(g_ctx_mu);
+    alive = std::find(g_ctxs.begin(), g_ctxs.end(), c) != g_ctxs.end();
+  }
+  if (alive) cudaStreamSynchronize(c->stream);
+  else cudaDeviceSynchronize();
+}
+
 // ---------------------------------------------------------------------------
 // context
 // ---------------------------------------------------------------------------
@@ -247,12 +267,20 @@ extern "C" int kc_ctx_create(int device, kc_ctx_t* out) {
   cudaEventCreate(&c->step_a);
   cudaEventCreate(&c->step_b);
   g_live++;
+  {
+    std::lock_guard<std::mutex> lk(g_ctx_mu);
+    g_ctxs.push_back(c);
+  }
   *out = c;
   return KC_OK;
 }
 
 extern "C" void kc_ctx_destroy(kc_ctx_t c) {
   if (!c) return;
+  {
+    std::lock_guard<std::mutex> lk(g_ctx_mu);
+    g_ctxs.erase(std::remove(g_ctxs.begin(), g_ctxs.end(), c), g_ctxs.end());
+  }
   cudaSetDevice(c->device);
   cudaStreamSynchronize(c->stream);
   for (auto& sp : c->spans) { cudaEventDestroy(sp.a); cudaEventDestroy(sp.b); }
@@ -371,7 +399,7 @@ extern "C" int kc_kv_create(kc_ctx_t c, int32_t layers, int32_t kv_heads, int32_
   if (rows > 0x7fffffffull) return fail(KC_ERR_UNSUPPORTED, "kc_kv_create: %zu pool rows overflow i32 addressing", rows);
   CK(cudaSetDevice(c->device));
   kc_kv* kv = new kc_kv;
-  kv->ctx = c; kv->layers = layers; kv->kv_heads = kv_heads; kv->head_dim = head_dim;
+  kv->ctx = c; kv->device = c->device; kv->layers = layers; kv->kv_heads = kv_heads; kv->head_dim = head_dim;
   kv->num_blocks = num_blocks; kv->block_size = block_size;
   kv->block_elems = (size_t)kv_heads * block_size * head_dim;
   kv->bytes = rows * head_dim * sizeof(bf16);
@@ -394,8 +422,7 @@ extern "C" int kc_kv_create(kc_ctx_t c, int32_t layers, int32_t kv_heads, int32_
 
 extern "C" void kc_kv_free(kc_kv_t kv) {
   if (!kv) return;
-  cudaSetDevice(kv->ctx->device);
-  cudaStreamSynchronize(kv->ctx->stream);
+  quiesce(kv->ctx, kv->device);
   cudaFree(kv->pool);
   delete kv;
   g_live--;
@@ -542,7 +569,7 @@ extern "C" int kc_qweight_create(kc_ctx_t c, const uint32_t* w, const void* scal
     return rc;
   }
   kc_qweight* q = new kc_qweight;
-  q->ctx = c;
+  q->ctx = c; q->device = c->device;
   cudaError_t e = qweight_build(&q->w, (const uint32_t*)dw, (const bf16*)ds, (const bf16*)db, out_features,
                                 in_features, bits, group_size, c->sm_count, c->stream);
   if (e == cudaSuccess) {
@@ -561,8 +588,7 @@ extern "C" int kc_qweight_create(kc_ctx_t c, const uint32_t* w, const void* scal
 
 extern "C" void kc_qweight_free(kc_qweight_t q) {
   if (!q) return;
-  cudaSetDevice(q->ctx->device);
-  cudaStreamSynchronize(q->ctx->stream);
+  quiesce(q->ctx, q->device);
   qweight_free(&q->w);
   cudaFree(q->partial);
   delete q;
@@ -832,7 +858,7 @@ extern "C" int kc_model_load(kc_ctx_t c, const kc_model_desc* desc, const kc_ten
   }
 
   kc_model* m = new kc_model;
-  m->ctx = c; m->d = d; m->d.tp_world = tp;
+  m->ctx = c; m->device = c->device; m->d = d; m->d.tp_world = tp;
   m->Hq = d.num_heads / tp; m->Hkv = d.num_kv_heads / tp; m->F = d.intermediate_size / tp;
   m->n_qkv = (m->Hq + 2 * m->Hkv) * d.head_dim;
   const int H = d.hidden_size, D = d.head_dim, V = d.vocab_size;
@@ -976,8 +1002,7 @@ extern "C" int kc_model_load(kc_ctx_t c, const kc_model_desc* desc, const kc_ten
 
 extern "C" void kc_model_free(kc_model_t m) {
   if (!m) return;
-  cudaSetDevice(m->ctx->device);
-  cudaStreamSynchronize(m->ctx->stream);
+  quiesce(m->ctx, m->device);
   free_model(m);
   g_live--;
 }

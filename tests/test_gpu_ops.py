@@ -147,3 +147,24 @@ def test_greedy_rows_by_the_thousand(ctx, vocab):
     edge = _boundary_rows(vocab, 24, vocab)
     got = api.greedy_rows(ctx, edge.cuda(), True).cpu().numpy().astype(np.uint32)
     assert np.array_equal(got, O.greedy_rows(edge, True)), "a row next to a logsumexp rounding boundary rounded the other way"
+
+
+def test_handles_may_outlive_their_context(ctx):
+    """The convention is handles first, context last; a garbage-collected host language does not promise an order, so a
+    pool or a weight freed after its context must not touch the context's stream (it synchronises the device)."""
+    import ctypes as C
+    from kiln_b200 import _lib as L
+    before = api.live_objects()
+    c2 = api.Context(0)
+    kv = api.PagedKv(c2, api.KvSpec(layers=1, kv_heads=2, head_dim=64, num_blocks=4, block_size=16))
+    p = torch.randint(0, 2 ** 31 - 1, (128, 32), dtype=torch.int32)
+    s = torch.full((128, 4), 0.01, dtype=torch.bfloat16)
+    qw = api.QuantizedWeight(c2, p.cuda(), s.cuda(), s.cuda(), 4, 64)
+    c2._children.discard(kv)
+    c2._children.discard(qw)
+    L.lib().kc_ctx_destroy(c2._h)            # the context goes first
+    c2._h = C.c_void_p()
+    kv.close()
+    qw.close()
+    assert api.live_objects() == before
+    assert ctx.device_status() == 0
