@@ -278,12 +278,15 @@ def test_engine_pipelines_plain_decode_on_the_device(ctx):
     assert ctx.device_status() == 0
 
 
-@pytest.mark.parametrize("name", ["tiny-llama", "tiny-qwen2", "tiny-gemma2", "tiny-llama-h2048"])
-def test_stream_lane_decode_logits_match_oracle(ctx, name):
-    """A model with the weight-streaming lane on (kc_model_set_stream_lane): decode forwards of 1..8 rows against the
-    oracle, and kc_draft_chain == the same steps taken one by one."""
+@pytest.mark.parametrize("every_weight", [True, False])
+@pytest.mark.parametrize("name", ["tiny-llama", "tiny-qwen2", "tiny-gemma2", "tiny-llama-h2048", "tiny-llama-wide"])
+def test_stream_lane_decode_logits_match_oracle(ctx, name, every_weight):
+    """A model with the small-step lanes on (kc_model_set_stream_lane): decode forwards of 1..8 rows against the
+    oracle, and kc_draft_chain == the same steps taken one by one. every_weight: all weights through the streaming
+    kernel; otherwise the size rule, which puts these small models' weights on the small-weight kernel (with the gated
+    activation folded into the down projection where the shapes allow it)."""
     cfg, model, kv, omodel, okv = load(ctx, name)
-    model.set_stream_lane(True, every_weight=True)   # the test models' weights are far below the lane's size threshold
+    model.set_stream_lane(True, every_weight=every_weight)
     ps = prompts(cfg, [21, 9, 30], 8)
     tables = [[3, 8], [5], [1, 2]]
     seqs = [api.SeqStep(len(p), 0, 1, t) for p, t in zip(ps, tables)]
