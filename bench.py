@@ -701,7 +701,7 @@ def draft_lane_line(args, metric, config, warmup):
     max_step = 256
     model = api.CudaModel(ctx, cfg, ck, max_step_tokens=max_step, max_step_seqs=4)
     dmodel = api.CudaModel(ctx, dcfg, dck, max_step_tokens=max_step, max_step_seqs=4)
-    dmodel.set_stream_lane(True)     # the draft's chained decode forwards take the weight-streaming kernels
+    dmodel.set_stream_lane(True)     # the draft's chained decode forwards take the streaming and the small-weight kernels
     del ck, dck
     bs, nb = 16, 64 + (hi + gen + 64) // 16
     kv = api.PagedKv(ctx, model.kv_spec(nb, bs))
@@ -786,7 +786,7 @@ def draft_lane_line(args, metric, config, warmup):
         "draft_lane": {"us_per_proposed_token": draft_us, "hbm_floor_us": floor_us, "frac_of_hbm_floor": floor_us / draft_us,
                        "proposed_tokens": d_tok, "chains": d_calls,
                        "draft_weight_bytes": weight_bytes(dcfg), "peak_source": pk["source"],
-                       "lane": "weight-streaming kernels (kc_model_set_stream_lane) for the chained one-row forwards"},
+                       "lane": "kc_model_set_stream_lane: streaming kernel for the head, small-weight kernel for the layers (gated activation folded into the down projection, arg-max into the head's reduction)"},
         "injected_acceptance": injected,
         "stream_gemv": gemv,
         "verify_forward": {"p50_device_ms": verify_ms, "hbm_floor_ms": verify_floor_ms, "frac_of_hbm_floor": verify_floor_ms / verify_ms,
