@@ -42,18 +42,20 @@ def bench_qlinear(args) -> dict:
     y = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
     torch.cuda.synchronize()
     lib = L.lib()
+    # the lane: the tensor-core kernel, or (at most 8 rows) the weight-streaming or the small-weight kernel
+    entry = {"tensor": lib.kc_quantized_matmul, "stream": lib.kc_quantized_matmul_stream, "gemv": lib.kc_quantized_matmul_gemv}[args.lane]
     for i in range(max(args.warmup, copies)):
-        api.check(lib.kc_quantized_matmul(ctx._h, qws[i % copies]._h, x.data_ptr(), m, y.data_ptr()))
+        api.check(entry(ctx._h, qws[i % copies]._h, x.data_ptr(), m, y.data_ptr()))
     ctx.sync()
     stream, e0, e1 = _events(ctx)
     e0.record(stream)
     for i in range(args.iters):
-        api.check(lib.kc_quantized_matmul(ctx._h, qws[i % copies]._h, x.data_ptr(), m, y.data_ptr()))
+        api.check(entry(ctx._h, qws[i % copies]._h, x.data_ptr(), m, y.data_ptr()))
     e1.record(stream)
     ctx.sync()
     us = e0.elapsed_time(e1) * 1e3 / args.iters
     flops = 2.0 * m * n * k
-    out = {"op": "qlinear", "N": n, "K": k, "rows": m, "bits": args.bits, "group": args.group, "copies": copies, "us": us,
+    out = {"op": "qlinear", "lane": args.lane, "N": n, "K": k, "rows": m, "bits": args.bits, "group": args.group, "copies": copies, "us": us,
            "tflops": flops / us / 1e6, "weight_gbs": wbytes / us / 1e3}
     for qw in qws:
         qw.close()
@@ -115,6 +117,8 @@ def main(argv=None):
     a.add_argument("--bits", type=int, default=4)
     a.add_argument("--group", type=int, default=64)
     a.add_argument("--copies", type=int, default=0, help="separate weight copies to rotate over (0: more than 2 x L2 in total)")
+    a.add_argument("--lane", choices=["tensor", "stream", "gemv"], default="tensor",
+                   help="tensor: kc_quantized_matmul; stream / gemv: the two small-step lanes (at most 8 rows; the time includes the reduction of their partials)")
     b = sub.add_parser("attention")
     b.add_argument("--seqs", type=int, default=32)
     b.add_argument("--context", type=int, default=1400)
