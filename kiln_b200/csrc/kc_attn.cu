@@ -380,20 +380,50 @@ __global__ void attn_combine_kernel(const AttnParams p, int n_rows) {
   const int c_hi = pos / ATT_CHUNK;
   const int c_lo = p.window > 0 ? max(0, pos - p.window + 1) / ATT_CHUNK : 0;
   const float2* ml = p.part_ml + (size_t)row * p.max_chunks;
+  // Chunks are taken eight at a time with all of a batch's loads issued before the first use: the arithmetic and its
+  // order are those of a chunk-by-chunk loop, the kernel's duration is two round trips to L2 instead of two per chunk.
+  constexpr int CB = 8;
   float mmax = -INFINITY;
-  for (int c = c_lo; c <= c_hi; ++c) mmax = fmaxf(mmax, ml[c].x);
+  for (int c0 = c_lo; c0 <= c_hi; c0 += CB) {
+    float2 v[CB];
+#pragma unroll
+    for (int j = 0; j < CB; ++j) v[j] = c0 + j <= c_hi ? ml[c0 + j] : make_float2(-INFINITY, 0.f);
+#pragma unroll
+    for (int j = 0; j < CB; ++j) mmax = fmaxf(mmax, v[j].x);
+  }
   constexpr int PER = D / 32;
   float acc[PER];
 #pragma unroll
   for (int i = 0; i < PER; ++i) acc[i] = 0.f;
   float lsum = 0.f;
-  for (int c = c_lo; c <= c_hi; ++c) {
-    const float2 v = ml[c];
-    const float w = (v.x == -INFINITY) ? 0.f : exp2f(v.x - mmax);
-    lsum += w * v.y;
-    const float* po = p.part_o + ((size_t)row * p.max_chunks + c) * D + lane * PER;
+  for (int c0 = c_lo; c0 <= c_hi; c0 += CB) {
+    float2 v[CB];
+    float po[CB][PER];
 #pragma unroll
-    for (int i = 0; i < PER; ++i) acc[i] += w * po[i];
+    for (int j = 0; j < CB; ++j) {
+      const bool on = c0 + j <= c_hi;
+      v[j] = on ? ml[c0 + j] : make_float2(-INFINITY, 0.f);
+      const float* src = p.part_o + ((size_t)row * p.max_chunks + (on ? c0 + j : c_lo)) * D + lane * PER;
+      if (PER % 4 == 0) {
+#pragma unroll
+        for (int i = 0; i < PER; i += 4) {
+          const float4 q = on ? *reinterpret_cast<const float4*>(src + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+          po[j][i] = q.x; po[j][i + 1] = q.y; po[j][i + 2] = q.z; po[j][i + 3] = q.w;
+        }
+      } else {
+        const float2 q = on ? *reinterpret_cast<const float2*>(src) : make_float2(0.f, 0.f);
+        po[j][0] = q.x; po[j][PER - 1] = q.y;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < CB; ++j) {
+      if (c0 + j <= c_hi) {
+        const float w = (v[j].x == -INFINITY) ? 0.f : exp2f(v[j].x - mmax);
+        lsum += w * v[j].y;
+#pragma unroll
+        for (int i = 0; i < PER; ++i) acc[i] += w * po[j][i];
+      }
+    }
   }
   bf16* out = p.out + (size_t)row * D + lane * PER;
 #pragma unroll
