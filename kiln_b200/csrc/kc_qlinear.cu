@@ -1168,24 +1168,16 @@ __global__ void __launch_bounds__(QV_THREADS) qlinear_gemv_kernel(const QvParams
       }
     }
     *reinterpret_cast<uint4*>(xs + (size_t)m * row_elems + c8 * 8) = v;
+    // the sum of x per (k-block, scale group, row) in the same pass: the 64 / GPK features of a group are the chunks of
+    // 8 / GPK neighbouring threads (the loop's trip count is a multiple of 64, so a warp is in it whole or not at all)
+    const float2 e0 = unpack_bf162(v.x), e1 = unpack_bf162(v.y), e2 = unpack_bf162(v.z), e3 = unpack_bf162(v.w);
+    float sx = ((e0.x + e0.y) + (e1.x + e1.y)) + ((e2.x + e2.y) + (e3.x + e3.y));
+    sx += __shfl_xor_sync(0xffffffffu, sx, 1);
+    sx += __shfl_xor_sync(0xffffffffu, sx, 2);
+    if (GPK == 1) sx += __shfl_xor_sync(0xffffffffu, sx, 4);
+    if ((c8 & (8 / GPK - 1)) == 0) xsum[(size_t)((c8 >> 3) * GPK + ((c8 & 7) >> (GPK == 1 ? 3 : 2))) * 8 + m] = sx;
   }
   __syncthreads();
-  // sums of x per (k-block, scale group, row)
-  for (int i = threadIdx.x; i < nkb * GPK * 8; i += QV_THREADS) {
-    const int m = i & 7, q = (i >> 3) % GPK, kbl = i / (8 * GPK);
-    constexpr int SPAN = QL_KB / GPK;
-    const bf16* src = xs + (size_t)m * row_elems + kbl * QL_KB + q * SPAN;
-    float s0 = 0.f;
-#pragma unroll
-    for (int e = 0; e < SPAN; e += 8) {
-      const uint4 v = *reinterpret_cast<const uint4*>(src + e);
-      const float2 a = unpack_bf162(v.x), b = unpack_bf162(v.y), c = unpack_bf162(v.z), d = unpack_bf162(v.w);
-      s0 += ((a.x + a.y) + (b.x + b.y)) + ((c.x + c.y) + (d.x + d.y));
-    }
-    xsum[(size_t)(kbl * GPK + q) * 8 + m] = s0;
-  }
-  __syncthreads();
-
   const int g = lane >> 2, t = lane & 3;
   const int r0 = warp * 16 + g;
   const uint32_t lane_off = (uint32_t)r0 * ROW_BYTES + t * (4 * LANE_WORDS);
